@@ -1,0 +1,166 @@
+/*
+ * wtc_launch.h -- thin C-ABI launch layer for the fused Matmul -> row-Softmax
+ * chain  Out[b,M,N] = softmax_row(scale * A[b,M,K] . B[b,K,N])  on sm_100a.
+ *
+ * This is the device boundary of the chain.  In the reference the same boundary
+ * is the `welder-profiler` tool, which JIT-loads the PTX embedded in
+ * 05.out.nvvm.runnable.mlir and launches it through the CUDA driver API
+ * (backend/welder/compiler/solver/WelderProfiler.cpp:296-303 context/stream,
+ * :321-340 buffers, :359-428 module load, :752-793 warm-up + timed launch loop).
+ * Here the kernels are precompiled for sm_100a and the host side (runner,
+ * harness, bindings) reaches them only through the entry points below.
+ *
+ * Rules of the ABI: plain C types; every pointer named "device" is a CUDA device
+ * pointer owned by the caller; calls are asynchronous on `stream` unless stated;
+ * return 0 on success, a negative WTC_E_* code otherwise (wtc_last_error() gives
+ * the text for the calling thread); no exceptions cross the boundary; there is no
+ * CPU fallback -- without a usable CUDA device every launch fails with
+ * WTC_E_CUDA.
+ */
+#ifndef WTC_LAUNCH_H
+#define WTC_LAUNCH_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define WTC_ABI_VERSION 1
+
+/* element types */
+#define WTC_F32 0
+#define WTC_F16 1
+
+/* variants: the reference compiles the same chain twice -- one fused kernel, or a
+ * five-kernel baseline with intermediates in global memory
+ * (compiler/transform/BuildCutEdgesTransformCommon.cpp:27-34). */
+#define WTC_VARIANT_FUSED 0
+#define WTC_VARIANT_BASELINE 1
+
+/* flags */
+#define WTC_FLAG_FORCE_SIMT 0x1   /* never use the tensor-core kernels            */
+#define WTC_FLAG_FORCE_TILED 0x2  /* two-pass tiled kernel even if a cluster fits  */
+
+/* error codes */
+#define WTC_OK 0
+#define WTC_E_ARG (-1)        /* null pointer, bad size, unknown dtype ...            */
+#define WTC_E_UNSUPPORTED (-2)/* a legal request no kernel here covers               */
+#define WTC_E_WORKSPACE (-3)  /* workspace missing or too small                      */
+#define WTC_E_CUDA (-4)       /* a CUDA call failed (no device, launch error ...)    */
+#define WTC_E_DEVICE (-5)     /* a kernel reported a non-zero device status word     */
+
+/* Which kernel family a descriptor resolves to (wtc_plan_query). */
+#define WTC_KERNEL_SIMT_FUSED 0
+#define WTC_KERNEL_TC_CLUSTER 1   /* tcgen05, cluster of CTAs per 128 rows, one launch   */
+#define WTC_KERNEL_TC_TILED 2     /* tcgen05 tiles + row rescale, two launches           */
+#define WTC_KERNEL_SIMT_UNFUSED 3 /* five launches (baseline variant)                    */
+
+/*
+ * The chain, as the compiler front-end recognised it.  Strides are in elements;
+ * 0 means dense (lda = K, ldb = N, ldo = N, batch strides = rows * ld).
+ * b_batch_stride < 0 means one B shared by every batch.
+ * tile_* carry the tile choice of best.json (tileM/tileN/tileK,
+ * compiler/include/wtc/scheduler/Search.h:11-17); 0 lets the library choose.
+ * As in the reference's fused mode the softmax row is never cut: tile_n < N
+ * selects a multi-CTA (cluster) or two-pass schedule, not a narrower softmax.
+ */
+typedef struct wtc_chain_desc {
+  int32_t struct_size; /* sizeof(wtc_chain_desc) */
+  int32_t batch;
+  int64_t M, N, K;
+  int64_t lda, ldb, ldo;
+  int64_t a_batch_stride, b_batch_stride, o_batch_stride;
+  int32_t in_dtype;  /* WTC_F32 | WTC_F16 (A and B) */
+  int32_t out_dtype; /* WTC_F32 | WTC_F16 */
+  int32_t acc_dtype; /* WTC_F32, or WTC_F16 when the chain spells an f16 matmul result */
+  float scale;
+  int32_t tile_m, tile_n, tile_k;
+  int32_t variant; /* WTC_VARIANT_* */
+  int32_t flags;   /* WTC_FLAG_* */
+} wtc_chain_desc;
+
+typedef struct wtc_plan_info {
+  int32_t kernel;       /* WTC_KERNEL_* */
+  int32_t launches;     /* kernel launches per call */
+  int32_t tile_m, tile_n, tile_k; /* tile actually used (after legalisation) */
+  int32_t cluster_n;    /* CTAs per cluster along N (1 if none) */
+  int32_t grid, threads, smem_bytes; /* main kernel; grid is 0 until a device is known */
+  int32_t tmem_columns; /* tensor-memory columns allocated per CTA */
+  int32_t stages;       /* shared-memory pipeline depth */
+  int32_t tile_substituted; /* 1 if a requested tile_* was not legal and was replaced */
+  size_t workspace_bytes;
+} wtc_plan_info;
+
+/* ABI version of the loaded library (== WTC_ABI_VERSION of its build). */
+int wtc_abi_version(void);
+
+/* Text of the last error on this thread ("" if none).  Never NULL. */
+const char *wtc_last_error(void);
+
+/* Resolve a descriptor to a kernel plan without touching the device. */
+int wtc_plan_query(const wtc_chain_desc *desc, wtc_plan_info *out);
+
+/* Scratch memory (global memory beyond inputs and outputs) a launch needs. */
+int wtc_matmul_softmax_workspace_bytes(const wtc_chain_desc *desc, size_t *bytes);
+
+/*
+ * Launch the chain.  A, B, Out, workspace: device pointers.  stream: a
+ * cudaStream_t (NULL = default stream).  device_status: optional device pointer
+ * to one int32 the caller zeroed; kernels store a non-zero code there instead of
+ * trapping when a bounded wait gives up (read it after synchronising, or use
+ * wtc_check_device_status).  Replaces the launch loop body of
+ * WelderProfiler.cpp:773-786.
+ */
+int wtc_matmul_softmax_launch(const wtc_chain_desc *desc, const void *A, const void *B, void *Out,
+                              void *workspace, size_t workspace_bytes, void *stream, int *device_status);
+
+/*
+ * N-sharded use (one shard of the columns per GPU): `partial` runs the chain on
+ * this shard's columns, leaving un-normalised exp() values in Out and the
+ * shard's per-row (max, sum) pairs -- maxima in the log2 domain -- in
+ * row_stats[batch*M] (device, 2 floats per row).  After the shards' row_stats
+ * have been gathered into all_stats[num_parts][batch*M] (device), `finish`
+ * normalises Out against the whole row.  The reference has no counterpart: it is
+ * single-GPU (WelderProfiler.cpp:296-303).
+ */
+int wtc_matmul_softmax_partial_launch(const wtc_chain_desc *desc, const void *A, const void *B, void *Out,
+                                      void *workspace, size_t workspace_bytes, void *row_stats,
+                                      void *stream, int *device_status);
+int wtc_matmul_softmax_finish_launch(const wtc_chain_desc *desc, void *Out, const void *workspace,
+                                     const void *all_stats, int32_t num_parts, void *stream);
+
+/*
+ * Whole call with HOST buffers: copies A and B to the device, launches, copies
+ * Out back and synchronises.  Device buffers are cached per thread between calls.
+ * This is what a host-side caller of the reference would otherwise do around the
+ * profiler's cuMemcpyHtoD / launch / dump sequence (WelderProfiler.cpp:601-677,
+ * :808-864).
+ */
+int wtc_matmul_softmax_host(const wtc_chain_desc *desc, const void *hostA, const void *hostB, void *hostOut);
+
+/* Synchronise `stream`, read a device status word, 0 if clean else WTC_E_DEVICE. */
+int wtc_check_device_status(const int *device_status, void *stream);
+
+/*
+ * Timed launch loop with CUDA events on `stream`: `warmup` untimed launches, then
+ * `iters` back-to-back launches between two events; *avg_ms = elapsed / iters.
+ * Same method as WelderProfiler.cpp:752-793.
+ */
+int wtc_matmul_softmax_time(const wtc_chain_desc *desc, const void *A, const void *B, void *Out,
+                            void *workspace, size_t workspace_bytes, void *stream, int warmup, int iters,
+                            float *avg_ms);
+
+/*
+ * Bring-up aid: override the UMMA shared-memory descriptor geometry (byte
+ * offsets: leading / stride / per-MMA K step, for A then B) used by the
+ * tensor-core kernels.  Pass all zeros to restore the built-in values.
+ */
+int wtc_debug_set_umma_geometry(uint32_t a_lbo, uint32_t a_sbo, uint32_t a_kstep, uint32_t b_lbo,
+                                uint32_t b_sbo, uint32_t b_kstep);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WTC_LAUNCH_H */

@@ -1,0 +1,111 @@
+// Bandwidth-bound companions of the tiled kernel: combine per-tile (max, sum)
+// pairs into per-row statistics and rescale the stored exp(v - tile max) values
+// into probabilities.  All maxima are in the log2 domain (v = scale*log2(e)*s).
+#include "wtc_kernels.h"
+#include "wtc_ptx.cuh"
+
+namespace wtc {
+namespace {
+
+__device__ __forceinline__ float2 lse_combine(float2 a, float2 b) {
+  // (max, sum) pairs of disjoint column sets -> pair of their union
+  const float m = fmaxf(a.x, b.x);
+  if (m == -INFINITY) return make_float2(m, 0.f);
+  return make_float2(m, a.y * ex2_approx(a.x - m) + b.y * ex2_approx(b.x - m));
+}
+
+__device__ __forceinline__ float2 warp_lse(float2 v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float2 other = make_float2(__shfl_xor_sync(0xffffffffu, v.x, o), __shfl_xor_sync(0xffffffffu, v.y, o));
+    v = lse_combine(v, other);
+  }
+  return v;
+}
+
+// one warp per row
+__global__ void row_stats_kernel(const float2 *__restrict__ tile_stats, float2 *__restrict__ row_stats,
+                                 int64_t rows, int num_nb) {
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  float2 v = make_float2(-INFINITY, 0.f);
+  for (int t = lane; t < num_nb; t += 32) v = lse_combine(v, tile_stats[row * num_nb + t]);
+  v = warp_lse(v);
+  if (lane == 0) row_stats[row] = v;
+}
+
+// one CTA per row
+__global__ void __launch_bounds__(256)
+rescale_rows_kernel(__half *__restrict__ out, int N, int64_t ld_out, int BN, int num_nb,
+                    const float2 *__restrict__ tile_stats, const float2 *__restrict__ global_stats,
+                    int num_parts, int64_t rows) {
+  extern __shared__ float factor[];          // [num_nb]
+  __shared__ float2 warp_part[8];
+  __shared__ float2 row_total;
+  const int64_t row = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+
+  float2 v = make_float2(-INFINITY, 0.f);
+  if (global_stats) {
+    for (int t = threadIdx.x; t < num_parts; t += blockDim.x) v = lse_combine(v, global_stats[static_cast<int64_t>(t) * rows + row]);
+  } else {
+    for (int t = threadIdx.x; t < num_nb; t += blockDim.x) v = lse_combine(v, tile_stats[row * num_nb + t]);
+  }
+  v = warp_lse(v);
+  if (lane == 0) warp_part[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float2 t = lane < (blockDim.x >> 5) ? warp_part[lane] : make_float2(-INFINITY, 0.f);
+    t = warp_lse(t);
+    if (lane == 0) row_total = t;
+  }
+  __syncthreads();
+  const float gm = row_total.x;
+  const float inv = 1.0f / row_total.y;
+  for (int t = threadIdx.x; t < num_nb; t += blockDim.x)
+    factor[t] = ex2_approx(tile_stats[row * num_nb + t].x - gm) * inv;
+  __syncthreads();
+
+  __half *orow = out + row * ld_out;
+  const bool vec_ok = (N % 8 == 0) && (ld_out % 8 == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0) && (BN % 8 == 0);
+  if (vec_ok) {
+    uint4 *o4 = reinterpret_cast<uint4 *>(orow);
+    for (int j = threadIdx.x; j < N / 8; j += blockDim.x) {
+      const float f = factor[(j * 8) / BN];
+      uint4 x = o4[j];
+      __half2 *h = reinterpret_cast<__half2 *>(&x);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float2 t = __half22float2(h[i]);
+        h[i] = __floats2half2_rn(t.x * f, t.y * f);
+      }
+      o4[j] = x;
+    }
+  } else {
+    for (int j = threadIdx.x; j < N; j += blockDim.x)
+      orow[j] = __float2half_rn(__half2float(orow[j]) * factor[j / BN]);
+  }
+}
+
+} // namespace
+
+cudaError_t launch_row_stats(const float2 *tile_stats, float2 *row_stats_out, int64_t rows, int num_nb,
+                             cudaStream_t s) {
+  if (rows <= 0) return cudaSuccess;
+  const int warps = 8;
+  const unsigned grid = static_cast<unsigned>((rows + warps - 1) / warps);
+  row_stats_kernel<<<grid, warps * 32, 0, s>>>(tile_stats, row_stats_out, rows, num_nb);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_rescale_rows(void *out_f16, int64_t rows, int N, int64_t ld_out, int BN, int num_nb,
+                                const float2 *tile_stats, const float2 *global_stats, int num_parts,
+                                cudaStream_t s) {
+  if (rows <= 0) return cudaSuccess;
+  rescale_rows_kernel<<<static_cast<unsigned>(rows), 256, num_nb * sizeof(float), s>>>(
+      static_cast<__half *>(out_f16), N, ld_out, BN, num_nb, tile_stats, global_stats, num_parts, rows);
+  return cudaGetLastError();
+}
+
+} // namespace wtc

@@ -1,0 +1,77 @@
+// Host-visible declarations of the kernel launchers.  The launch layer
+// (wtc_launch.cu) is the only caller.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace wtc {
+
+// UMMA shared-memory descriptor geometry, kept as data so a known-answer run
+// can check the operand layouts without a rebuild.  Bytes.
+struct UmmaGeom {
+  uint32_t a_lbo, a_sbo, a_kstep;
+  uint32_t b_lbo, b_sbo, b_kstep;
+};
+
+struct TcParams {
+  int batch, M, N, K;
+  int num_rb;      // row blocks of 128 per batch
+  int num_nb;      // column blocks of BN per row
+  int num_kb;      // K blocks of 64
+  int num_items;   // work items: cluster mode batch*num_rb, tiled mode batch*num_rb*num_nb
+  int b_batched;   // B has its own batch dimension
+  int group_rb;    // tiled mode: row blocks per rasterisation group
+  int round_logits_f16;  // chain spelled with an f16 matmul result: round s to f16 before the softmax
+  float c2;        // scale * log2(e)
+  float2 *tile_stats;    // tiled mode: [batch*M][num_nb] (max in log2 domain, sum of 2^(v-max))
+  int *status;     // device status word (0 = ok)
+  UmmaGeom geom;
+};
+
+struct TcLaunchInfo {
+  int grid, cluster, smem_bytes, threads;
+};
+
+// Fused cluster kernel: a cluster of ceil(N/BN) CTAs owns 128 full rows, exchanges
+// per-row (max, sum) through distributed shared memory and writes probabilities.
+cudaError_t launch_fused_cluster(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO,
+                                 const TcParams &p, int cluster_n, int num_sms, cudaStream_t s,
+                                 TcLaunchInfo *info);
+// Tiled kernel: independent 128 x BN tiles write exp(v - tile max) and per-tile
+// (max, sum); rescale_rows() then normalises the rows.
+cudaError_t launch_tiled_partial(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO,
+                                 const TcParams &p, int num_sms, cudaStream_t s, TcLaunchInfo *info);
+
+// rows = batch*M.  tile_stats [rows][num_nb].  row_stats_out (optional) receives
+// the per-row combination over this launch's tiles.  global_stats (optional):
+// [num_parts][rows] (max, sum) pairs covering the WHOLE row (all N shards); when
+// given, rows are normalised against their combination instead of the local one.
+cudaError_t launch_row_stats(const float2 *tile_stats, float2 *row_stats_out, int64_t rows, int num_nb,
+                             cudaStream_t s);
+cudaError_t launch_rescale_rows(void *out_f16, int64_t rows, int N, int64_t ld_out, int BN, int num_nb,
+                                const float2 *tile_stats, const float2 *global_stats, int num_parts,
+                                cudaStream_t s);
+
+// SIMT kernels: any shape, f32 or f16 operands, f32 or f16 output.
+struct SimtParams {
+  int batch, M, N, K;
+  int64_t lda, ldb, ldo;
+  int64_t a_batch_stride, b_batch_stride, o_batch_stride;
+  int in_f16, out_f16;
+  int acc_mode;  // 0 f32 accumulate, 1 round the finished sum to f16 (f16 matmul result)
+  float scale;
+};
+cudaError_t launch_simt_fused(const void *A, const void *B, void *Out, const SimtParams &p, cudaStream_t s);
+// Unfused five-kernel pipeline: matmul -> row max -> exp -> row sum -> divide,
+// with C32[M,N], max[M], E[M,N], sum[M] in global memory (workspace).
+cudaError_t launch_simt_unfused(const void *A, const void *B, void *Out, void *workspace, const SimtParams &p,
+                                cudaStream_t s);
+size_t simt_unfused_workspace_bytes(const SimtParams &p);
+
+constexpr int kTcBlockM = 128;
+constexpr int kTcBlockK = 64;
+constexpr int kTcBlockN = 256;
+
+} // namespace wtc

@@ -1,0 +1,460 @@
+// C-ABI launch layer (see include/wtc_launch.h for the contract).  Resolves a
+// chain descriptor to one of the kernel families, encodes and caches the TMA
+// tensor maps, and launches.  No CPU fallback: without a CUDA device every
+// launch returns WTC_E_CUDA.
+#include "../../include/wtc_launch.h"
+
+#include "wtc_kernels.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(int code, const char *fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+  return code;
+}
+
+int cuda_fail(cudaError_t e, const char *what) {
+  return fail(WTC_E_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+// built-in UMMA descriptor geometry (bytes):
+//   A (K-major, 128-byte swizzle): 8-row groups are 1024 B apart; one 16-wide K step is 32 B.
+//   B (MN-major, 128-byte swizzle): 64-column blocks are 64 k-rows * 128 B = 8192 B apart
+//   (leading), 8-k-row groups are 1024 B apart (stride); one 16-deep K step is 16 * 128 B.
+constexpr wtc::UmmaGeom kDefaultGeom = {16, 1024, 32, 8192, 1024, 2048};
+wtc::UmmaGeom g_geom = kDefaultGeom;
+
+struct Resolved {
+  wtc_chain_desc d;  // strides filled in
+  wtc_plan_info plan;
+  int num_rb, num_nb, num_kb;
+  bool b_batched;
+  bool tc_ok;
+};
+
+bool mult8(int64_t v) { return (v & 7) == 0; }
+
+int resolve(const wtc_chain_desc *in, Resolved &r) {
+  if (!in) return fail(WTC_E_ARG, "null descriptor");
+  if (in->struct_size != static_cast<int32_t>(sizeof(wtc_chain_desc)))
+    return fail(WTC_E_ARG, "descriptor struct_size %d does not match this library (%zu)", in->struct_size,
+                sizeof(wtc_chain_desc));
+  r.d = *in;
+  wtc_chain_desc &d = r.d;
+  if (d.batch < 1) return fail(WTC_E_ARG, "batch must be >= 1 (got %d)", d.batch);
+  if (d.M < 0 || d.N < 0 || d.K < 0) return fail(WTC_E_ARG, "negative extent M=%lld N=%lld K=%lld", (long long)d.M, (long long)d.N, (long long)d.K);
+  if (d.M > 0x7fffffff || d.N > 0x7fffffff || d.K > 0x7fffffff) return fail(WTC_E_ARG, "extent exceeds 2^31-1");
+  if ((d.in_dtype != WTC_F32 && d.in_dtype != WTC_F16) || (d.out_dtype != WTC_F32 && d.out_dtype != WTC_F16) ||
+      (d.acc_dtype != WTC_F32 && d.acc_dtype != WTC_F16))
+    return fail(WTC_E_ARG, "unknown dtype (in=%d out=%d acc=%d)", d.in_dtype, d.out_dtype, d.acc_dtype);
+  if (d.variant != WTC_VARIANT_FUSED && d.variant != WTC_VARIANT_BASELINE) return fail(WTC_E_ARG, "unknown variant %d", d.variant);
+  if (d.tile_m < 0 || d.tile_n < 0 || d.tile_k < 0) return fail(WTC_E_ARG, "negative tile size");
+  if (d.lda == 0) d.lda = d.K;
+  if (d.ldb == 0) d.ldb = d.N;
+  if (d.ldo == 0) d.ldo = d.N;
+  if (d.lda < d.K || d.ldb < d.N || d.ldo < d.N) return fail(WTC_E_ARG, "row stride smaller than the row");
+  r.b_batched = d.b_batch_stride >= 0;
+  if (d.a_batch_stride == 0) d.a_batch_stride = d.M * d.lda;
+  if (d.b_batch_stride == 0) d.b_batch_stride = d.K * d.ldb;
+  if (d.o_batch_stride == 0) d.o_batch_stride = d.M * d.ldo;
+  if (!r.b_batched) d.b_batch_stride = 0;
+
+  wtc_plan_info &p = r.plan;
+  memset(&p, 0, sizeof(p));
+  p.cluster_n = 1;
+  r.num_rb = static_cast<int>((d.M + wtc::kTcBlockM - 1) / wtc::kTcBlockM);
+  r.num_nb = static_cast<int>((d.N + wtc::kTcBlockN - 1) / wtc::kTcBlockN);
+  r.num_kb = static_cast<int>((d.K + wtc::kTcBlockK - 1) / wtc::kTcBlockK);
+
+  const bool tc_shape = d.in_dtype == WTC_F16 && d.out_dtype == WTC_F16 && d.M > 0 && d.N > 0 && d.K > 0 &&
+                        mult8(d.K) && mult8(d.N) && mult8(d.lda) && mult8(d.ldb) && mult8(d.ldo) &&
+                        mult8(d.a_batch_stride) && mult8(d.b_batch_stride) && mult8(d.o_batch_stride) &&
+                        static_cast<int64_t>(d.batch) * r.num_rb * r.num_nb < 0x7fffffff;
+  r.tc_ok = tc_shape && !(d.flags & WTC_FLAG_FORCE_SIMT) && d.variant == WTC_VARIANT_FUSED;
+
+  if (d.variant == WTC_VARIANT_BASELINE) {
+    p.kernel = WTC_KERNEL_SIMT_UNFUSED;
+    p.launches = 5;
+    p.threads = 256;
+    const size_t rows = static_cast<size_t>(d.batch) * d.M;
+    p.workspace_bytes = (2 * rows * d.N + 2 * rows) * sizeof(float);
+    p.tile_m = 8; p.tile_n = static_cast<int32_t>(d.N); p.tile_k = 64;
+  } else if (r.tc_ok) {
+    p.tile_m = wtc::kTcBlockM; p.tile_n = wtc::kTcBlockN; p.tile_k = wtc::kTcBlockK;
+    p.threads = 192;
+    p.tmem_columns = 2 * wtc::kTcBlockN;
+    if (r.num_nb <= 8 && !(d.flags & WTC_FLAG_FORCE_TILED)) {
+      p.kernel = WTC_KERNEL_TC_CLUSTER;
+      p.launches = 1;
+      p.cluster_n = r.num_nb;
+      p.stages = 3;
+    } else {
+      p.kernel = WTC_KERNEL_TC_TILED;
+      p.launches = 2;
+      p.stages = 4;
+      p.workspace_bytes = static_cast<size_t>(d.batch) * d.M * r.num_nb * sizeof(float2);
+    }
+  } else {
+    p.kernel = WTC_KERNEL_SIMT_FUSED;
+    p.launches = (d.M > 0 && d.N > 0) ? 1 : 0;
+    p.threads = 256;
+    p.tile_m = 16; p.tile_n = static_cast<int32_t>(d.N); p.tile_k = 64;
+  }
+  p.tile_substituted = ((d.tile_m && d.tile_m != p.tile_m) || (d.tile_n && d.tile_n != p.tile_n && d.tile_n < d.N) ||
+                        (d.tile_k && d.tile_k != p.tile_k)) ? 1 : 0;
+  return WTC_OK;
+}
+
+// ---- tensor maps -------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                              const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+std::mutex g_mu;
+EncodeFn g_encode = nullptr;
+
+int get_encoder() {
+  if (g_encode) return WTC_OK;
+  void *fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+  if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) {
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDriverEntryPoint(cuTensorMapEncodeTiled)");
+    return fail(WTC_E_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  }
+  g_encode = reinterpret_cast<EncodeFn>(fn);
+  return WTC_OK;
+}
+
+struct MapKey {
+  const void *ptr;
+  uint64_t d0, d1, d2, s1, s2;
+  uint32_t b0, b1;
+  bool operator==(const MapKey &o) const {
+    return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && d2 == o.d2 && s1 == o.s1 && s2 == o.s2 && b0 == o.b0 && b1 == o.b1;
+  }
+};
+struct MapEntry { MapKey key; CUtensorMap map; };
+std::vector<MapEntry> g_maps;   // small LRU-ish cache, newest at the back
+constexpr size_t kMaxMaps = 256;
+
+// rank-3 f16 tensor (d0 innermost, contiguous), 128-byte swizzle, zero fill
+int get_map(const void *ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1_bytes, uint64_t s2_bytes, uint32_t b0,
+            uint32_t b1, CUtensorMap *out) {
+  MapKey key{ptr, d0, d1, d2, s1_bytes, s2_bytes, b0, b1};
+  std::lock_guard<std::mutex> lk(g_mu);
+  for (size_t i = g_maps.size(); i-- > 0;)
+    if (g_maps[i].key == key) { *out = g_maps[i].map; return WTC_OK; }
+  int rc = get_encoder();
+  if (rc) return rc;
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {s1_bytes, s2_bytes};
+  cuuint32_t box[3] = {b0, b1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUtensorMap m;
+  CUresult cr = g_encode(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(ptr), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (cr != CUDA_SUCCESS)
+    return fail(WTC_E_CUDA, "cuTensorMapEncodeTiled failed (%d) for dims=(%llu,%llu,%llu) strides=(%llu,%llu) box=(%u,%u)",
+                (int)cr, (unsigned long long)d0, (unsigned long long)d1, (unsigned long long)d2,
+                (unsigned long long)s1_bytes, (unsigned long long)s2_bytes, b0, b1);
+  if (g_maps.size() >= kMaxMaps) g_maps.erase(g_maps.begin(), g_maps.begin() + kMaxMaps / 2);
+  g_maps.push_back({key, m});
+  *out = m;
+  return WTC_OK;
+}
+
+int num_sms() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (!cached[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+// per-device status word used when the caller passes none
+int *default_status() {
+  static int *words[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (!words[dev]) {
+    if (cudaMalloc(&words[dev], sizeof(int)) != cudaSuccess) return nullptr;
+    cudaMemset(words[dev], 0, sizeof(int));
+  }
+  return words[dev];
+}
+
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+wtc::SimtParams simt_params(const Resolved &r) {
+  wtc::SimtParams s;
+  s.batch = r.d.batch; s.M = (int)r.d.M; s.N = (int)r.d.N; s.K = (int)r.d.K;
+  s.lda = r.d.lda; s.ldb = r.d.ldb; s.ldo = r.d.ldo;
+  s.a_batch_stride = r.d.a_batch_stride; s.b_batch_stride = r.d.b_batch_stride; s.o_batch_stride = r.d.o_batch_stride;
+  s.in_f16 = r.d.in_dtype == WTC_F16; s.out_f16 = r.d.out_dtype == WTC_F16;
+  s.acc_mode = r.d.acc_dtype == WTC_F16 ? 1 : 0;
+  s.scale = r.d.scale;
+  return s;
+}
+
+// mode: 0 whole chain, 1 partial (leave un-normalised values + row stats)
+int launch_resolved(Resolved &r, const void *A, const void *B, void *Out, void *ws, size_t ws_bytes, void *row_stats,
+                    int mode, cudaStream_t s, int *status) {
+  const wtc_chain_desc &d = r.d;
+  if (d.M == 0 || d.N == 0) return WTC_OK;
+  if (!A || !B || !Out) return fail(WTC_E_ARG, "null operand pointer");
+
+  if (r.plan.kernel == WTC_KERNEL_SIMT_UNFUSED) {
+    if (mode != 0) return fail(WTC_E_UNSUPPORTED, "the baseline variant has no sharded form");
+    if (!ws || ws_bytes < r.plan.workspace_bytes)
+      return fail(WTC_E_WORKSPACE, "baseline variant needs %zu workspace bytes, got %zu", r.plan.workspace_bytes, ws_bytes);
+    cudaError_t e = wtc::launch_simt_unfused(A, B, Out, ws, simt_params(r), s);
+    return e == cudaSuccess ? WTC_OK : cuda_fail(e, "unfused pipeline launch");
+  }
+
+  const bool ptr_ok = aligned16(A) && aligned16(B) && aligned16(Out);
+  bool tiled = r.plan.kernel == WTC_KERNEL_TC_TILED || (mode == 1 && r.tc_ok);
+  if ((r.plan.kernel == WTC_KERNEL_TC_CLUSTER || tiled) && ptr_ok) {
+    const int sms = num_sms();
+    if (sms <= 0) return fail(WTC_E_CUDA, "no usable CUDA device");
+    CUtensorMap tmA, tmB, tmO;
+    int rc = get_map(A, d.K, d.M, d.batch, d.lda * 2, d.a_batch_stride * 2, wtc::kTcBlockK, wtc::kTcBlockM, &tmA);
+    if (rc) return rc;
+    rc = get_map(B, d.N, d.K, r.b_batched ? d.batch : 1, d.ldb * 2, (r.b_batched ? d.b_batch_stride : d.K * d.ldb) * 2, 64,
+                 wtc::kTcBlockK, &tmB);
+    if (rc) return rc;
+    rc = get_map(Out, d.N, d.M, d.batch, d.ldo * 2, d.o_batch_stride * 2, 64, 32, &tmO);
+    if (rc) return rc;
+
+    wtc::TcParams p;
+    memset(&p, 0, sizeof(p));
+    p.batch = d.batch; p.M = (int)d.M; p.N = (int)d.N; p.K = (int)d.K;
+    p.num_rb = r.num_rb; p.num_nb = r.num_nb; p.num_kb = r.num_kb;
+    p.b_batched = r.b_batched;
+    p.group_rb = 16;
+    p.round_logits_f16 = d.acc_dtype == WTC_F16;
+    p.c2 = d.scale * 1.4426950408889634f;
+    p.status = status ? status : default_status();
+    p.geom = g_geom;
+    wtc::TcLaunchInfo info;
+    cudaError_t e;
+    if (!tiled) {
+      p.num_items = d.batch * r.num_rb;
+      e = wtc::launch_fused_cluster(tmA, tmB, tmO, p, r.num_nb, sms, s, &info);
+      if (e != cudaSuccess) return cuda_fail(e, "fused cluster kernel launch");
+      return WTC_OK;
+    }
+    const size_t need = static_cast<size_t>(d.batch) * d.M * r.num_nb * sizeof(float2);
+    if (!ws || ws_bytes < need) return fail(WTC_E_WORKSPACE, "tiled schedule needs %zu workspace bytes, got %zu", need, ws_bytes);
+    p.num_items = d.batch * r.num_rb * r.num_nb;
+    p.tile_stats = static_cast<float2 *>(ws);
+    e = wtc::launch_tiled_partial(tmA, tmB, tmO, p, sms, s, &info);
+    if (e != cudaSuccess) return cuda_fail(e, "tiled kernel launch");
+    const int64_t rows = static_cast<int64_t>(d.batch) * d.M;
+    if (mode == 1) {
+      if (!row_stats) return fail(WTC_E_ARG, "partial launch needs a row_stats buffer");
+      if (d.o_batch_stride != d.M * d.ldo && d.batch > 1) return fail(WTC_E_UNSUPPORTED, "sharded form needs densely stacked batches");
+      e = wtc::launch_row_stats(p.tile_stats, static_cast<float2 *>(row_stats), rows, r.num_nb, s);
+      return e == cudaSuccess ? WTC_OK : cuda_fail(e, "row statistics launch");
+    }
+    if (d.o_batch_stride != d.M * d.ldo && d.batch > 1) return fail(WTC_E_UNSUPPORTED, "tiled schedule needs densely stacked output batches");
+    e = wtc::launch_rescale_rows(Out, rows, (int)d.N, d.ldo, wtc::kTcBlockN, r.num_nb, p.tile_stats, nullptr, 0, s);
+    return e == cudaSuccess ? WTC_OK : cuda_fail(e, "row rescale launch");
+  }
+
+  if (mode != 0) return fail(WTC_E_UNSUPPORTED, "the sharded form needs f16 operands/output with 16-byte aligned rows");
+  cudaError_t e = wtc::launch_simt_fused(A, B, Out, simt_params(r), s);
+  if (e == cudaErrorInvalidValue) return fail(WTC_E_UNSUPPORTED, "N=%lld: one row of logits does not fit shared memory on the SIMT path", (long long)d.N);
+  return e == cudaSuccess ? WTC_OK : cuda_fail(e, "SIMT fused kernel launch");
+}
+
+} // namespace
+
+extern "C" {
+
+int wtc_abi_version(void) { return WTC_ABI_VERSION; }
+
+const char *wtc_last_error(void) { return g_last_error.c_str(); }
+
+int wtc_plan_query(const wtc_chain_desc *desc, wtc_plan_info *out) {
+  if (!out) return fail(WTC_E_ARG, "null plan pointer");
+  Resolved r;
+  int rc = resolve(desc, r);
+  if (rc) return rc;
+  *out = r.plan;
+  return WTC_OK;
+}
+
+int wtc_matmul_softmax_workspace_bytes(const wtc_chain_desc *desc, size_t *bytes) {
+  if (!bytes) return fail(WTC_E_ARG, "null size pointer");
+  Resolved r;
+  int rc = resolve(desc, r);
+  if (rc) return rc;
+  size_t need = r.plan.workspace_bytes;
+  // the sharded form always runs the tiled schedule
+  if (r.tc_ok) {
+    const size_t tiled = static_cast<size_t>(r.d.batch) * r.d.M * r.num_nb * sizeof(float2);
+    if (tiled > need) need = tiled;
+  }
+  *bytes = need;
+  return WTC_OK;
+}
+
+int wtc_matmul_softmax_launch(const wtc_chain_desc *desc, const void *A, const void *B, void *Out, void *workspace,
+                              size_t workspace_bytes, void *stream, int *device_status) {
+  Resolved r;
+  int rc = resolve(desc, r);
+  if (rc) return rc;
+  return launch_resolved(r, A, B, Out, workspace, workspace_bytes, nullptr, 0, static_cast<cudaStream_t>(stream), device_status);
+}
+
+int wtc_matmul_softmax_partial_launch(const wtc_chain_desc *desc, const void *A, const void *B, void *Out, void *workspace,
+                                      size_t workspace_bytes, void *row_stats, void *stream, int *device_status) {
+  Resolved r;
+  int rc = resolve(desc, r);
+  if (rc) return rc;
+  if (!r.tc_ok) return fail(WTC_E_UNSUPPORTED, "the sharded form needs f16 operands/output with 16-byte aligned rows");
+  return launch_resolved(r, A, B, Out, workspace, workspace_bytes, row_stats, 1, static_cast<cudaStream_t>(stream), device_status);
+}
+
+int wtc_matmul_softmax_finish_launch(const wtc_chain_desc *desc, void *Out, const void *workspace, const void *all_stats,
+                                     int32_t num_parts, void *stream) {
+  Resolved r;
+  int rc = resolve(desc, r);
+  if (rc) return rc;
+  if (!r.tc_ok) return fail(WTC_E_UNSUPPORTED, "the sharded form needs f16 operands/output with 16-byte aligned rows");
+  if (r.d.M == 0 || r.d.N == 0) return WTC_OK;
+  if (!Out || !workspace || !all_stats || num_parts < 1) return fail(WTC_E_ARG, "null pointer or num_parts < 1");
+  const int64_t rows = static_cast<int64_t>(r.d.batch) * r.d.M;
+  cudaError_t e = wtc::launch_rescale_rows(Out, rows, (int)r.d.N, r.d.ldo, wtc::kTcBlockN, r.num_nb,
+                                           static_cast<const float2 *>(workspace), static_cast<const float2 *>(all_stats),
+                                           num_parts, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? WTC_OK : cuda_fail(e, "row rescale launch");
+}
+
+int wtc_check_device_status(const int *device_status, void *stream) {
+  cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
+  const int *src = device_status ? device_status : default_status();
+  if (!src) return fail(WTC_E_CUDA, "no status word");
+  int v = 0;
+  e = cudaMemcpy(&v, src, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return cuda_fail(e, "reading the device status word");
+  if (v != 0) {
+    static const char *names[] = {"ok", "a TMA stage never landed", "a pipeline stage was never released",
+                                  "an accumulator never completed", "an accumulator buffer was never drained",
+                                  "cluster peers never sent their row statistics"};
+    return fail(WTC_E_DEVICE, "device status %d: %s", v, (v > 0 && v < 6) ? names[v] : "unknown");
+  }
+  return WTC_OK;
+}
+
+int wtc_matmul_softmax_time(const wtc_chain_desc *desc, const void *A, const void *B, void *Out, void *workspace,
+                            size_t workspace_bytes, void *stream, int warmup, int iters, float *avg_ms) {
+  if (!avg_ms || iters < 1 || warmup < 0) return fail(WTC_E_ARG, "bad timing arguments");
+  Resolved r;
+  int rc = resolve(desc, r);
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  for (int i = 0; i < warmup; ++i) {
+    rc = launch_resolved(r, A, B, Out, workspace, workspace_bytes, nullptr, 0, s, nullptr);
+    if (rc) return rc;
+  }
+  cudaEvent_t e0, e1;
+  cudaError_t e = cudaEventCreate(&e0);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaEventCreate");
+  e = cudaEventCreate(&e1);
+  if (e != cudaSuccess) { cudaEventDestroy(e0); return cuda_fail(e, "cudaEventCreate"); }
+  cudaEventRecord(e0, s);
+  for (int i = 0; i < iters && rc == 0; ++i)
+    rc = launch_resolved(r, A, B, Out, workspace, workspace_bytes, nullptr, 0, s, nullptr);
+  cudaEventRecord(e1, s);
+  e = cudaEventSynchronize(e1);
+  float ms = 0.f;
+  if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, e0, e1);
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  if (rc) return rc;
+  if (e != cudaSuccess) return cuda_fail(e, "timed launch loop");
+  *avg_ms = ms / static_cast<float>(iters);
+  return wtc_check_device_status(nullptr, stream);
+}
+
+int wtc_matmul_softmax_host(const wtc_chain_desc *desc, const void *hostA, const void *hostB, void *hostOut) {
+  Resolved r;
+  int rc = resolve(desc, r);
+  if (rc) return rc;
+  const wtc_chain_desc &d = r.d;
+  if (d.M == 0 || d.N == 0) return WTC_OK;
+  if (!hostA || !hostB || !hostOut) return fail(WTC_E_ARG, "null host pointer");
+  const size_t in_sz = d.in_dtype == WTC_F16 ? 2 : 4, out_sz = d.out_dtype == WTC_F16 ? 2 : 4;
+  const size_t a_bytes = static_cast<size_t>(d.batch) * d.a_batch_stride * in_sz;
+  const size_t b_bytes = static_cast<size_t>(r.b_batched ? d.batch : 1) * d.K * d.ldb * in_sz;
+  const size_t o_bytes = static_cast<size_t>(d.batch) * d.o_batch_stride * out_sz;
+  const size_t w_bytes = r.plan.workspace_bytes;
+
+  struct Buf { void *p = nullptr; size_t cap = 0; int dev = -1; };
+  thread_local Buf bufs[4];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  const size_t want[4] = {a_bytes, b_bytes, o_bytes, w_bytes};
+  for (int i = 0; i < 4; ++i) {
+    if (bufs[i].dev != dev || bufs[i].cap < want[i]) {
+      if (bufs[i].p && bufs[i].dev == dev) cudaFree(bufs[i].p);
+      bufs[i].p = nullptr; bufs[i].cap = 0; bufs[i].dev = dev;
+      if (want[i]) {
+        e = cudaMalloc(&bufs[i].p, want[i]);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc (host-buffer entry point)");
+        bufs[i].cap = want[i];
+      }
+    }
+  }
+  thread_local cudaStream_t hs = nullptr;
+  thread_local int hs_dev = -1;
+  if (!hs || hs_dev != dev) {
+    e = cudaStreamCreateWithFlags(&hs, cudaStreamNonBlocking);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaStreamCreate");
+    hs_dev = dev;
+  }
+  e = cudaMemcpyAsync(bufs[0].p, hostA, a_bytes, cudaMemcpyHostToDevice, hs);
+  if (e != cudaSuccess) return cuda_fail(e, "copy of A to the device");
+  e = cudaMemcpyAsync(bufs[1].p, hostB, b_bytes, cudaMemcpyHostToDevice, hs);
+  if (e != cudaSuccess) return cuda_fail(e, "copy of B to the device");
+  rc = launch_resolved(r, bufs[0].p, bufs[1].p, bufs[2].p, bufs[3].p, bufs[3].cap, nullptr, 0, hs, nullptr);
+  if (rc) return rc;
+  e = cudaMemcpyAsync(hostOut, bufs[2].p, o_bytes, cudaMemcpyDeviceToHost, hs);
+  if (e != cudaSuccess) return cuda_fail(e, "copy of the result to the host");
+  return wtc_check_device_status(nullptr, hs);
+}
+
+int wtc_debug_set_umma_geometry(uint32_t a_lbo, uint32_t a_sbo, uint32_t a_kstep, uint32_t b_lbo, uint32_t b_sbo,
+                                uint32_t b_kstep) {
+  if (!a_lbo && !a_sbo && !a_kstep && !b_lbo && !b_sbo && !b_kstep) g_geom = kDefaultGeom;
+  else g_geom = wtc::UmmaGeom{a_lbo, a_sbo, a_kstep, b_lbo, b_sbo, b_kstep};
+  return WTC_OK;
+}
+
+} // extern "C"
