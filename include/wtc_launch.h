@@ -160,6 +160,16 @@ int wtc_matmul_softmax_time(const wtc_chain_desc *desc, const void *A, const voi
 int wtc_debug_set_umma_geometry(uint32_t a_lbo, uint32_t a_sbo, uint32_t a_kstep, uint32_t b_lbo,
                                 uint32_t b_sbo, uint32_t b_kstep);
 
+/*
+ * Profiling aid: when set to a device buffer of grid*16 int64, the tensor-core
+ * kernels stamp %globaltimer (ns) for their first tile: [0] set-up done,
+ * [1] accumulator complete, [2] first softmax pass done, [3] row statistics
+ * received, [4] staged for the store, [5] epilogue finished, [6] first TMA load
+ * issued, [7] first stage landed, [8] last MMA of the first tile committed.
+ * NULL (the default) switches the stamps off.
+ */
+int wtc_debug_set_timeline(void *device_buffer);
+
 #ifdef __cplusplus
 }
 #endif

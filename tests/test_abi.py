@@ -1,0 +1,93 @@
+"""The C-ABI library loads without a GPU, exports every symbol the header
+declares, and resolves descriptors to the documented kernel plans.  No compute."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def header_symbols(name):
+    text = open(os.path.join(ROOT, "include", name)).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b((?:wtc|welder)_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_launch_header_symbols_exported(wtc_lib):
+    L = wtc_lib.lib()
+    syms = header_symbols("wtc_launch.h")
+    assert len(syms) >= 10
+    for s in syms:
+        assert hasattr(L, s), f"{s} declared in include/wtc_launch.h but not exported"
+    assert sorted(wtc_lib.launch.EXPORTS) == [s for s in syms if s in wtc_lib.launch.EXPORTS]
+    assert L.wtc_abi_version() == 1
+
+
+def test_struct_layout_matches_header(wtc_lib):
+    # the library checks struct_size; a mismatch between the ctypes mirror and the C struct shows here
+    d = wtc_lib.make_desc(1, 8, 8, 8)
+    wtc_lib.plan_query(d)
+    d.struct_size += 4
+    with pytest.raises(wtc_lib.WtcError) as e:
+        wtc_lib.plan_query(d)
+    assert e.value.code == -1 and "struct_size" in str(e.value)
+
+
+@pytest.mark.parametrize("shape,kernel,cluster,launches", [
+    ((1, 4096, 1024, 1024), "tc_cluster", 4, 1),      # f16 native chain
+    ((64, 2048, 2048, 128), "tc_cluster", 8, 1),      # batched attention scores
+    ((1, 8192, 32000, 4096), "tc_tiled", 1, 2),       # vocab-wide logits: online two-pass
+    ((1, 16, 32000, 4096), "tc_tiled", 1, 2),         # skinny decode
+    ((1, 8192, 128, 64), "tc_cluster", 1, 1),         # the reference's own shape
+])
+def test_plans_for_benchmark_configs(wtc_lib, shape, kernel, cluster, launches):
+    p = wtc_lib.plan_query(wtc_lib.make_desc(*shape))
+    assert wtc_lib.launch.KERNEL_NAMES[p.kernel] == kernel
+    assert (p.cluster_n, p.launches) == (cluster, launches)
+    assert (p.tile_m, p.tile_n, p.tile_k) == (128, 256, 64)
+    assert p.tmem_columns == 512 and p.threads == 320
+    if kernel == "tc_tiled":
+        b, M, N, K = shape
+        assert p.workspace_bytes == b * M * ((N + 255) // 256) * 8
+        assert wtc_lib.workspace_bytes(wtc_lib.make_desc(*shape)) == p.workspace_bytes
+
+
+def test_plan_fallbacks_and_variants(wtc_lib):
+    w = wtc_lib
+    assert w.plan_query(w.make_desc(1, 128, 128, 128, w.F32, w.F32)).kernel == w.KERNEL_SIMT_FUSED
+    assert w.plan_query(w.make_desc(1, 100, 70, 64)).kernel == w.KERNEL_SIMT_FUSED        # N % 8 != 0
+    assert w.plan_query(w.make_desc(1, 100, 72, 60)).kernel == w.KERNEL_SIMT_FUSED        # K % 8 != 0
+    assert w.plan_query(w.make_desc(1, 100, 72, 64, out_dtype=w.F32)).kernel == w.KERNEL_SIMT_FUSED
+    assert w.plan_query(w.make_desc(1, 100, 72, 64, flags=w.FLAG_FORCE_SIMT)).kernel == w.KERNEL_SIMT_FUSED
+    assert w.plan_query(w.make_desc(1, 100, 512, 64, flags=w.FLAG_FORCE_TILED)).kernel == w.KERNEL_TC_TILED
+    p = w.plan_query(w.make_desc(2, 100, 72, 64, variant=w.VARIANT_BASELINE))
+    assert p.kernel == w.KERNEL_SIMT_UNFUSED and p.launches == 5
+    assert p.workspace_bytes == (2 * 200 * 72 + 2 * 200) * 4
+    # tile hints: legal ones pass, others are replaced and flagged
+    assert w.plan_query(w.make_desc(1, 4096, 1024, 1024, tile_m=128, tile_n=256, tile_k=64)).tile_substituted == 0
+    assert w.plan_query(w.make_desc(1, 4096, 1024, 1024, tile_m=64, tile_n=128, tile_k=32)).tile_substituted == 1
+
+
+@pytest.mark.parametrize("kw", [dict(batch=0), dict(M=-1), dict(in_dtype=7), dict(variant=3), dict(tile_m=-2),
+                                dict(lda=3)])
+def test_bad_descriptors_rejected(wtc_lib, kw):
+    args = dict(batch=1, M=16, N=16, K=16)
+    args.update(kw)
+    with pytest.raises(wtc_lib.WtcError) as e:
+        wtc_lib.plan_query(wtc_lib.make_desc(**args))
+    assert e.value.code == -1
+
+
+def test_no_cpu_fallback(wtc_lib):
+    """Without a device a launch must fail loudly, never compute on the host."""
+    import numpy as np
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a device is present")
+    with pytest.raises(wtc_lib.WtcError) as e:
+        wtc_lib.matmul_softmax_host(np.zeros((4, 8), np.float32), np.zeros((8, 8), np.float32))
+    assert e.value.code == -4
+    with pytest.raises(wtc_lib.WtcError):
+        wtc_lib.matmul_softmax(torch.zeros(4, 8), torch.zeros(8, 8))

@@ -1,0 +1,252 @@
+"""Parity of the CUDA path (through the C ABI) against the CPU checker.
+
+Tolerances are the contract's: max |p - p_ref| <= 2e-3, |row sum - 1| <= 1e-3,
+identical row argmax (an argmax may differ only between columns whose checker
+probabilities are within one output ulp of each other)."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def w(wtc_lib, cuda_dev):
+    return wtc_lib
+
+
+def _run(w, dev, A, B, scale, **kw):
+    import torch
+    st = torch.zeros(1, dtype=torch.int32, device=dev)
+    out = w.matmul_softmax(torch.from_numpy(A).to(dev), torch.from_numpy(B).to(dev), scale, status=st, **kw)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0, f"device status {int(st.item())}"
+    return out.cpu().numpy()
+
+
+def _check(out, ref):
+    r = oracle.compare(out.reshape(-1, out.shape[-1]), ref.reshape(-1, ref.shape[-1]))
+    assert r["ok"], r
+    return r
+
+
+# ---------------------------------------------------------------- golden fixtures
+
+def test_golden_known_answers(w, cuda_dev, golden_dir):
+    kat = np.load(os.path.join(golden_dir, "chain_kat.npz"))
+    meta = json.load(open(os.path.join(golden_dir, "chain_kat.json")))
+    for name in meta["cases"]:
+        A, B, P = kat[name + "_A"], kat[name + "_B"], kat[name + "_P"]
+        _check(_run(w, cuda_dev, A, B, 1.0), P)                       # f32 chain, SIMT
+        if "f16" in name:                                             # operands are exact f16 values
+            _check(_run(w, cuda_dev, A.astype(np.float16), B.astype(np.float16), 1.0), P)   # tcgen05
+            _check(_run(w, cuda_dev, A.astype(np.float16), B.astype(np.float16), 1.0, out_dtype=w.F32), P)
+
+
+# ---------------------------------------------------------------- benchmark configurations
+
+def test_cfg1_decomposed_f32(w, cuda_dev):
+    A = oracle.fill((128, 128), "random", 1)
+    B = oracle.fill((128, 128), "random", 1)
+    r = _check(_run(w, cuda_dev, A, B, 1.0), oracle.chain(A, B, 1.0))
+    assert r["max_abs"] < 1e-5
+    assert w.plan_query(w.make_desc(1, 128, 128, 128, w.F32, w.F32)).kernel == w.KERNEL_SIMT_FUSED
+
+
+def test_cfg2_f16_native_full_size(w, cuda_dev):
+    A = oracle.normal((4096, 1024), 21)
+    B = oracle.normal((1024, 1024), 22)
+    out = _run(w, cuda_dev, A, B, 1 / 32)
+    _check(out, oracle.chain(A, B, 1 / 32))
+
+
+def test_cfg3_batched_named_softmax_slice(w, cuda_dev):
+    A = oracle.normal((4, 2048, 128), 31)
+    B = oracle.normal((4, 128, 2048), 32)
+    _check(_run(w, cuda_dev, A, B, 128 ** -0.5), oracle.chain(A, B, 128 ** -0.5))
+
+
+def test_cfg3_full_batch_properties(w, cuda_dev):
+    """All 64 batches: every batch must equal the same batch run alone (no cross-batch
+    leakage), rows sum to one, and a sampled batch matches the checker."""
+    import torch
+    g = torch.Generator(device=cuda_dev); g.manual_seed(5)
+    A = torch.randn((64, 2048, 128), device=cuda_dev, generator=g).half()
+    B = torch.randn((64, 128, 2048), device=cuda_dev, generator=g).half()
+    out = w.matmul_softmax(A, B, 128 ** -0.5)
+    w.check_device_status()
+    sums = out.float().sum(-1)
+    assert float((sums - 1).abs().max()) <= 1e-3
+    for b in (0, 37, 63):
+        alone = w.matmul_softmax(A[b].contiguous(), B[b].contiguous(), 128 ** -0.5)
+        assert torch.equal(alone, out[b])
+    ref = oracle.chain(A[37].cpu().numpy(), B[37].cpu().numpy(), 128 ** -0.5)
+    _check(out[37].cpu().numpy(), ref)
+
+
+def test_cfg4_vocab_wide_sampled_rows(w, cuda_dev):
+    import torch
+    g = torch.Generator(device=cuda_dev); g.manual_seed(7)
+    A = torch.randn((8192, 4096), device=cuda_dev, generator=g).half()
+    B = (torch.randn((4096, 32000), device=cuda_dev, generator=g) * 0.02).half()
+    out = w.matmul_softmax(A, B, 1.0)
+    w.check_device_status()
+    assert w.plan_query(w.make_desc(1, 8192, 32000, 4096)).kernel == w.KERNEL_TC_TILED
+    sums = out.float().sum(-1)
+    assert float((sums - 1).abs().max()) <= 1e-3
+    idx = [0, 1, 127, 128, 129, 4095, 4096, 8191]
+    ref = oracle.chain(A[idx].cpu().numpy(), B.cpu().numpy(), 1.0)
+    _check(out[idx].cpu().numpy(), ref)
+    # the row split is invisible: the first 128 rows alone give the same bits
+    alone = w.matmul_softmax(A[:128].contiguous(), B, 1.0)
+    assert torch.equal(alone, out[:128])
+
+
+def test_cfg5_skinny_decode(w, cuda_dev):
+    A = oracle.normal((16, 4096), 51)
+    B = oracle.normal((4096, 32000), 52, 0.02)
+    _check(_run(w, cuda_dev, A, B, 1.0), oracle.chain(A, B, 1.0))
+
+
+# ---------------------------------------------------------------- shapes and edges
+
+@pytest.mark.parametrize("M,N,K,scale", [
+    (128, 256, 64, 0.125), (128, 256, 16, 0.25), (128, 256, 1024, 1 / 32), (256, 1024, 256, 1 / 16),
+    (200, 520, 72, 0.2), (64, 128, 64, 0.125), (1, 8, 8, 1.0), (129, 2048, 40, 0.1), (777, 264, 136, -0.07),
+    (8192, 128, 64, 1.0),
+])
+def test_tensor_core_cluster_shapes(w, cuda_dev, M, N, K, scale):
+    assert w.plan_query(w.make_desc(1, M, N, K)).kernel == w.KERNEL_TC_CLUSTER
+    A = oracle.normal((M, K), M + N)
+    B = oracle.normal((K, N), K)
+    _check(_run(w, cuda_dev, A, B, scale), oracle.chain(A, B, scale))
+
+
+@pytest.mark.parametrize("M,N,K,flags", [(300, 1024, 256, "tiled"), (256, 4096, 128, 0), (50, 2304, 64, 0),
+                                           (130, 520, 72, "tiled")])
+def test_tiled_two_pass_shapes(w, cuda_dev, M, N, K, flags):
+    fl = w.FLAG_FORCE_TILED if flags == "tiled" else 0
+    d = w.make_desc(1, M, N, K, flags=fl)
+    assert w.plan_query(d).kernel == w.KERNEL_TC_TILED
+    A = oracle.normal((M, K), 3)
+    B = oracle.normal((K, N), 4)
+    _check(_run(w, cuda_dev, A, B, 0.09, flags=fl), oracle.chain(A, B, 0.09))
+
+
+def test_persistent_many_tiles(w, cuda_dev):
+    """More row blocks than resident clusters: accumulator double buffering, barrier
+    phases and the statistics exchange wrap around many times."""
+    for M, N in ((20000, 256), (40000, 512), (9000, 2048)):
+        A = oracle.normal((M, 64), 9)
+        B = oracle.normal((64, N), 10)
+        _check(_run(w, cuda_dev, A, B, 0.125), oracle.chain(A, B, 0.125))
+
+
+def test_batched_shared_and_own_b(w, cuda_dev):
+    A = oracle.normal((3, 300, 128), 1)
+    B = oracle.normal((3, 128, 512), 2)
+    _check(_run(w, cuda_dev, A, B, 0.09), oracle.chain(A, B, 0.09))
+    _check(_run(w, cuda_dev, A, B[0], 0.09), oracle.chain(A, B[0], 0.09))
+
+
+@pytest.mark.parametrize("M,N,K", [(100, 72, 40), (33, 70, 17), (5, 1, 3), (16, 3000, 50)])
+def test_simt_odd_shapes(w, cuda_dev, M, N, K):
+    for dt in (np.float32, np.float16):
+        A = oracle.normal((M, K), 5, 1.0, dt)
+        B = oracle.normal((K, N), 6, 1.0, dt)
+        _check(_run(w, cuda_dev, A, B, 0.3, flags=w.FLAG_FORCE_SIMT), oracle.chain(A, B, 0.3))
+
+
+def test_baseline_variant_matches_fused(w, cuda_dev):
+    A = oracle.normal((257, 96), 7)
+    B = oracle.normal((96, 200), 8)
+    ref = oracle.chain(A, B, 0.2)
+    _check(_run(w, cuda_dev, A, B, 0.2, variant=w.VARIANT_BASELINE), ref)
+    _check(_run(w, cuda_dev, A, B, 0.2, variant=w.VARIANT_BASELINE, out_dtype=w.F32), ref)
+
+
+def test_f16_matmul_result_chain(w, cuda_dev):
+    """The reference's f16-native file spells the matmul with an f16 result; the logits
+    are then f16 values.  Checked against the checker's f16-accumulate mode with the
+    looser bound that mode needs (a different accumulation order in f16)."""
+    A = oracle.normal((256, 64), 11) * np.float16(0.25)
+    B = oracle.normal((64, 128), 12) * np.float16(0.25)
+    out = _run(w, cuda_dev, A, B, 1.0, acc_dtype=w.F16, out_dtype=w.F32)
+    ref16 = oracle.chain(A, B, 1.0, acc=oracle.ACC_F16_SEQ)
+    assert np.abs(out - ref16).max() < 5e-3
+    out_tc = _run(w, cuda_dev, A, B, 1.0, acc_dtype=w.F16)
+    assert np.abs(out_tc.astype(np.float64) - ref16).max() < 5e-3
+
+
+def test_empty_and_degenerate(w, cuda_dev):
+    import torch
+    out = w.matmul_softmax(torch.zeros((0, 8), device=cuda_dev).half(), torch.zeros((8, 16), device=cuda_dev).half())
+    assert out.shape == (0, 16)
+    out = w.matmul_softmax(torch.zeros((4, 0), device=cuda_dev), torch.zeros((0, 5), device=cuda_dev))
+    torch.cuda.synchronize()
+    assert torch.allclose(out, torch.full((4, 5), 0.2, device=cuda_dev))
+    # all-equal logits, and one dominant column
+    A = np.zeros((130, 64), np.float16); B = oracle.normal((64, 256), 1)
+    out = _run(w, cuda_dev, A, B, 1.0)
+    assert np.allclose(out.astype(np.float64), 1 / 256, atol=1e-5)
+    A = np.ones((128, 64), np.float16); B = np.zeros((64, 512), np.float16); B[:, 300] = 1
+    out = _run(w, cuda_dev, A, B, 1.0)
+    assert (out.argmax(1) == 300).all() and np.abs(out[:, 300] - 1).max() < 1e-3
+
+
+def test_host_buffer_entry_point(w, cuda_dev):
+    A = oracle.normal((512, 256), 13)
+    B = oracle.normal((256, 1024), 14)
+    out = w.matmul_softmax_host(A, B, 1 / 16)
+    _check(out, oracle.chain(A, B, 1 / 16))
+    out2 = w.matmul_softmax_host(A, B, 1 / 16)          # cached device buffers
+    assert np.array_equal(out, out2)
+    A32 = oracle.fill((64, 32), "linear"); B32 = oracle.fill((32, 48), "linear")
+    _check(w.matmul_softmax_host(A32, B32, 1.0), oracle.chain(A32, B32, 1.0))
+
+
+def test_n_sharded_partial_and_finish(w, cuda_dev):
+    """Two column shards on one GPU, combined the way two GPUs would combine them:
+    per-row (max, sum) of each shard gathered, then each shard normalised."""
+    import torch
+    A = oracle.normal((300, 128), 15)
+    B = oracle.normal((128, 1536), 16)
+    ref = oracle.chain(A, B, 0.11)
+    tA = torch.from_numpy(A).to(cuda_dev)
+    splits = [(0, 768), (768, 1536)]
+    outs, wss, stats, descs = [], [], [], []
+    for c0, c1 in splits:
+        tB = torch.from_numpy(np.ascontiguousarray(B[:, c0:c1])).to(cuda_dev)
+        o = torch.empty((300, c1 - c0), device=cuda_dev, dtype=torch.float16)
+        d0 = w.make_desc(1, 300, c1 - c0, 128)
+        ws = torch.empty(max(16, w.workspace_bytes(d0)), device=cuda_dev, dtype=torch.uint8)
+        rs = torch.empty((300, 2), device=cuda_dev, dtype=torch.float32)
+        descs.append(w.matmul_softmax_partial(tA, tB, 0.11, o, ws, rs))
+        outs.append(o); wss.append(ws); stats.append(rs)
+    allst = torch.stack(stats).contiguous()
+    for i in range(2):
+        w.matmul_softmax_finish(descs[i], outs[i], wss[i], allst, 2)
+    w.check_device_status()
+    full = torch.cat(outs, dim=1).cpu().numpy()
+    _check(full, ref)
+
+
+def test_linearity_and_shift_properties(w, cuda_dev):
+    """Size-independent properties at the full f16 size: scaling the logits by 0 gives
+    the uniform row; permuting B's columns permutes the probabilities."""
+    import torch
+    g = torch.Generator(device=cuda_dev); g.manual_seed(3)
+    A = torch.randn((4096, 1024), device=cuda_dev, generator=g).half()
+    B = torch.randn((1024, 1024), device=cuda_dev, generator=g).half()
+    uni = w.matmul_softmax(A, B, 0.0)
+    assert torch.allclose(uni.float(), torch.full_like(uni, 1 / 1024).float(), atol=1e-6)
+    p = w.matmul_softmax(A, B, 1 / 32)
+    perm = torch.randperm(1024, device=cuda_dev, generator=g)
+    pp = w.matmul_softmax(A, B[:, perm].contiguous(), 1 / 32)
+    w.check_device_status()
+    assert float((pp.float() - p[:, perm].float()).abs().max()) <= 2e-3
+    assert float((p.float().sum(-1) - 1).abs().max()) <= 1e-3

@@ -3,18 +3,27 @@
 //
 //   CLUSTER = true   a thread-block cluster of ceil(N/BN) CTAs owns 128 complete
 //                    rows.  Each CTA contracts its 128 x BN slice, reduces its
-//                    local row (max, sum), swaps the pair with its peers through
-//                    distributed shared memory and writes normalised f16.
+//                    local row (max, sum), sends the pair to its peers' shared
+//                    memory (st.async + mbarrier transaction bytes: no fences, no
+//                    cluster-wide barrier) and writes normalised f16.
 //   CLUSTER = false  independent 128 x BN tiles.  Each writes exp(v - tile max)
 //                    as f16 and the per-tile (max, sum); a second, bandwidth-bound
 //                    kernel (row_softmax_kernels.cu) rescales the rows.  Used when
 //                    a row does not fit one cluster, and for skinny M.
 //
-// Warp roles (192 threads): warp 0 feeds shared memory with TMA, warp 1 owns TMEM
-// and issues tcgen05.mma, warps 2..5 are the softmax epilogue (one thread per row,
-// TMEM lane quarter = warp_id % 4).  Two accumulator buffers in TMEM let the
-// epilogue of tile i run under the contraction of tile i+1.  The logits never
-// leave the SM: TMEM -> registers -> (TMEM) -> swizzled shared -> TMA store.
+// Warp roles (320 threads): warp 0 feeds shared memory with TMA, warp 1 owns TMEM
+// and issues tcgen05.mma, warps 2..9 are the softmax epilogue: thread = one row x
+// half of the tile's columns (TMEM lane quarter = warp_id % 4, column half =
+// (warp_id - 2) / 4).  Two accumulator buffers in TMEM let the epilogue of tile i
+// run under the contraction of tile i+1.  The logits never leave the SM:
+// TMEM -> registers -> swizzled shared -> TMA store.
+//
+// Epilogue, per thread: its 128 accumulator values go TMEM -> registers in one go
+// and the accumulator buffer is released at once; row extreme, e = 2^(v - max) in
+// place (one MUFU per element), the row's (max, sum) exchange -- between the two
+// column halves through shared memory, between the CTAs of the cluster through
+// st.async -- then p = e * factor, packed to f16, staged 64 columns at a time in
+// 128-byte-swizzled shared memory and written with TMA stores.
 //
 // Operand layouts: A [M,K] is K-major, staged as 128 rows x 128 B with the 128-byte
 // swizzle.  B [K,N] has N contiguous, i.e. it is MN-major for the MMA: it is staged
@@ -29,8 +38,9 @@ namespace {
 
 constexpr int BM = kTcBlockM;
 constexpr int BK = kTcBlockK;
-constexpr int kThreads = 192;
-constexpr int kEpiThreads = 128;
+constexpr int kEpiWarps = 8;
+constexpr int kEpiThreads = kEpiWarps * 32;
+constexpr int kThreads = 64 + kEpiThreads;
 constexpr int kMaxCluster = 8;
 
 template <int BN, int STAGES, bool CLUSTER>
@@ -38,26 +48,31 @@ struct SmemLayout {
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BK * BN * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kOutWarpBytes = 2 * 32 * 128;            // two 32-row x 64-col f16 buffers
-  static constexpr int kOutBytes = 4 * kOutWarpBytes;
+  static constexpr int kHalfCols = BN / 2;                            // columns per epilogue thread
+  static constexpr int kOutWarpBytes = 32 * 64 * 2;                   // one 32-row x 64-column f16 staging tile
+  static constexpr int kOutBytes = kEpiWarps * kOutWarpBytes;
+  static constexpr int kPairBytes = 2 * BM * 8;                       // [half][row] float2
   static constexpr int kStatsBytes = CLUSTER ? 2 * kMaxCluster * BM * 8 : 0;
   static constexpr int kOffOut = STAGES * kStageBytes;
-  static constexpr int kOffStats = kOffOut + kOutBytes;
+  static constexpr int kOffPair = kOffOut + kOutBytes;
+  static constexpr int kOffStats = kOffPair + kPairBytes;
   static constexpr int kOffBars = kOffStats + kStatsBytes;
   static constexpr int kNumBars = 2 * STAGES + 4 + 2;
   static constexpr int kOffTmemSlot = kOffBars + kNumBars * 8;
   static constexpr int kTotal = kOffTmemSlot + 16;
-  static constexpr int kDynamic = kTotal + 1024;                 // slack to align the base to 1024 B
+  static constexpr int kDynamic = kTotal;
+  static_assert(kDynamic <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
 };
 
 __device__ __forceinline__ void record_failure(int *status, int code) {
   if (status) atomicCAS(status, 0, code);
 }
 
-// Writes one thread's 32 consecutive f16 columns (64 B) into its row of the
-// 128-byte-swizzled staging tile.  `half` selects the left or right 64 B of the row.
-__device__ __forceinline__ void stage_row_chunk(uint8_t *buf, int lane, int half, const uint32_t (&h)[16]) {
-  uint8_t *row = buf + lane * 128;
+// Writes one thread's 32 consecutive f16 columns (64 B) into its row of a
+// 128-byte-swizzled 32-row x 64-column staging tile.  `half` selects the left or
+// right 64 B of the row.
+__device__ __forceinline__ void stage_row_chunk(uint8_t *tile, int lane, int half, const uint32_t (&h)[16]) {
+  uint8_t *row = tile + lane * 128;
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const int phys = ((half * 4 + j) ^ (lane & 7)) * 16;
@@ -65,13 +80,22 @@ __device__ __forceinline__ void stage_row_chunk(uint8_t *buf, int lane, int half
   }
 }
 
+__device__ __forceinline__ void stamp(long long *timeline, int slot) {
+  if (timeline) timeline[static_cast<size_t>(blockIdx.x) * 16 + slot] = static_cast<long long>(globaltimer_ns());
+}
+
 template <int BN, int STAGES, bool CLUSTER>
 __global__ void __launch_bounds__(kThreads, 1)
 fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmO, const TcParams p) {
   using L = SmemLayout<BN, STAGES, CLUSTER>;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int HC = L::kHalfCols;      // columns per epilogue thread
+  constexpr int NCH = HC / 32;          // 32-column chunks per epilogue thread
+  // The 128-byte swizzle needs the stage buffers on 1024-byte boundaries.  There is no
+  // static shared memory in this kernel, so the dynamic window starts aligned; if it ever
+  // does not, every thread leaves before any barrier or TMEM state exists.
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if ((smem_u32(smem) & 1023u) != 0) { record_failure(p.status, WTC_DEV_BAD_SMEM_ALIGN); return; }
 
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + L::kOffBars);
   uint64_t *full = bars;
@@ -80,6 +104,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   uint64_t *accum_empty = bars + 2 * STAGES + 2;
   uint64_t *stats_bar = bars + 2 * STAGES + 4;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + L::kOffTmemSlot);
+  float2 *pair = reinterpret_cast<float2 *>(smem + L::kOffPair);    // [2][BM]
   float2 *stats = reinterpret_cast<float2 *>(smem + L::kOffStats);  // [2][kMaxCluster][BM]
 
   const int warp = threadIdx.x >> 5;
@@ -92,7 +117,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     for (int i = 0; i < 2; ++i) {
       mbar_init(&accum_full[i], 1);
       mbar_init(&accum_empty[i], kEpiThreads);
-      mbar_init(&stats_bar[i], cluster_n * kEpiThreads);
+      mbar_init(&stats_bar[i], 1);
     }
     mbar_fence_init();
     tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); tma_prefetch_desc(&tmO);
@@ -102,7 +127,13 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  if (CLUSTER) cluster_sync_all();   // every peer's barriers exist before anyone touches them
+  if (CLUSTER) cluster_sync_all();   // every peer's barriers exist before anyone signals them
+  // Programmatic dependent launch: everything above overlapped the tail of the previous
+  // kernel on the stream; from here on global memory is touched, so wait for that kernel
+  // to finish, and let the next one start its own set-up as our CTAs retire.
+  grid_dependency_wait();
+  grid_launch_dependents();
+  if (threadIdx.x == 64) stamp(p.timeline, 0);
 
   // ---- work distribution --------------------------------------------------
   int first, stride;
@@ -143,6 +174,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
           for (int j = 0; j < BN / 64; ++j)
             tma_load_3d(sb + j * (BK * 128), &tmB, &full[s], nb * BN + j * 64, kb * BK, p.b_batched ? b : 0);
+          if (n == 0) stamp(p.timeline, 6);
         }
         __syncwarp();
       }
@@ -164,6 +196,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         if (!mbar_wait(&full[s], ph)) { record_failure(p.status, WTC_DEV_TIMEOUT_FULL); ok = false; break; }
         tc_fence_after_sync();
         if (lane == 0) {
+          if (n == 0) stamp(p.timeline, 7);
           const uint32_t sa = smem_u32(smem + s * L::kStageBytes);
           const uint32_t sb = sa + L::kABytes;
 #pragma unroll
@@ -176,134 +209,190 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
         __syncwarp();
       }
-      if (ok && lane == 0) umma_commit(&accum_full[ab]);
+      if (ok && lane == 0) { umma_commit(&accum_full[ab]); if (it == 0) stamp(p.timeline, 8); }
       __syncwarp();
     }
   } else {
     // ======================= softmax epilogue ==============================
-    const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    const int q = warp & 3;                      // TMEM lane quarter this warp may read
+    const int half = (warp - 2) >> 2;            // which half of the tile's columns
     const int row_in_tile = q * 32 + lane;
-    uint8_t *stg = smem + L::kOffOut + (warp - 2) * L::kOutWarpBytes;
+    const bool lead = threadIdx.x == 64;         // first epilogue thread: posts expect_tx, stamps
+    uint8_t *stg = smem + L::kOffOut + (warp - 2) * L::kOutWarpBytes;   // one 32-row x 64-col f16 tile
+    float2 *mine = &pair[half * BM + row_in_tile];
+    const float2 *other = &pair[(half ^ 1) * BM + row_in_tile];
     const float c2 = p.c2;
+    const bool pos = c2 >= 0.f;
     int it = 0;
-    uint32_t groups = 0;                    // staging tiles handed to TMA so far (per warp)
     for (int w = first; w < p.num_items; w += stride, ++it) {
       int b, rb, nb; decode(w, b, rb, nb);
       const int ab = it & 1;
-      if (!mbar_wait(&accum_full[ab], (it >> 1) & 1)) { record_failure(p.status, WTC_DEV_TIMEOUT_ACCUM); break; }
+      const int par = it & 1;
+      const uint32_t tile_phase = (it >> 1) & 1;
+      if (CLUSTER && lead) mbar_expect_tx(&stats_bar[par], cluster_n * BM * 8);
+      if (!mbar_wait(&accum_full[ab], tile_phase)) { record_failure(p.status, WTC_DEV_TIMEOUT_ACCUM); break; }
       tc_fence_after_sync();
-      const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ab * BN;
-      const int col0 = nb * BN;
-      const int valid = min(BN, p.N - col0);          // columns of this tile inside the matrix
-      const int chunks = (valid + 31) >> 5;
-      const int row0 = rb * BM + q * 32;              // first row of this warp
+      if (lead && it == 0) stamp(p.timeline, 1);
+      const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ab * BN + half * HC;
+      const int col0 = nb * BN + half * HC;               // first matrix column of this thread
+      const int valid = max(0, min(HC, p.N - col0));      // my columns that exist
+      const int row0 = rb * BM + q * 32;                  // first row of this warp
       const bool rows_live = row0 < p.M;
 
-      // Stages one 32-column chunk of this warp's 32 rows; every second chunk (or
-      // the last one) hands the 32 x 64 staging tile to TMA.  Two tiles alternate:
-      // group g uses tile g & 1, and every group commits (possibly empty), so
-      // "at most one group still reading" means tile g & 1 is free again.
-      auto stage_and_store = [&](int c, int nchunks, const uint32_t (&h)[16]) {
-        const int buf = groups & 1;
-        if ((c & 1) == 0) {
-          if (lane == 0) tma_store_wait_read1();
-          __syncwarp();
+      // ---- the thread's whole share of the accumulator row goes to registers at once,
+      //      and the accumulator buffer is handed back to the MMA warp straight away ----
+      uint32_t r[NCH][32];
+#pragma unroll
+      for (int c = 0; c < NCH; ++c)
+        if (c * 32 < valid) tmem_ld_32x32b_x32(tbase + c * 32, r[c]);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      mbar_arrive(&accum_empty[ab]);
+      if (p.round_logits_f16) {
+#pragma unroll
+        for (int c = 0; c < NCH; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[c][i] = __float_as_uint(__half2float(__float2half_rn(__uint_as_float(r[c][i]))));
+      }
+
+      // ---- extreme of the raw accumulators (max if scale >= 0, else min), four chains ----
+      float m_half;
+      if (valid == HC) {
+        float m0 = __uint_as_float(r[0][0]), m1 = __uint_as_float(r[0][1]);
+        float m2 = __uint_as_float(r[0][2]), m3 = __uint_as_float(r[0][3]);
+        if (pos) {
+#pragma unroll
+          for (int c = 0; c < NCH; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              m0 = fmaxf(m0, __uint_as_float(r[c][i]));     m1 = fmaxf(m1, __uint_as_float(r[c][i + 1]));
+              m2 = fmaxf(m2, __uint_as_float(r[c][i + 2])); m3 = fmaxf(m3, __uint_as_float(r[c][i + 3]));
+            }
+          m_half = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+        } else {
+#pragma unroll
+          for (int c = 0; c < NCH; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              m0 = fminf(m0, __uint_as_float(r[c][i]));     m1 = fminf(m1, __uint_as_float(r[c][i + 1]));
+              m2 = fminf(m2, __uint_as_float(r[c][i + 2])); m3 = fminf(m3, __uint_as_float(r[c][i + 3]));
+            }
+          m_half = fminf(fminf(m0, m1), fminf(m2, m3));
         }
-        stage_row_chunk(stg + buf * 4096, lane, c & 1, h);
-        if ((c & 1) == 1 || c == nchunks - 1) {
+        m_half *= c2;
+      } else if (valid > 0) {
+        float m = __uint_as_float(r[0][0]);
+#pragma unroll
+        for (int c = 0; c < NCH; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i < valid) m = pos ? fmaxf(m, __uint_as_float(r[c][i])) : fminf(m, __uint_as_float(r[c][i]));
+        m_half = m * c2;
+      } else {
+        m_half = -INFINITY;
+      }
+
+      // ---- e = 2^(v - m_half) in place, row sum ----
+      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+      if (valid == HC) {
+#pragma unroll
+        for (int c = 0; c < NCH; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const float e0 = ex2_approx(fmaf(__uint_as_float(r[c][i]), c2, -m_half));
+            const float e1 = ex2_approx(fmaf(__uint_as_float(r[c][i + 1]), c2, -m_half));
+            const float e2 = ex2_approx(fmaf(__uint_as_float(r[c][i + 2]), c2, -m_half));
+            const float e3 = ex2_approx(fmaf(__uint_as_float(r[c][i + 3]), c2, -m_half));
+            s0 += e0; s1 += e1; s2 += e2; s3 += e3;
+            r[c][i] = __float_as_uint(e0); r[c][i + 1] = __float_as_uint(e1);
+            r[c][i + 2] = __float_as_uint(e2); r[c][i + 3] = __float_as_uint(e3);
+          }
+      } else {
+#pragma unroll
+        for (int c = 0; c < NCH; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float e = 0.f;
+            if (c * 32 + i < valid) e = ex2_approx(fmaf(__uint_as_float(r[c][i]), c2, -m_half));
+            s0 += e;
+            r[c][i] = __float_as_uint(e);
+          }
+      }
+      float sum = (s0 + s1) + (s2 + s3);
+      if (lead && it == 0) stamp(p.timeline, 2);
+
+      // ---- the two halves of a row meet through shared memory ----
+      *mine = make_float2(m_half, sum);
+      named_bar_sync(1 + q, 64);
+      const float2 o = *other;
+      named_bar_sync(1 + q, 64);                   // both have read: the slots may be reused
+      const float lm = fmaxf(m_half, o.x);         // tile-row max (log2 domain)
+      float f;                                     // what my e values still have to be multiplied by
+      if (CLUSTER) {
+        const float ll = (m_half == -INFINITY ? 0.f : sum * ex2_approx(m_half - lm)) +
+                         (o.x == -INFINITY ? 0.f : o.y * ex2_approx(o.x - lm));
+        // ... and the CTAs of the cluster through each other's shared memory
+        if (half == 0) {
+          const uint32_t slot = smem_u32(&stats[(par * kMaxCluster + cta_rank) * BM + row_in_tile]);
+          const uint32_t bar = smem_u32(&stats_bar[par]);
+          for (uint32_t peer = 0; peer < cluster_n; ++peer)
+            st_async_f32x2(map_to_cta(slot, peer), lm, ll, map_to_cta(bar, peer));
+        }
+        if (!mbar_wait_cluster(&stats_bar[par], tile_phase)) { record_failure(p.status, WTC_DEV_TIMEOUT_STATS); break; }
+        if (lead && it == 0) stamp(p.timeline, 3);
+        float gm = -INFINITY;
+        for (uint32_t peer = 0; peer < cluster_n; ++peer)
+          gm = fmaxf(gm, stats[(par * kMaxCluster + peer) * BM + row_in_tile].x);
+        float gl = 0.f;
+        for (uint32_t peer = 0; peer < cluster_n; ++peer) {
+          const float2 st = stats[(par * kMaxCluster + peer) * BM + row_in_tile];
+          gl += st.y * ex2_approx(st.x - gm);
+        }
+        f = ex2_approx(m_half - gm) / gl;
+      } else {
+        f = ex2_approx(m_half - lm);               // tiled: values relative to the tile max, not normalised
+      }
+
+      // ---- p = e * f -> f16 -> swizzled staging -> TMA store, 64 columns at a time ----
+      float sum_r = 0.f;                           // tiled: sum of what is actually stored
+#pragma unroll
+      for (int g = 0; g < NCH / 2; ++g) {
+        if (g * 64 < valid) {
+          if (lane == 0) tma_store_wait_read();    // the previous store has read the staging tile
+          __syncwarp();
+#pragma unroll
+          for (int hc = 0; hc < 2; ++hc) {
+            const int c = g * 2 + hc;
+            uint32_t h[16];
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const __half2 hh = __floats2half2_rn(__uint_as_float(r[c][i]) * f, __uint_as_float(r[c][i + 1]) * f);
+              if (!CLUSTER) { const float2 back = __half22float2(hh); sum_r += back.x + back.y; }
+              h[i >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
+            }
+            stage_row_chunk(stg, lane, hc, h);
+          }
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            if (rows_live) tma_store_3d(&tmO, stg + buf * 4096, col0 + (c >> 1) * 64, row0, b);
+            if (rows_live) tma_store_3d(&tmO, stg, col0 + g * 64, row0, b);
             tma_store_commit();
           }
-          ++groups;
-        }
-      };
-
-      uint32_t r[32];
-      // ---- pass 1: row maximum of v = s * c2 (log2 domain) ----
-      float mx = -INFINITY;
-      for (int c = 0; c < chunks; ++c) {
-        tmem_ld_32x32b_x32(tbase + c * 32, r);
-        tmem_ld_wait();
-        const int lim = valid - c * 32;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float s = __uint_as_float(r[i]);
-          if (p.round_logits_f16) s = __half2float(__float2half_rn(s));
-          const float v = s * c2;
-          if (i < lim) mx = fmaxf(mx, v);
-        }
-      }
-      // ---- pass 2: e = 2^(v - mx), row sum ----
-      float sum = 0.f;
-      for (int c = 0; c < chunks; ++c) {
-        tmem_ld_32x32b_x32(tbase + c * 32, r);
-        tmem_ld_wait();
-        const int lim = valid - c * 32;
-        uint32_t h[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float s0 = __uint_as_float(r[i]), s1 = __uint_as_float(r[i + 1]);
-          if (p.round_logits_f16) { s0 = __half2float(__float2half_rn(s0)); s1 = __half2float(__float2half_rn(s1)); }
-          float e0 = ex2_approx(fmaf(s0, c2, -mx));
-          float e1 = ex2_approx(fmaf(s1, c2, -mx));
-          if (i >= lim) e0 = 0.f;
-          if (i + 1 >= lim) e1 = 0.f;
-          sum += e0 + e1;
-          if (CLUSTER) { r[i] = __float_as_uint(e0); r[i + 1] = __float_as_uint(e1); }
-          else h[i >> 1] = pack_f16x2(e0, e1);
-        }
-        if (CLUSTER) {
-          tmem_st_32x32b_x32(tbase + c * 32, r);   // park e in place of the logits
-        } else {
-          stage_and_store(c, chunks, h);
         }
       }
       if (!CLUSTER) {
-        tc_fence_before_sync();
-        mbar_arrive(&accum_empty[ab]);
+        // tile statistics: max of the tile row, sum of the stored values of both halves
+        mine->y = sum_r;
+        named_bar_sync(1 + q, 64);
         const int row = rb * BM + row_in_tile;
-        if (row < p.M)
-          p.tile_stats[(static_cast<int64_t>(b) * p.M + row) * p.num_nb + nb] = make_float2(mx, sum);
-        continue;
+        if (half == 0 && row < p.M)
+          p.tile_stats[(static_cast<int64_t>(b) * p.M + row) * p.num_nb + nb] = make_float2(lm, sum_r + other->y);
+        named_bar_sync(1 + q, 64);
       }
-
-      // ---- cluster: swap (max, sum) with the peers that hold the rest of the row ----
-      tmem_st_wait();
-      const int sbuf = it & 1;
-      {
-        const uint32_t slot = smem_u32(&stats[(sbuf * kMaxCluster + cta_rank) * BM + row_in_tile]);
-        const uint32_t bar = smem_u32(&stats_bar[sbuf]);
-        for (uint32_t peer = 0; peer < cluster_n; ++peer) st_cluster_f32x2(map_to_cta(slot, peer), mx, sum);
-        for (uint32_t peer = 0; peer < cluster_n; ++peer) mbar_arrive_remote_release(map_to_cta(bar, peer));
-      }
-      if (!mbar_wait_cluster(&stats_bar[sbuf], (it >> 1) & 1)) { record_failure(p.status, WTC_DEV_TIMEOUT_STATS); break; }
-      float gm = mx;
-      for (uint32_t peer = 0; peer < cluster_n; ++peer)
-        gm = fmaxf(gm, stats[(sbuf * kMaxCluster + peer) * BM + row_in_tile].x);
-      float gl = 0.f;
-      for (uint32_t peer = 0; peer < cluster_n; ++peer) {
-        const float2 st = stats[(sbuf * kMaxCluster + peer) * BM + row_in_tile];
-        gl += st.y * ex2_approx(st.x - gm);
-      }
-      const float f = ex2_approx(mx - gm) / gl;
-
-      // ---- pass 3: p = e * f -> f16 -> swizzled staging -> TMA store ----
-      for (int c = 0; c < chunks; ++c) {
-        tmem_ld_32x32b_x32(tbase + c * 32, r);
-        tmem_ld_wait();
-        uint32_t h[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2)
-          h[i >> 1] = pack_f16x2(__uint_as_float(r[i]) * f, __uint_as_float(r[i + 1]) * f);
-        stage_and_store(c, chunks, h);
-      }
-      tc_fence_before_sync();
-      mbar_arrive(&accum_empty[ab]);
+      if (lead && it == 0) stamp(p.timeline, 4);
     }
     if (lane == 0) tma_store_wait_all();
+    if (lead) stamp(p.timeline, 5);
   }
 
   // ---- teardown: nothing in flight, peers done with our shared memory, TMEM freed ----
@@ -322,33 +411,49 @@ cudaError_t launch_impl(const CUtensorMap &tmA, const CUtensorMap &tmB, const CU
                         int cluster_n, int num_sms, cudaStream_t s, TcLaunchInfo *info) {
   using L = SmemLayout<BN, STAGES, CLUSTER>;
   auto kern = fused_tc_kernel<BN, STAGES, CLUSTER>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
-  if (e != cudaSuccess) return e;
+  static bool attr_set = false;   // per template instance
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
 
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = L::kDynamic;
   cfg.stream = s;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
+  int nattr = 0;
+  if (p.use_pdl) {
+    attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[nattr].val.programmaticStreamSerializationAllowed = 1;
+    ++nattr;
+  }
   int grid;
   if (CLUSTER) {
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = cluster_n;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
+    attr[nattr].id = cudaLaunchAttributeClusterDimension;
+    attr[nattr].val.clusterDim.x = cluster_n;
+    attr[nattr].val.clusterDim.y = 1;
+    attr[nattr].val.clusterDim.z = 1;
+    ++nattr;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cfg.gridDim = dim3(cluster_n, 1, 1);
-    int max_clusters = 0;
-    e = cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg);
-    if (e != cudaSuccess) return e;
-    if (max_clusters < 1) return cudaErrorInvalidConfiguration;
+    cfg.numAttrs = nattr;
+    static int max_clusters_cache[kMaxCluster + 1] = {0};
+    if (!max_clusters_cache[cluster_n]) {
+      cfg.gridDim = dim3(cluster_n, 1, 1);
+      int mc = 0;
+      cudaError_t e = cudaOccupancyMaxActiveClusters(&mc, kern, &cfg);
+      if (e != cudaSuccess) return e;
+      if (mc < 1) return cudaErrorInvalidConfiguration;
+      max_clusters_cache[cluster_n] = mc;
+    }
+    const int max_clusters = max_clusters_cache[cluster_n];
     const int clusters = p.num_items < max_clusters ? p.num_items : max_clusters;
     grid = clusters * cluster_n;
   } else {
     grid = p.num_items < num_sms ? p.num_items : num_sms;
-    cfg.attrs = nullptr;
-    cfg.numAttrs = 0;
+    cfg.attrs = nattr ? attr : nullptr;
+    cfg.numAttrs = nattr;
   }
   cfg.gridDim = dim3(grid, 1, 1);
   if (info) { info->grid = grid; info->cluster = CLUSTER ? cluster_n : 1; info->smem_bytes = L::kDynamic; info->threads = kThreads; }

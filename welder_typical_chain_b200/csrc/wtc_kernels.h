@@ -23,10 +23,12 @@ struct TcParams {
   int num_items;   // work items: cluster mode batch*num_rb, tiled mode batch*num_rb*num_nb
   int b_batched;   // B has its own batch dimension
   int group_rb;    // tiled mode: row blocks per rasterisation group
+  int use_pdl;     // launch with programmatic stream serialisation
   int round_logits_f16;  // chain spelled with an f16 matmul result: round s to f16 before the softmax
   float c2;        // scale * log2(e)
   float2 *tile_stats;    // tiled mode: [batch*M][num_nb] (max in log2 domain, sum of 2^(v-max))
   int *status;     // device status word (0 = ok)
+  long long *timeline;   // optional [grid][16] nanosecond stamps of the first tile (bring-up / profiling)
   UmmaGeom geom;
 };
 

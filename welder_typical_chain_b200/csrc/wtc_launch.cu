@@ -11,6 +11,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -40,6 +41,8 @@ int cuda_fail(cudaError_t e, const char *what) {
 //   (leading), 8-k-row groups are 1024 B apart (stride); one 16-deep K step is 16 * 128 B.
 constexpr wtc::UmmaGeom kDefaultGeom = {16, 1024, 32, 8192, 1024, 2048};
 wtc::UmmaGeom g_geom = kDefaultGeom;
+long long *g_timeline = nullptr;
+const int g_use_pdl = [] { const char *e = getenv("WTC_NO_PDL"); return (e && e[0] == '1') ? 0 : 1; }();
 
 struct Resolved {
   wtc_chain_desc d;  // strides filled in
@@ -98,7 +101,7 @@ int resolve(const wtc_chain_desc *in, Resolved &r) {
     p.tile_m = 8; p.tile_n = static_cast<int32_t>(d.N); p.tile_k = 64;
   } else if (r.tc_ok) {
     p.tile_m = wtc::kTcBlockM; p.tile_n = wtc::kTcBlockN; p.tile_k = wtc::kTcBlockK;
-    p.threads = 192;
+    p.threads = 320;
     p.tmem_columns = 2 * wtc::kTcBlockN;
     if (r.num_nb <= 8 && !(d.flags & WTC_FLAG_FORCE_TILED)) {
       p.kernel = WTC_KERNEL_TC_CLUSTER;
@@ -258,6 +261,8 @@ int launch_resolved(Resolved &r, const void *A, const void *B, void *Out, void *
     p.c2 = d.scale * 1.4426950408889634f;
     p.status = status ? status : default_status();
     p.geom = g_geom;
+    p.timeline = g_timeline;
+    p.use_pdl = g_use_pdl;
     wtc::TcLaunchInfo info;
     cudaError_t e;
     if (!tiled) {
@@ -365,8 +370,9 @@ int wtc_check_device_status(const int *device_status, void *stream) {
   if (v != 0) {
     static const char *names[] = {"ok", "a TMA stage never landed", "a pipeline stage was never released",
                                   "an accumulator never completed", "an accumulator buffer was never drained",
-                                  "cluster peers never sent their row statistics"};
-    return fail(WTC_E_DEVICE, "device status %d: %s", v, (v > 0 && v < 6) ? names[v] : "unknown");
+                                  "cluster peers never sent their row statistics",
+                                  "dynamic shared memory was not 1024-byte aligned"};
+    return fail(WTC_E_DEVICE, "device status %d: %s", v, (v > 0 && v < 7) ? names[v] : "unknown");
   }
   return WTC_OK;
 }
@@ -454,6 +460,11 @@ int wtc_debug_set_umma_geometry(uint32_t a_lbo, uint32_t a_sbo, uint32_t a_kstep
                                 uint32_t b_kstep) {
   if (!a_lbo && !a_sbo && !a_kstep && !b_lbo && !b_sbo && !b_kstep) g_geom = kDefaultGeom;
   else g_geom = wtc::UmmaGeom{a_lbo, a_sbo, a_kstep, b_lbo, b_sbo, b_kstep};
+  return WTC_OK;
+}
+
+int wtc_debug_set_timeline(void *device_buffer) {
+  g_timeline = static_cast<long long *>(device_buffer);
   return WTC_OK;
 }
 

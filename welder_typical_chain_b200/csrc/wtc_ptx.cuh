@@ -20,6 +20,7 @@ enum : int {
   WTC_DEV_TIMEOUT_ACCUM = 3,   // epilogue waited for an accumulator that never completed
   WTC_DEV_TIMEOUT_TMEM = 4,    // MMA waited for an accumulator buffer the epilogue never drained
   WTC_DEV_TIMEOUT_STATS = 5,   // epilogue waited for row statistics a cluster peer never sent
+  WTC_DEV_BAD_SMEM_ALIGN = 6,  // dynamic shared memory did not start on a 1024-byte boundary
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -101,6 +102,12 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local_smem_addr, uint32_
 __device__ __forceinline__ void st_cluster_f32x2(uint32_t cluster_addr, float a, float b) {
   asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(cluster_addr), "f"(a), "f"(b) : "memory");
 }
+// Asynchronous 8-byte store into a peer CTA's shared memory; the write is counted as
+// 8 transaction bytes on the mbarrier `cluster_bar` (which must live in the same peer).
+__device__ __forceinline__ void st_async_f32x2(uint32_t cluster_addr, float a, float b, uint32_t cluster_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v2.f32 [%0], {%1, %2}, [%3];"
+               ::"r"(cluster_addr), "f"(a), "f"(b), "r"(cluster_bar) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive_remote_release(uint32_t cluster_bar_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar_addr) : "memory");
 }
@@ -126,6 +133,13 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t *bar, uint32_t parity
     }
   }
 }
+
+// ---- programmatic dependent launch ---------------------------------------------
+// Blocks until the kernel this one was serialised behind has completed and its
+// writes are visible (returns at once when there is no such dependency).
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Allows the next kernel on the stream, if it opted in, to start launching.
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ---- fences -----------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() {

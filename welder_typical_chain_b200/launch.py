@@ -23,7 +23,7 @@ EXPORTS = [
     "wtc_abi_version", "wtc_last_error", "wtc_plan_query", "wtc_matmul_softmax_workspace_bytes",
     "wtc_matmul_softmax_launch", "wtc_matmul_softmax_partial_launch", "wtc_matmul_softmax_finish_launch",
     "wtc_matmul_softmax_host", "wtc_check_device_status", "wtc_matmul_softmax_time",
-    "wtc_debug_set_umma_geometry",
+    "wtc_debug_set_umma_geometry", "wtc_debug_set_timeline",
 ]
 
 
@@ -81,6 +81,7 @@ def lib() -> C.CDLL:
         L.wtc_check_device_status.argtypes = [vp, vp]
         L.wtc_matmul_softmax_time.argtypes = [dp, vp, vp, vp, vp, sz, vp, C.c_int, C.c_int, C.POINTER(C.c_float)]
         L.wtc_debug_set_umma_geometry.argtypes = [C.c_uint32] * 6
+        L.wtc_debug_set_timeline.argtypes = [vp]
         _LIB = L
     return _LIB
 
@@ -122,6 +123,11 @@ def workspace_bytes(desc: ChainDesc) -> int:
 
 def set_umma_geometry(a_lbo=0, a_sbo=0, a_kstep=0, b_lbo=0, b_sbo=0, b_kstep=0) -> None:
     _check(lib().wtc_debug_set_umma_geometry(a_lbo, a_sbo, a_kstep, b_lbo, b_sbo, b_kstep))
+
+
+def set_timeline(buf=None) -> None:
+    """buf: a CUDA int64 tensor of at least grid*16 elements, or None to switch the stamps off."""
+    _check(lib().wtc_debug_set_timeline(C.c_void_p(buf.data_ptr()) if buf is not None else None))
 
 
 # ------------------------------------------------------------------ torch side
