@@ -43,13 +43,15 @@ constexpr int kEpiThreads = kEpiWarps * 32;
 constexpr int kThreads = 64 + kEpiThreads;
 constexpr int kMaxCluster = 8;
 
-template <int BN, int STAGES, bool CLUSTER>
+// OUT_TILES: 32-row x 64-column f16 staging tiles per epilogue warp (2 = the warp's two
+// column groups never wait for each other's TMA read; 1 = smaller, leaves room for a stage).
+template <int BN, int STAGES, bool CLUSTER, int OUT_TILES>
 struct SmemLayout {
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BK * BN * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kHalfCols = BN / 2;                            // columns per epilogue thread
-  static constexpr int kOutWarpBytes = 32 * 64 * 2;                   // one 32-row x 64-column f16 staging tile
+  static constexpr int kOutWarpBytes = OUT_TILES * 32 * 64 * 2;
   static constexpr int kOutBytes = kEpiWarps * kOutWarpBytes;
   static constexpr int kPairBytes = 2 * BM * 8;                       // [half][row] float2
   static constexpr int kStatsBytes = CLUSTER ? 2 * kMaxCluster * BM * 8 : 0;
@@ -84,11 +86,11 @@ __device__ __forceinline__ void stamp(long long *timeline, int slot) {
   if (timeline) timeline[static_cast<size_t>(blockIdx.x) * 16 + slot] = static_cast<long long>(globaltimer_ns());
 }
 
-template <int BN, int STAGES, bool CLUSTER>
+template <int BN, int STAGES, bool CLUSTER, int OUT_TILES>
 __global__ void __launch_bounds__(kThreads, 1)
 fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmO, const TcParams p) {
-  using L = SmemLayout<BN, STAGES, CLUSTER>;
+  using L = SmemLayout<BN, STAGES, CLUSTER, OUT_TILES>;
   constexpr int HC = L::kHalfCols;      // columns per epilogue thread
   constexpr int NCH = HC / 32;          // 32-column chunks per epilogue thread
   // The 128-byte swizzle needs the stage buffers on 1024-byte boundaries.  There is no
@@ -224,6 +226,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const float c2 = p.c2;
     const bool pos = c2 >= 0.f;
     int it = 0;
+    uint32_t gcount = 0;                         // staging groups committed so far by this warp
     for (int w = first; w < p.num_items; w += stride, ++it) {
       int b, rb, nb; decode(w, b, rb, nb);
       const int ab = it & 1;
@@ -358,7 +361,9 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
       for (int g = 0; g < NCH / 2; ++g) {
         if (g * 64 < valid) {
-          if (lane == 0) tma_store_wait_read();    // the previous store has read the staging tile
+          uint8_t *tile = stg + (OUT_TILES == 2 ? (gcount & 1) * 4096 : 0);   // tiles alternate per committed group
+          // the store that last used this staging tile must have read it
+          if (lane == 0) { if (OUT_TILES == 2) tma_store_wait_read1(); else tma_store_wait_read(); }
           __syncwarp();
 #pragma unroll
           for (int hc = 0; hc < 2; ++hc) {
@@ -370,14 +375,15 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
               if (!CLUSTER) { const float2 back = __half22float2(hh); sum_r += back.x + back.y; }
               h[i >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
             }
-            stage_row_chunk(stg, lane, hc, h);
+            stage_row_chunk(tile, lane, hc, h);
           }
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            if (rows_live) tma_store_3d(&tmO, stg, col0 + g * 64, row0, b);
+            if (rows_live) tma_store_3d(&tmO, tile, col0 + g * 64, row0, b);
             tma_store_commit();
           }
+          ++gcount;
         }
       }
       if (!CLUSTER) {
@@ -406,11 +412,11 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
 }
 
-template <int BN, int STAGES, bool CLUSTER>
+template <int BN, int STAGES, bool CLUSTER, int OUT_TILES>
 cudaError_t launch_impl(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO, const TcParams &p,
                         int cluster_n, int num_sms, cudaStream_t s, TcLaunchInfo *info) {
-  using L = SmemLayout<BN, STAGES, CLUSTER>;
-  auto kern = fused_tc_kernel<BN, STAGES, CLUSTER>;
+  using L = SmemLayout<BN, STAGES, CLUSTER, OUT_TILES>;
+  auto kern = fused_tc_kernel<BN, STAGES, CLUSTER, OUT_TILES>;
   static bool attr_set = false;   // per template instance
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
@@ -466,12 +472,12 @@ cudaError_t launch_fused_cluster(const CUtensorMap &tmA, const CUtensorMap &tmB,
                                  const TcParams &p, int cluster_n, int num_sms, cudaStream_t s,
                                  TcLaunchInfo *info) {
   if (cluster_n < 1 || cluster_n > kMaxCluster) return cudaErrorInvalidValue;
-  return launch_impl<kTcBlockN, 3, true>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+  return launch_impl<kTcBlockN, 3, true, 2>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
 }
 
 cudaError_t launch_tiled_partial(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO,
                                  const TcParams &p, int num_sms, cudaStream_t s, TcLaunchInfo *info) {
-  return launch_impl<kTcBlockN, 4, false>(tmA, tmB, tmO, p, 1, num_sms, s, info);
+  return launch_impl<kTcBlockN, 4, false, 1>(tmA, tmB, tmO, p, 1, num_sms, s, info);
 }
 
 } // namespace wtc

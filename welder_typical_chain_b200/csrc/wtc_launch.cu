@@ -227,7 +227,7 @@ int launch_resolved(Resolved &r, const void *A, const void *B, void *Out, void *
                     int mode, cudaStream_t s, int *status) {
   const wtc_chain_desc &d = r.d;
   if (d.M == 0 || d.N == 0) return WTC_OK;
-  if (!A || !B || !Out) return fail(WTC_E_ARG, "null operand pointer");
+  if (!Out || (d.K > 0 && (!A || !B))) return fail(WTC_E_ARG, "null operand pointer");
 
   if (r.plan.kernel == WTC_KERNEL_SIMT_UNFUSED) {
     if (mode != 0) return fail(WTC_E_UNSUPPORTED, "the baseline variant has no sharded form");

@@ -218,6 +218,36 @@ def matmul_softmax_finish(desc: ChainDesc, out, workspace, all_stats, num_parts:
                                                       C.c_void_p(all_stats.data_ptr()), num_parts, _stream_ptr()))
 
 
+class PreparedCall:
+    """One chain call with every argument converted once: launch() is a single
+    foreign call, for loops where Python overhead would otherwise outweigh a
+    10-microsecond kernel."""
+
+    def __init__(self, A, B, out, scale: float = 1.0, workspace=None, acc_dtype: int = F32,
+                 variant: int = VARIANT_FUSED, flags: int = 0):
+        torch = _torch()
+        self.desc = _desc_for(A, B, _dt(out), scale, acc_dtype, variant, flags, None)
+        need = workspace_bytes(self.desc)
+        if need and (workspace is None or workspace.numel() * workspace.element_size() < need):
+            workspace = torch.empty(need, device=A.device, dtype=torch.uint8)
+        self._keep = (A, B, out, workspace)
+        self._fn = lib().wtc_matmul_softmax_launch
+        self._args = (C.byref(self.desc), C.c_void_p(A.data_ptr()), C.c_void_p(B.data_ptr()),
+                      C.c_void_p(out.data_ptr()),
+                      C.c_void_p(workspace.data_ptr()) if workspace is not None else None,
+                      workspace.numel() * workspace.element_size() if workspace is not None else 0)
+        self.out = out
+
+    def launch(self, stream_ptr) -> None:
+        rc = self._fn(*self._args, stream_ptr, None)
+        if rc != 0:
+            _check(rc)
+
+
+def current_stream_ptr():
+    return _stream_ptr()
+
+
 def check_device_status(status=None) -> None:
     ptr = C.c_void_p(status.data_ptr()) if status is not None else None
     _check(lib().wtc_check_device_status(ptr, _stream_ptr()))
