@@ -140,6 +140,40 @@ int wtc_matmul_softmax_finish_launch(const wtc_chain_desc *desc, void *Out, cons
  */
 int wtc_matmul_softmax_host(const wtc_chain_desc *desc, const void *hostA, const void *hostB, void *hostOut);
 
+/*
+ * Same chain, for callers that must not allocate device memory.  (No counterpart
+ * in the reference: its profiler allocates every buffer itself with cuMemAlloc.)
+ *
+ * Some hosts of this library cannot call cudaMalloc at the point where they need
+ * the chain: an inference server that handed all of HBM to its own pool at start
+ * up, a step loop that must not hit the device-wide synchronisation an
+ * allocation implies, a plugin running under a memory budget it may not exceed.
+ * This entry point runs the two-pass tiled schedule with its scratch -- the
+ * per-tile (max, sum) pairs and the device status word -- in an array that is
+ * part of the library image: WTC_STATIC_SCRATCH_BYTES (16 MiB) on every GPU
+ * that loads the library, held until the process exits.  It calls no cudaMalloc,
+ * cudaFree or allocating library routine; the caller still provides A, B and Out
+ * (device pointers).
+ *
+ * Limits and rules:
+ *  - f16 operands and output on the tensor-core path only (K, N and the row
+ *    strides multiples of 8), and batch * M * ceil(N/256) * 8 bytes of scratch
+ *    must fit: WTC_E_UNSUPPORTED / WTC_E_WORKSPACE otherwise, with the sizes in
+ *    wtc_last_error().
+ *  - The first call on each device looks the array's device address up (with
+ *    that device current).  Make that first call outside any stream capture.
+ *  - Every call on a device shares the one array.  Calls whose kernels may
+ *    overlap on the GPU (two streams, two threads) race on it: serialise them.
+ *    Nothing is assumed about what the previous call left there.
+ *  - device_status: as for wtc_matmul_softmax_launch (a zeroed int32 in the
+ *    caller's own device memory, checked with wtc_check_device_status).  With
+ *    NULL the kernels report into a word inside the static array, which this
+ *    call clears first and no entry point reads back.
+ */
+#define WTC_STATIC_SCRATCH_BYTES (16u << 20)
+int wtc_matmul_softmax_launch_static(const wtc_chain_desc *desc, const void *A, const void *B, void *Out,
+                                     void *stream, int *device_status);
+
 /* Synchronise `stream`, read a device status word, 0 if clean else WTC_E_DEVICE. */
 int wtc_check_device_status(const int *device_status, void *stream);
 

@@ -463,6 +463,64 @@ int wtc_debug_set_umma_geometry(uint32_t a_lbo, uint32_t a_sbo, uint32_t a_kstep
   return WTC_OK;
 }
 
+// ---- the entry point that allocates nothing -----------------------------------
+// Scratch for wtc_matmul_softmax_launch_static: one array that lives in the
+// library's device image (every GPU that loads the library carries it until the
+// process exits).  First 256 bytes: the device status word.  Rest: the per-tile
+// (max, sum) pairs of the two-pass schedule.
+constexpr size_t kStaticScratchBytes = WTC_STATIC_SCRATCH_BYTES;
+constexpr size_t kStaticStatusBytes = 256;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// The array's name is only a host-side handle here; the address kernels can use has to
+// be asked for, once per device, with that device current.
+unsigned char *static_scratch_for_current_device(int *rc_out) {
+  static unsigned char *ptrs[64] = {nullptr};
+  *rc_out = WTC_OK;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) { *rc_out = cuda_fail(e, "cudaGetDevice"); return nullptr; }
+  if (dev < 0 || dev >= 64) { *rc_out = fail(WTC_E_UNSUPPORTED, "device index %d out of range", dev); return nullptr; }
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (!ptrs[dev]) {
+    unsigned char *ptr = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_static_scratch);
+    if (e != cudaSuccess || !ptr) { *rc_out = cuda_fail(e, "cudaGetSymbolAddress(static scratch)"); return nullptr; }
+    ptrs[dev] = ptr;
+    g_maps.reserve(kMaxMaps);   // keep the tensor-map cache from growing later
+  }
+  return ptrs[dev];
+}
+
+int wtc_matmul_softmax_launch_static(const wtc_chain_desc *desc, const void *A, const void *B, void *Out, void *stream,
+                                     int *device_status) {
+  Resolved r;
+  int rc = resolve(desc, r);
+  if (rc) return rc;
+  if (!r.tc_ok)
+    return fail(WTC_E_UNSUPPORTED, "the static-scratch entry point covers the tensor-core two-pass schedule only "
+                                   "(f16 operands and output, K, N and row strides multiples of 8)");
+  const size_t need = static_cast<size_t>(r.d.batch) * r.d.M * r.num_nb * sizeof(float2);
+  if (need > kStaticScratchBytes - kStaticStatusBytes)
+    return fail(WTC_E_WORKSPACE, "this shape needs %zu bytes of scratch; the static scratch holds %zu "
+                                 "(use wtc_matmul_softmax_launch with a caller-provided workspace)",
+                need, kStaticScratchBytes - kStaticStatusBytes);
+  unsigned char *base = static_scratch_for_current_device(&rc);
+  if (!base) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // the array keeps whatever the previous call left: the status word must start at zero,
+  // the (max, sum) pairs are all rewritten before they are read
+  if (!device_status) {
+    cudaError_t e = cudaMemsetAsync(base, 0, sizeof(int), s);
+    if (e != cudaSuccess) return cuda_fail(e, "clearing the static status word");
+  }
+  r.d.flags |= WTC_FLAG_FORCE_TILED;
+  rc = resolve(&r.d, r);
+  if (rc) return rc;
+  return launch_resolved(r, A, B, Out, base + kStaticStatusBytes, kStaticScratchBytes - kStaticStatusBytes, nullptr, 0, s,
+                         device_status ? device_status : reinterpret_cast<int *>(base));
+}
+
 int wtc_debug_set_timeline(void *device_buffer) {
   g_timeline = static_cast<long long *>(device_buffer);
   return WTC_OK;

@@ -23,7 +23,7 @@ EXPORTS = [
     "wtc_abi_version", "wtc_last_error", "wtc_plan_query", "wtc_matmul_softmax_workspace_bytes",
     "wtc_matmul_softmax_launch", "wtc_matmul_softmax_partial_launch", "wtc_matmul_softmax_finish_launch",
     "wtc_matmul_softmax_host", "wtc_check_device_status", "wtc_matmul_softmax_time",
-    "wtc_debug_set_umma_geometry", "wtc_debug_set_timeline",
+    "wtc_debug_set_umma_geometry", "wtc_debug_set_timeline", "wtc_matmul_softmax_launch_static",
 ]
 
 
@@ -82,6 +82,7 @@ def lib() -> C.CDLL:
         L.wtc_matmul_softmax_time.argtypes = [dp, vp, vp, vp, vp, sz, vp, C.c_int, C.c_int, C.POINTER(C.c_float)]
         L.wtc_debug_set_umma_geometry.argtypes = [C.c_uint32] * 6
         L.wtc_debug_set_timeline.argtypes = [vp]
+        L.wtc_matmul_softmax_launch_static.argtypes = [dp, vp, vp, vp, vp, vp]
         _LIB = L
     return _LIB
 
@@ -246,6 +247,17 @@ class PreparedCall:
 
 def current_stream_ptr():
     return _stream_ptr()
+
+
+def matmul_softmax_static(A, B, scale: float, out, status=None, acc_dtype: int = F32):
+    """The entry point that allocates nothing: scratch lives in the library image."""
+    torch = _torch()
+    d = _desc_for(A, B, _dt(out), scale, acc_dtype, VARIANT_FUSED, 0, None)
+    with torch.cuda.device(A.device):
+        _check(lib().wtc_matmul_softmax_launch_static(
+            C.byref(d), C.c_void_p(A.data_ptr()), C.c_void_p(B.data_ptr()), C.c_void_p(out.data_ptr()),
+            _stream_ptr(), C.c_void_p(status.data_ptr()) if status is not None else None))
+    return out
 
 
 def check_device_status(status=None) -> None:
