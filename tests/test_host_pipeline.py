@@ -1,0 +1,206 @@
+"""The native host side on the CPU: chain recogniser, tile contract, the three backend
+modes of wtc-compiler, artifact tree, error behaviour, the dlopen C APIs and the harness
+scripts that need no GPU.  Mirrors the reference's script-level regression
+(bench/run_regression.sh:60-112, bench/run_pure_api_stress.sh:46-68)."""
+import ctypes
+import json
+import os
+import re
+import subprocess
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PKG = os.path.join(ROOT, "welder_typical_chain_b200")
+WTC = os.path.join(PKG, "build", "wtc-compiler")
+BK = os.path.join(PKG, "backend", "welder", "compiler", "build")
+MLIR = os.path.join(PKG, "mlir")
+
+
+@pytest.fixture(scope="module", autouse=True)
+def built(wtc_lib):
+    if not (os.path.exists(WTC) and os.path.exists(os.path.join(BK, "libwelder-compile-capi.so"))):
+        subprocess.run(["make", "-C", os.path.join(PKG, "host"), "-j8"], check=True, capture_output=True)
+
+
+def run(args, **kw):
+    return subprocess.run([WTC] + args, capture_output=True, text=True, **kw)
+
+
+def test_capi_headers_match_exports():
+    for header, lib in (("welder_solver_capi.h", "libwelder-solver-capi.so"), ("welder_compile_capi.h", "libwelder-compile-capi.so")):
+        text = re.sub(r"/\*.*?\*/", "", open(os.path.join(ROOT, "include", header)).read(), flags=re.S)
+        L = ctypes.CDLL(os.path.join(BK, lib))
+        for sym in re.findall(r"\b(welder_[a-z_]+)\s*\(", text):
+            assert hasattr(L, sym), f"{sym} missing from {lib}"
+    # the C++-linkage in-process entry is exported from the compile library too
+    out = subprocess.run(["nm", "-D", "--defined-only", os.path.join(BK, "libwelder-compile-capi.so")], capture_output=True, text=True).stdout
+    assert "_Z18welderCompilerMainiPPc" in out
+
+
+@pytest.mark.parametrize("mode", ["api", "process_chain", "shell", "inprocess"])
+def test_full_pipeline_artifact_tree(tmp_path, mode):
+    out = tmp_path / "o"
+    r = run(["--input", os.path.join(MLIR, "cfg2_f16_native_4096x1024x1024.mlir"), "--out-dir", str(out), "--backend-mode", mode, "--verbose"])
+    assert r.returncode == 0, r.stderr
+    for rel in ("ir/01.canonicalized.mlir", "ir/01.canonicalize.log", "ir/02.tagged.mlir", "ir/02.tags.json", "ir/chain.json",
+                "search/best.json", "search/best_summary.json", "search/candidates.tsv", "search/solver.log",
+                "fused/03.after_postbufferize.mlir", "fused/04.after_workgroup_launch.mlir", "fused/04c.after_linalg_to_loops.mlir",
+                "fused/05.out.nvvm.runnable.mlir", "fused/compile.log", "fused/postbufferize_report.txt"):
+        assert (out / rel).stat().st_size > 0, rel
+    best = json.load(open(out / "search/best.json"))
+    assert best == dict(tileM=128, tileN=256, tileK=64, threadTileM=1, threadTileN=128)
+    chain = json.load(open(out / "ir/chain.json"))
+    assert (chain["M"], chain["N"], chain["K"], chain["scale"]) == (4096, 1024, 1024, 0.03125)
+    assert (chain["in_dtype"], chain["acc_dtype"], chain["out_dtype"]) == ("f16", "f32", "f16")
+    plan = open(out / "fused/05.out.nvvm.runnable.mlir").read()
+    assert 'kernel = "tc_cluster"' in plan and "cluster_n = 4" in plan and "gpu.launch_func" in plan
+    assert "workgroup(" in open(out / "fused/04.after_workgroup_launch.mlir").read()
+    tags = json.load(open(out / "ir/02.tags.json"))
+    assert tags["counts"]["matmul"] == 1 and tags["counts"]["exp"] == 1 and tags["counts"]["div"] == 1
+    tagged = open(out / "ir/02.tagged.mlir").read()
+    for t in ("welder.matmul_anchor", "welder.row_reduction", "welder.elementwise_exp", "welder.elementwise_div"):
+        assert tagged.count("// wtc.tag: " + t) == 1
+    if mode == "api":
+        assert "search falls back to process_chain" in r.stdout
+
+
+def test_named_softmax_is_decomposed(tmp_path):
+    for name, batched in (("matmul_softmax_chain_named_softmax.mlir", False), ("cfg3_batched_attention_named.mlir", True)):
+        out = tmp_path / name
+        r = run(["--input", os.path.join(MLIR, name), "--out-dir", str(out), "--backend-mode", "process_chain", "--search-only"])
+        assert r.returncode == 0, r.stderr
+        text = open(out / "ir/01.canonicalized.mlir").read()
+        assert "linalg.softmax" not in text and "math.exp" in text and "arith.divf" in text
+        assert text.count('"reduction"') == 2
+        assert ("linalg.batch_matmul" in text) == batched
+        chain = json.load(open(out / "ir/chain.json"))
+        assert chain["softmax_form"] == "named" and chain["batched"] == batched
+
+
+def test_every_shipped_chain_compiles_to_the_expected_kernel(tmp_path):
+    expect = {"cfg1_decomposed_f32_128": "simt_fused", "cfg2_f16_native_4096x1024x1024": "tc_cluster",
+              "cfg3_batched_attention_named": "tc_cluster", "cfg4_vocab_logits": "tc_tiled", "cfg5_skinny_decode": "tc_tiled",
+              "matmul_softmax_chain": "simt_fused", "matmul_softmax_chain_f16_native": "simt_fused",
+              "matmul_softmax_chain_named_softmax": "simt_fused"}
+    for stem, kernel in expect.items():
+        out = tmp_path / stem
+        r = run(["--input", os.path.join(MLIR, stem + ".mlir"), "--out-dir", str(out), "--backend-mode", "api", "--pure-api-full"])
+        assert r.returncode == 0, (stem, r.stderr)
+        assert f'kernel = "{kernel}"' in open(out / "fused/05.out.nvvm.runnable.mlir").read(), stem
+
+
+def test_tile_source_priority_and_overrides(tmp_path):
+    inp = os.path.join(MLIR, "cfg2_f16_native_4096x1024x1024.mlir")
+    bj = tmp_path / "best.json"
+    # a nested summary loads too: the first occurrence of each key wins
+    bj.write_text('{"problem": {"m": 1}, "best": {"tileM": 64, "tileN": 128, "tileK": 32, "threadTileM": 8, "threadTileN": 2}}')
+    out = tmp_path / "o"
+    r = run(["--input", inp, "--out-dir", str(out), "--backend-mode", "api", "--compile-only", "--best-json", str(bj), "--tile-k", "16"])
+    assert r.returncode == 0, r.stderr
+    assert not (out / "search/best_summary.json").exists()            # --best-json given: no search
+    assert json.load(open(out / "search/best.json")) == dict(tileM=64, tileN=128, tileK=16, threadTileM=8, threadTileN=2)
+    plan = open(out / "fused/05.out.nvvm.runnable.mlir").read()
+    assert "requested_m = 64" in plan and "tile_m = 128" in plan and "substituted = 1" in plan
+    assert "substituted" in open(out / "fused/compile.log").read()
+    # --no-search without tiles: built-in defaults 32x64x16, thread tile 2x2
+    out2 = tmp_path / "o2"
+    assert run(["--input", inp, "--out-dir", str(out2), "--backend-mode", "api", "--no-search"]).returncode == 0
+    assert json.load(open(out2 / "search/best.json")) == dict(tileM=32, tileN=64, tileK=16, threadTileM=2, threadTileN=2)
+
+
+def test_baseline_variant_and_repeat(tmp_path):
+    inp = os.path.join(MLIR, "matmul_softmax_chain_f16_native.mlir")
+    out = tmp_path / "o"
+    assert run(["--input", inp, "--out-dir", str(out), "--backend-mode", "api", "--baseline"]).returncode == 0
+    assert open(out / "baseline/04.after_workgroup_launch.mlir").read().count("gpu.launch") == 5
+    assert "launch_kernel_count=5" in open(out / "baseline/postbufferize_report.txt").read()
+    out = tmp_path / "rep"
+    r = run(["--input", inp, "--out-dir", str(out), "--backend-mode", "api", "--pure-api-full", "--repeat", "25"])
+    assert r.returncode == 0, r.stderr
+    assert (out / "iter_24/fused/05.out.nvvm.runnable.mlir").exists()
+
+
+def test_usage_and_stage_errors(tmp_path):
+    assert run([]).returncode == 2
+    assert run(["--bogus"]).returncode == 2
+    assert run(["--input", "x.mlir", "--backend-mode", "nope"]).returncode == 2
+    assert run(["--input", "x.mlir", "--repeat", "0"]).returncode == 2
+    r = run(["--input", str(tmp_path / "missing.mlir"), "--out-dir", str(tmp_path / "o")])
+    assert r.returncode == 1 and "canonicalize failed" in r.stderr
+    bad = tmp_path / "bad.mlir"
+    bad.write_text("module { func.func @main(%A: tensor<4x4xf32>, %B: tensor<4x4xf32>) -> tensor<4x4xf32> { return %A : tensor<4x4xf32> } }")
+    r = run(["--input", str(bad), "--out-dir", str(tmp_path / "o")])
+    assert r.returncode == 1 and "matmul" in r.stderr
+    mism = open(os.path.join(MLIR, "cfg1_decomposed_f32_128.mlir")).read().replace("%B: tensor<128x128xf32>", "%B: tensor<64x128xf32>")
+    (tmp_path / "mism.mlir").write_text(mism)
+    r = run(["--input", str(tmp_path / "mism.mlir"), "--out-dir", str(tmp_path / "o")])
+    assert r.returncode == 1
+    r = run(["--input", os.path.join(MLIR, "cfg1_decomposed_f32_128.mlir"), "--out-dir", str(tmp_path / "o3"), "--backend-root", str(tmp_path / "nowhere")])
+    assert r.returncode == 1 and "backend root not found" in r.stderr
+    # a non-positive override is ignored (only values > 0 apply); a non-positive tile in best.json is refused
+    r = run(["--input", os.path.join(MLIR, "cfg1_decomposed_f32_128.mlir"), "--out-dir", str(tmp_path / "o4"), "--no-search", "--tile-m", "-4", "--backend-mode", "api"])
+    assert r.returncode == 0
+    zero = tmp_path / "zero.json"
+    zero.write_text('{"tileM": 0, "tileN": 64, "tileK": 16, "threadTileM": 2, "threadTileN": 2}')
+    for mode in ("api", "process_chain"):
+        r = run(["--input", os.path.join(MLIR, "cfg1_decomposed_f32_128.mlir"), "--out-dir", str(tmp_path / "o5"), "--best-json", str(zero), "--backend-mode", mode])
+        assert r.returncode == 1 and "tile" in r.stderr
+
+
+def test_solver_and_compile_c_api_directly(tmp_path):
+    inp = os.path.join(MLIR, "cfg4_vocab_logits.mlir").encode()
+    S = ctypes.CDLL(os.path.join(BK, "libwelder-solver-capi.so"))
+    tiles = [ctypes.c_int64(0) for _ in range(5)]
+    err = ctypes.create_string_buffer(4096)
+    rc = S.welder_solver_solve_typical_chain(inp, str(tmp_path / "bs.json").encode(), str(tmp_path / "c.tsv").encode(), ctypes.c_int64(1), 0,
+                                             *[ctypes.byref(t) for t in tiles], err, ctypes.c_size_t(4096))
+    assert rc == 0 and [t.value for t in tiles] == [128, 256, 64, 1, 128] and err.value == b""
+    header = open(tmp_path / "c.tsv").readline().split("\t")
+    assert len(header) == 13 and header[:6] == ["rank", "tileM", "tileN", "tileK", "threadTileM", "threadTileN"]
+    summary = json.load(open(tmp_path / "bs.json"))
+    assert summary["problem"] == dict(m=8192, n=32000, k=4096, batch=1) and summary["arch"]["numSM"] == 148
+    assert summary["best"]["bytesCut"] > 0          # two-pass: the output crosses HBM again
+    rc = S.welder_solver_solve_typical_chain(b"/nonexistent.mlir", None, None, ctypes.c_int64(1), 0, *[ctypes.byref(t) for t in tiles], err, ctypes.c_size_t(4096))
+    assert rc == 2 and b"failed to read" in err.value
+    assert S.welder_solver_solve_typical_chain(None, None, None, ctypes.c_int64(1), 0, *[ctypes.byref(t) for t in tiles], err, ctypes.c_size_t(4096)) == 1
+    Cc = ctypes.CDLL(os.path.join(BK, "libwelder-compile-capi.so"))
+    args = lambda tm: (inp, str(tmp_path / "cc").encode(), b"", b"", ctypes.c_int64(tm), ctypes.c_int64(256), ctypes.c_int64(64),
+                       ctypes.c_int64(1), ctypes.c_int64(128), ctypes.c_int64(1), 1, 0, err, ctypes.c_size_t(4096))
+    assert Cc.welder_compile_typical_chain_to_nvvm(*args(128)) == 0
+    assert 'kernel = "tc_tiled"' in open(tmp_path / "cc" / "05.out.nvvm.runnable.mlir").read()
+    assert Cc.welder_compile_typical_chain_to_nvvm(*args(0)) == 1 and err.value == b"invalid tile sizes"
+    small = ctypes.create_string_buffer(8)            # the buffer is always NUL-terminated, however small
+    a = list(args(0)); a[-2], a[-1] = small, ctypes.c_size_t(8)
+    assert Cc.welder_compile_typical_chain_to_nvvm(*a) == 1 and small.value == b"invalid"
+
+
+def test_harness_scripts_without_gpu(tmp_path):
+    env = dict(os.environ, OUT_BASE=str(tmp_path / "reg"), PURE_API_REPEAT="5")
+    r = subprocess.run(["bash", os.path.join(PKG, "bench", "run_regression.sh")], capture_output=True, text=True, env=env)
+    assert r.returncode == 0, r.stdout + r.stderr
+    rows = open(tmp_path / "reg" / "regression_summary.tsv").read().splitlines()[1:]
+    assert len(rows) >= 14 and all(x.split("\t")[1] == "PASS" for x in rows)
+    env = dict(os.environ, OUT_BASE=str(tmp_path / "st"), REPEAT="30")
+    r = subprocess.run(["bash", os.path.join(PKG, "bench", "run_pure_api_stress.sh")], capture_output=True, text=True, env=env)
+    assert r.returncode == 0 and "stress passed" in r.stdout
+    # perf guard arithmetic on synthetic summaries
+    base, cur = tmp_path / "base", tmp_path / "cur"
+    for d, (b, f) in ((base, (1.0, 0.5)), (cur, (1.02, 0.51))):
+        d.mkdir()
+        (d / "ab_summary.tsv").write_text(f"case\tavg_ms\nbaseline\t{b}\t5\nfused\t{f}\t1\n")
+        (d / "speedup.tsv").write_text(f"speedup\t{b / f:.4f}\n")
+    env = dict(os.environ, BASELINE_DIR=str(base), CURRENT_OUT_BASE=str(cur))
+    r = subprocess.run(["bash", os.path.join(PKG, "bench", "check_perf_guard.sh")], capture_output=True, text=True, env=env)
+    assert r.returncode == 0 and r.stdout.count("PASS") == 3
+    (cur / "ab_summary.tsv").write_text("case\tavg_ms\nbaseline\t1.0\t5\nfused\t0.6\t1\n")
+    r = subprocess.run(["bash", os.path.join(PKG, "bench", "check_perf_guard.sh")], capture_output=True, text=True, env=env)
+    assert r.returncode == 1 and "FAIL fused.avg_ms" in r.stdout
+
+
+def test_trace_file(tmp_path):
+    env = dict(os.environ, WTC_TRACE_FILE=str(tmp_path / "trace.jsonl"))
+    r = run(["--input", os.path.join(MLIR, "cfg1_decomposed_f32_128.mlir"), "--out-dir", str(tmp_path / "o"), "--backend-mode", "api", "--pure-api-full"], env=env)
+    assert r.returncode == 0
+    spans = [json.loads(l) for l in open(tmp_path / "trace.jsonl")]
+    assert {s["name"] for s in spans} >= {"canonicalize", "tagging", "search", "compile"} and all(s["ok"] for s in spans)

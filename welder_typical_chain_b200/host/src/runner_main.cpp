@@ -1,0 +1,268 @@
+// welder-profiler (B200 build): reads a 05.out.nvvm.runnable.mlir plan, allocates and
+// initialises the buffers, runs the chain through the C-ABI launch layer, times it with
+// CUDA events and optionally dumps the result.  Replaces the reference's PTX-JIT runner
+// (backend/welder/compiler/solver/WelderProfiler.cpp:59-882): same input patterns
+// (solver/WelderProfilerRuntime.h:128-168,193-231), same `avg_ms= iters= warmup=` line
+// (:788-793), same dump format (.bin + .bin.json, solver/WelderProfilerRuntime.h:104-126).
+//
+//   welder-profiler [--warmup=N] [--iters=N] [--init=zero|linear|random] [--seed=S]
+//                   [--dump-last-2d PATH] [--dump-as-f32] [--f16-rne] [--list-memrefs]
+//                   [--m M] [--batch B]   (run fewer rows / batches than the plan has)
+//                   <05.out.nvvm.runnable.mlir>
+// Flags that only make sense for the reference's memref-descriptor launches (--run-all-kernels,
+// --i64 %x=v, --init-ptr %x, --fill spec, --fill-each-iter) are accepted and ignored.
+#include "../../../include/wtc_launch.h"
+
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+
+#include <cmath>
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <filesystem>
+#include <fstream>
+#include <iostream>
+#include <regex>
+#include <sstream>
+#include <string>
+#include <vector>
+
+namespace {
+
+std::string readAll(const std::string &path) {
+  std::ifstream ifs(path);
+  std::ostringstream o;
+  o << ifs.rdbuf();
+  return o.str();
+}
+
+bool attrInt(const std::string &text, const std::string &key, long long &v) {
+  std::smatch m;
+  if (!std::regex_search(text, m, std::regex("\\b" + key + "\\s*=\\s*(-?[0-9]+)"))) return false;
+  v = std::stoll(m[1].str());
+  return true;
+}
+bool attrStr(const std::string &text, const std::string &key, std::string &v) {
+  std::smatch m;
+  if (!std::regex_search(text, m, std::regex("\\b" + key + "\\s*=\\s*\"([^\"]*)\""))) return false;
+  v = m[1].str();
+  return true;
+}
+bool attrDouble(const std::string &text, const std::string &key, double &v) {
+  std::smatch m;
+  if (!std::regex_search(text, m, std::regex("\\b" + key + "\\s*=\\s*([-+0-9.eE]+)"))) return false;
+  v = std::strtod(m[1].str().c_str(), nullptr);
+  return true;
+}
+
+// f32 -> f16 the way the reference profiler converts (adds half an ulp, then truncates).
+uint16_t f16_profiler(float x) {
+  uint32_t u; std::memcpy(&u, &x, 4);
+  const uint32_t sign = (u >> 31) & 1u; int exp = static_cast<int>((u >> 23) & 0xFFu); uint32_t mant = u & 0x7FFFFFu;
+  const uint16_t s = static_cast<uint16_t>(sign << 15);
+  if (exp == 0xFF) return static_cast<uint16_t>(s | (mant == 0 ? 0x7C00u : 0x7E00u));
+  int he = exp - 127 + 15;
+  if (he >= 31) return static_cast<uint16_t>(s | 0x7C00u);
+  if (he <= 0) {
+    if (he < -10) return s;
+    mant |= 0x800000u;
+    const int shift = 14 - he;
+    return static_cast<uint16_t>(s | static_cast<uint16_t>((mant + (1u << (shift - 1))) >> shift));
+  }
+  uint32_t r = mant + 0x1000u;
+  if (r & 0x800000u) { r = 0; if (++he >= 31) return static_cast<uint16_t>(s | 0x7C00u); }
+  return static_cast<uint16_t>(s | static_cast<uint16_t>(he << 10) | static_cast<uint16_t>((r >> 13) & 0x3FFu));
+}
+// round to nearest even
+uint16_t f16_rne(float x) {
+  uint32_t u; std::memcpy(&u, &x, 4);
+  const uint32_t sign = (u >> 31) & 1u, exp = (u >> 23) & 0xFFu; uint32_t mant = u & 0x7FFFFFu;
+  if (exp == 0xFF) return static_cast<uint16_t>((sign << 15) | 0x7C00u | (mant ? 0x200u : 0u));
+  int e = static_cast<int>(exp) - 127 + 15;
+  if (e >= 31) return static_cast<uint16_t>((sign << 15) | 0x7C00u);
+  if (e <= 0) {
+    if (e < -10) return static_cast<uint16_t>(sign << 15);
+    mant |= 0x800000u;
+    const int shift = 14 - e;
+    uint32_t m16 = mant >> shift;
+    const uint32_t rem = mant & ((1u << shift) - 1u), half = 1u << (shift - 1);
+    if (rem > half || (rem == half && (m16 & 1u))) ++m16;
+    return static_cast<uint16_t>((sign << 15) | m16);
+  }
+  uint32_t m16 = mant >> 13;
+  const uint32_t rem = mant & 0x1FFFu;
+  if (rem > 0x1000u || (rem == 0x1000u && (m16 & 1u))) { if (++m16 == 0x400u) { m16 = 0; if (++e >= 31) return static_cast<uint16_t>((sign << 15) | 0x7C00u); } }
+  return static_cast<uint16_t>((sign << 15) | (static_cast<uint32_t>(e) << 10) | m16);
+}
+float f16_to_f32(uint16_t h) {
+  const uint32_t sign = (h >> 15) & 1u, exp = (h >> 10) & 0x1Fu, mant = h & 0x3FFu;
+  float v;
+  if (exp == 0) v = std::ldexp(static_cast<float>(mant), -24);
+  else if (exp == 31) v = mant ? NAN : INFINITY;
+  else v = std::ldexp(static_cast<float>(mant | 0x400u), static_cast<int>(exp) - 25);
+  return sign ? -v : v;
+}
+
+// zero / linear / random(xorshift32) over the flat row-major index, one stream per buffer
+void fillPattern(std::vector<float> &dst, const std::string &mode, uint64_t seed) {
+  uint32_t rng = static_cast<uint32_t>(seed == 0 ? 1 : seed);
+  for (size_t i = 0; i < dst.size(); ++i) {
+    if (mode == "zero") dst[i] = 0.f;
+    else if (mode == "random") {
+      rng ^= rng << 13; rng ^= rng >> 17; rng ^= rng << 5;
+      dst[i] = static_cast<float>(rng) * (1.0f / 4294967296.0f) * 2.0f - 1.0f;
+    } else dst[i] = static_cast<float>(static_cast<int64_t>(i) % 1024) * 0.001f - 0.5f;
+  }
+}
+
+#define CK(call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) { std::cerr << "CUDA error in " #call ": " << cudaGetErrorString(e_) << "\n"; return 2; } } while (0)
+
+} // namespace
+
+int main(int argc, char **argv) {
+  int warmup = 10, iters = 200;
+  std::string init = "linear", dumpPath, planPath;
+  uint64_t seed = 1;
+  bool dumpAsF32 = false, rne = false, listMemrefs = false;
+  long long runM = 0, runBatch = 0;
+  for (int i = 1; i < argc; ++i) {
+    std::string a = argv[i];
+    auto eqval = [&](const char *name, std::string &out) {
+      const std::string p = std::string(name) + "=";
+      if (a.rfind(p, 0) == 0) { out = a.substr(p.size()); return true; }
+      if (a == name && i + 1 < argc) { out = argv[++i]; return true; }
+      return false;
+    };
+    std::string v;
+    if (eqval("--warmup", v)) warmup = std::atoi(v.c_str());
+    else if (eqval("--iters", v)) iters = std::atoi(v.c_str());
+    else if (eqval("--init", v)) init = v;
+    else if (eqval("--seed", v)) seed = std::strtoull(v.c_str(), nullptr, 10);
+    else if (eqval("--dump-last-2d", v)) dumpPath = v;
+    else if (eqval("--m", v)) runM = std::atoll(v.c_str());
+    else if (eqval("--batch", v)) runBatch = std::atoll(v.c_str());
+    else if (a == "--dump-as-f32") dumpAsF32 = true;
+    else if (a == "--f16-rne") rne = true;
+    else if (a == "--list-memrefs") listMemrefs = true;
+    else if (a == "--run-all-kernels" || a == "--fill-each-iter") continue;
+    else if (a == "--i64" || a == "--init-ptr" || a == "--init-ptr-f16" || a == "--fill" || a == "--elem-bytes") { if (i + 1 < argc) ++i; }
+    else if (a.rfind("--", 0) == 0) continue;
+    else planPath = a;
+  }
+  if (planPath.empty()) { std::cerr << "usage: welder-profiler [options] <05.out.nvvm.runnable.mlir>\n"; return 2; }
+  if (init != "zero" && init != "linear" && init != "random") { std::cerr << "error: unknown --init pattern: " << init << "\n"; return 2; }
+  const std::string plan = readAll(planPath);
+  if (plan.empty()) { std::cerr << "error: cannot open file: " << planPath << "\n"; return 2; }
+  long long batch = 1, M = 0, N = 0, K = 0, bBatched = 0, tm = 0, tn = 0, tk = 0;
+  std::string inT, accT, outT, variant = "fused";
+  double scale = 1.0;
+  if (!attrInt(plan, "batch", batch) || !attrInt(plan, "M", M) || !attrInt(plan, "N", N) || !attrInt(plan, "K", K) ||
+      !attrStr(plan, "in_dtype", inT) || !attrStr(plan, "acc_dtype", accT) || !attrStr(plan, "out_dtype", outT)) {
+    std::cerr << "error: " << planPath << " is not a wtc launch plan (no wtc.chain attributes)\n";
+    return 2;
+  }
+  attrInt(plan, "b_batched", bBatched); attrDouble(plan, "scale", scale); attrStr(plan, "variant", variant);
+  attrInt(plan, "requested_m", tm); attrInt(plan, "requested_n", tn); attrInt(plan, "requested_k", tk);
+  if (runM > 0 && runM <= M) M = runM;
+  if (runBatch > 0 && runBatch <= batch) batch = runBatch;
+  const size_t inSz = inT == "f16" ? 2 : 4, outSz = outT == "f16" ? 2 : 4;
+  const size_t aElems = static_cast<size_t>(batch) * M * K, bElems = static_cast<size_t>(bBatched ? batch : 1) * K * N,
+               oElems = static_cast<size_t>(batch) * M * N;
+  if (listMemrefs) {
+    std::cout << "%A rank=" << (batch > 1 ? 3 : 2) << " elem_bytes=" << inSz << " sizes=[" << batch * M << ", " << K << "] role=input\n"
+              << "%B rank=2 elem_bytes=" << inSz << " sizes=[" << K << ", " << N << "] role=input\n"
+              << "%Out rank=2 elem_bytes=" << outSz << " sizes=[" << batch * M << ", " << N << "] role=output\n";
+    return 0;
+  }
+
+  // ---- the launch layer
+  std::string lib;
+  if (const char *e = std::getenv("WTC_LAUNCH_LIB"); e && *e) lib = e;
+  else {
+    std::error_code ec;
+    std::filesystem::path dir = std::filesystem::read_symlink("/proc/self/exe", ec).parent_path();
+    for (int up = 0; up < 6 && lib.empty(); ++up, dir = dir.parent_path())
+      if (std::filesystem::exists(dir / "libwtc_launch.so")) lib = (dir / "libwtc_launch.so").string();
+  }
+  void *h = lib.empty() ? nullptr : dlopen(lib.c_str(), RTLD_NOW | RTLD_LOCAL);
+  if (!h) { std::cerr << "error: cannot load the launch library libwtc_launch.so (" << (lib.empty() ? "not found; set WTC_LAUNCH_LIB" : dlerror()) << ")\n"; return 2; }
+  auto wsBytes = reinterpret_cast<decltype(&wtc_matmul_softmax_workspace_bytes)>(dlsym(h, "wtc_matmul_softmax_workspace_bytes"));
+  auto timeFn = reinterpret_cast<decltype(&wtc_matmul_softmax_time)>(dlsym(h, "wtc_matmul_softmax_time"));
+  auto launchFn = reinterpret_cast<decltype(&wtc_matmul_softmax_launch)>(dlsym(h, "wtc_matmul_softmax_launch"));
+  auto statusFn = reinterpret_cast<decltype(&wtc_check_device_status)>(dlsym(h, "wtc_check_device_status"));
+  auto lastError = reinterpret_cast<decltype(&wtc_last_error)>(dlsym(h, "wtc_last_error"));
+  if (!wsBytes || !timeFn || !launchFn || !statusFn || !lastError) { std::cerr << "error: launch library lacks the expected entry points\n"; return 2; }
+
+  wtc_chain_desc d = {};
+  d.struct_size = sizeof d;
+  d.batch = static_cast<int32_t>(batch);
+  d.M = M; d.N = N; d.K = K;
+  d.b_batch_stride = (bBatched || batch == 1) ? 0 : -1;
+  d.in_dtype = inT == "f16" ? WTC_F16 : WTC_F32;
+  d.out_dtype = outT == "f16" ? WTC_F16 : WTC_F32;
+  d.acc_dtype = accT == "f16" ? WTC_F16 : WTC_F32;
+  d.scale = static_cast<float>(scale);
+  d.tile_m = static_cast<int32_t>(tm); d.tile_n = static_cast<int32_t>(tn); d.tile_k = static_cast<int32_t>(tk);
+  d.variant = variant == "baseline" ? WTC_VARIANT_BASELINE : WTC_VARIANT_FUSED;
+  size_t ws = 0;
+  if (wsBytes(&d, &ws) != 0) { std::cerr << "error: " << lastError() << "\n"; return 2; }
+
+  // ---- buffers: both inputs are filled from the start of the same stream, like `--init-ptr %arg0 --init-ptr %arg7`
+  std::vector<float> hostA(aElems), hostB(bElems);
+  fillPattern(hostA, init, seed);
+  fillPattern(hostB, init, seed);
+  void *dA = nullptr, *dB = nullptr, *dO = nullptr, *dW = nullptr;
+  CK(cudaSetDevice(0));
+  CK(cudaMalloc(&dA, std::max<size_t>(aElems * inSz, 16)));
+  CK(cudaMalloc(&dB, std::max<size_t>(bElems * inSz, 16)));
+  CK(cudaMalloc(&dO, std::max<size_t>(oElems * outSz, 16)));
+  if (ws) CK(cudaMalloc(&dW, ws));
+  if (inSz == 2) {
+    std::vector<uint16_t> t(std::max(aElems, bElems));
+    for (size_t i = 0; i < aElems; ++i) t[i] = rne ? f16_rne(hostA[i]) : f16_profiler(hostA[i]);
+    CK(cudaMemcpy(dA, t.data(), aElems * 2, cudaMemcpyHostToDevice));
+    for (size_t i = 0; i < bElems; ++i) t[i] = rne ? f16_rne(hostB[i]) : f16_profiler(hostB[i]);
+    CK(cudaMemcpy(dB, t.data(), bElems * 2, cudaMemcpyHostToDevice));
+  } else {
+    CK(cudaMemcpy(dA, hostA.data(), aElems * 4, cudaMemcpyHostToDevice));
+    CK(cudaMemcpy(dB, hostB.data(), bElems * 4, cudaMemcpyHostToDevice));
+  }
+  CK(cudaMemset(dO, 0xFF, oElems * outSz));   // NaN pattern: unwritten output shows up in a verify run
+  cudaStream_t s;
+  CK(cudaStreamCreate(&s));
+
+  float avgMs = 0.f;
+  if (iters > 0) {
+    if (timeFn(&d, dA, dB, dO, dW, ws, s, warmup, iters, &avgMs) != 0) { std::cerr << "error: " << lastError() << "\n"; return 2; }
+  } else {
+    if (launchFn(&d, dA, dB, dO, dW, ws, s, nullptr) != 0 || statusFn(nullptr, s) != 0) { std::cerr << "error: " << lastError() << "\n"; return 2; }
+  }
+
+  if (!dumpPath.empty()) {
+    std::vector<unsigned char> raw(oElems * outSz);
+    CK(cudaMemcpy(raw.data(), dO, raw.size(), cudaMemcpyDeviceToHost));
+    size_t elemBytes = outSz;
+    std::vector<unsigned char> out;
+    if (dumpAsF32 && outSz == 2) {
+      out.resize(oElems * 4);
+      for (size_t i = 0; i < oElems; ++i) {
+        uint16_t hbits; std::memcpy(&hbits, &raw[i * 2], 2);
+        const float f = f16_to_f32(hbits);
+        std::memcpy(&out[i * 4], &f, 4);
+      }
+      elemBytes = 4;
+    } else out.swap(raw);
+    std::ofstream ofs(dumpPath, std::ios::binary);
+    ofs.write(reinterpret_cast<const char *>(out.data()), static_cast<std::streamsize>(out.size()));
+    std::ofstream meta(dumpPath + ".json");
+    meta << "{\n  \"sym\": \"%Out\",\n  \"rank\": 2,\n  \"elem_bytes\": " << elemBytes << ",\n  \"offset\": 0,\n  \"sizes\": [" << batch * M << ", " << N
+         << "],\n  \"strides\": [" << N << ", 1],\n  \"bytes\": " << out.size() << "\n}\n";
+    if (!ofs || !meta) { std::cerr << "error: cannot write dump: " << dumpPath << "\n"; return 2; }
+  }
+  cudaFree(dA); cudaFree(dB); cudaFree(dO); if (dW) cudaFree(dW);
+  std::printf("kernel_variant=%s shape=%lldx%lldx%lldx%lld\n", variant.c_str(), batch, M, N, K);
+  std::printf("avg_ms=%.7g iters=%d warmup=%d\n", avgMs, iters, warmup);
+  return 0;
+}
