@@ -224,7 +224,7 @@ def main():
     rows_total = batch * M
     if col_sharded:
         row_stats = torch.empty((rows_total, 2), device=dev, dtype=torch.float32)
-        all_stats = torch.empty((world, rows_total, 2), device=dev, dtype=torch.float32)
+        all_stats = torch.empty((world * rows_total, 2), device=dev, dtype=torch.float32)   # rank-major [world][rows][2]
 
     prepared = None
     if not col_sharded:

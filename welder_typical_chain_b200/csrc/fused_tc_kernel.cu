@@ -251,6 +251,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       tmem_ld_wait();
       tc_fence_before_sync();
       mbar_arrive(&accum_empty[ab]);
+      if (lead && it == 0) stamp(p.timeline, 14);
       if (p.round_logits_f16) {
 #pragma unroll
         for (int c = 0; c < NCH; ++c)
@@ -295,6 +296,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         m_half = -INFINITY;
       }
 
+      if (lead && it == 0) stamp(p.timeline, 15);
       // ---- e = 2^(v - m_half) in place, row sum ----
       float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
       if (valid == HC) {
@@ -365,6 +367,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           // the store that last used this staging tile must have read it
           if (lane == 0) { if (OUT_TILES == 2) tma_store_wait_read1(); else tma_store_wait_read(); }
           __syncwarp();
+          if (lead && it == 0 && g == 0) stamp(p.timeline, 9);
 #pragma unroll
           for (int hc = 0; hc < 2; ++hc) {
             const int c = g * 2 + hc;
@@ -377,12 +380,15 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             }
             stage_row_chunk(tile, lane, hc, h);
           }
+          if (lead && it == 0 && g == 0) stamp(p.timeline, 10);
           fence_proxy_async_smem();
           __syncwarp();
+          if (lead && it == 0 && g == 0) stamp(p.timeline, 11);
           if (lane == 0) {
             if (rows_live) tma_store_3d(&tmO, tile, col0 + g * 64, row0, b);
             tma_store_commit();
           }
+          if (lead && it == 0 && g == 0) stamp(p.timeline, 12);
           ++gcount;
         }
       }
