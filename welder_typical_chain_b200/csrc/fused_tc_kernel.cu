@@ -45,21 +45,22 @@ constexpr int kMaxCluster = 8;
 
 // OUT_TILES: 32-row x 64-column f16 staging tiles per epilogue warp (2 = the warp's two
 // column groups never wait for each other's TMA read; 1 = smaller, leaves room for a stage).
-template <int BN, int STAGES, bool CLUSTER, int OUT_TILES>
+template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool PIPE>
 struct SmemLayout {
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BK * BN * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kHalfCols = BN / 2;                            // columns per epilogue thread
-  static constexpr int kOutWarpBytes = OUT_TILES * 32 * 64 * 2;
+  static constexpr int kOutWarpBytes = OUT_TILES * 32 * 64 * 2;      // 0: the epilogue stores straight from registers
   static constexpr int kOutBytes = kEpiWarps * kOutWarpBytes;
   static constexpr int kPairBytes = 2 * BM * 8;                       // [half][row] float2
-  static constexpr int kStatsBytes = CLUSTER ? 2 * kMaxCluster * BM * 8 : 0;
+  static constexpr int kStatsSets = PIPE ? 4 : 2;                      // PIPE: two per epilogue group
+  static constexpr int kStatsBytes = CLUSTER ? kStatsSets * kMaxCluster * BM * 8 : 0;
   static constexpr int kOffOut = STAGES * kStageBytes;
   static constexpr int kOffPair = kOffOut + kOutBytes;
   static constexpr int kOffStats = kOffPair + kPairBytes;
   static constexpr int kOffBars = kOffStats + kStatsBytes;
-  static constexpr int kNumBars = 2 * STAGES + 4 + 2;
+  static constexpr int kNumBars = 2 * STAGES + 4 + 4 + 1;
   static constexpr int kOffTmemSlot = kOffBars + kNumBars * 8;
   static constexpr int kTotal = kOffTmemSlot + 16;
   static constexpr int kDynamic = kTotal;
@@ -86,11 +87,16 @@ __device__ __forceinline__ void stamp(long long *timeline, int slot) {
   if (timeline) timeline[static_cast<size_t>(blockIdx.x) * 16 + slot] = static_cast<long long>(globaltimer_ns());
 }
 
-template <int BN, int STAGES, bool CLUSTER, int OUT_TILES>
+// Second stamp layout (timeline_mode 1): four points of the first four tiles one thread sees.
+__device__ __forceinline__ void stamp_tile(const TcParams &p, int seq, int k) {
+  if (p.timeline && p.timeline_mode == 1 && seq < 4) stamp(p.timeline, seq * 4 + k);
+}
+
+template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool PIPE>
 __global__ void __launch_bounds__(kThreads, 1)
 fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmO, const TcParams p) {
-  using L = SmemLayout<BN, STAGES, CLUSTER, OUT_TILES>;
+  using L = SmemLayout<BN, STAGES, CLUSTER, OUT_TILES, PIPE>;
   constexpr int HC = L::kHalfCols;      // columns per epilogue thread
   constexpr int NCH = HC / 32;          // 32-column chunks per epilogue thread
   // The 128-byte swizzle needs the stage buffers on 1024-byte boundaries.  There is no
@@ -105,6 +111,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   uint64_t *accum_full = bars + 2 * STAGES;
   uint64_t *accum_empty = bars + 2 * STAGES + 2;
   uint64_t *stats_bar = bars + 2 * STAGES + 4;
+  uint64_t *stagger_bar = bars + 2 * STAGES + 8;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + L::kOffTmemSlot);
   float2 *pair = reinterpret_cast<float2 *>(smem + L::kOffPair);    // [2][BM]
   float2 *stats = reinterpret_cast<float2 *>(smem + L::kOffStats);  // [2][kMaxCluster][BM]
@@ -118,9 +125,10 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&accum_full[i], 1);
-      mbar_init(&accum_empty[i], kEpiThreads);
-      mbar_init(&stats_bar[i], 1);
+      mbar_init(&accum_empty[i], PIPE ? kEpiThreads / 2 : kEpiThreads);
     }
+    for (int i = 0; i < 4; ++i) mbar_init(&stats_bar[i], 1);
+    mbar_init(stagger_bar, kEpiThreads / 2);
     mbar_fence_init();
     tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); tma_prefetch_desc(&tmO);
   }
@@ -135,7 +143,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   // to finish, and let the next one start its own set-up as our CTAs retire.
   grid_dependency_wait();
   grid_launch_dependents();
-  if (threadIdx.x == 64) stamp(p.timeline, 0);
+  if (threadIdx.x == 64 && p.timeline_mode == 0) stamp(p.timeline, 0);
 
   // ---- work distribution --------------------------------------------------
   int first, stride;
@@ -176,7 +184,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
           for (int j = 0; j < BN / 64; ++j)
             tma_load_3d(sb + j * (BK * 128), &tmB, &full[s], nb * BN + j * 64, kb * BK, p.b_batched ? b : 0);
-          if (n == 0) stamp(p.timeline, 6);
+          if (n == 0 && p.timeline_mode == 0) stamp(p.timeline, 6);
         }
         __syncwarp();
       }
@@ -198,7 +206,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         if (!mbar_wait(&full[s], ph)) { record_failure(p.status, WTC_DEV_TIMEOUT_FULL); ok = false; break; }
         tc_fence_after_sync();
         if (lane == 0) {
-          if (n == 0) stamp(p.timeline, 7);
+          if (n == 0 && p.timeline_mode == 0) stamp(p.timeline, 7);
           const uint32_t sa = smem_u32(smem + s * L::kStageBytes);
           const uint32_t sb = sa + L::kABytes;
 #pragma unroll
@@ -211,9 +219,246 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
         __syncwarp();
       }
-      if (ok && lane == 0) { umma_commit(&accum_full[ab]); if (it == 0) stamp(p.timeline, 8); }
+      if (ok && lane == 0) { umma_commit(&accum_full[ab]); if (it == 0 && p.timeline_mode == 0) stamp(p.timeline, 8); }
       __syncwarp();
     }
+  } else if (PIPE) {
+    // ======================= softmax epilogue, tile-pipelined ==============
+    // Two groups of four warps take alternate tiles (group = accumulator buffer), so
+    // while one group is in its MUFU-bound exp phase the other loads, scales, packs and
+    // stores: the SM's special-function unit stays busy across tiles.  A thread owns a
+    // whole row of the tile and walks it in two halves of HC columns: the first half's
+    // exp values (taken against that half's own maximum) are parked in TMEM over the
+    // logits they came from, the second half's stay in registers.
+    const int q = warp & 3;
+    const int grp = (warp - 2) >> 2;
+    const int row_in_tile = q * 32 + lane;
+    const bool lead = lane == 0 && q == 2;       // one thread per group posts expect_tx (warps 2 and 6)
+    const bool stamper = threadIdx.x == 64;
+    uint8_t *stg = smem + L::kOffOut + (warp - 2) * L::kOutWarpBytes;
+    const float c2 = p.c2;
+    const bool pos = c2 >= 0.f;
+    uint32_t r[NCH][32];
+
+    // extreme of r over the first `valid` columns (log2 domain), four chains
+    auto half_max = [&](int valid) -> float {
+      float m;
+      if (valid == HC) {
+        float m0 = __uint_as_float(r[0][0]), m1 = __uint_as_float(r[0][1]), m2 = __uint_as_float(r[0][2]), m3 = __uint_as_float(r[0][3]);
+#pragma unroll
+        for (int c = 0; c < NCH; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            if (pos) {
+              m0 = fmaxf(m0, __uint_as_float(r[c][i]));     m1 = fmaxf(m1, __uint_as_float(r[c][i + 1]));
+              m2 = fmaxf(m2, __uint_as_float(r[c][i + 2])); m3 = fmaxf(m3, __uint_as_float(r[c][i + 3]));
+            } else {
+              m0 = fminf(m0, __uint_as_float(r[c][i]));     m1 = fminf(m1, __uint_as_float(r[c][i + 1]));
+              m2 = fminf(m2, __uint_as_float(r[c][i + 2])); m3 = fminf(m3, __uint_as_float(r[c][i + 3]));
+            }
+          }
+        m = pos ? fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) : fminf(fminf(m0, m1), fminf(m2, m3));
+      } else if (valid > 0) {
+        m = __uint_as_float(r[0][0]);
+#pragma unroll
+        for (int c = 0; c < NCH; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i < valid) m = pos ? fmaxf(m, __uint_as_float(r[c][i])) : fminf(m, __uint_as_float(r[c][i]));
+      } else {
+        return -INFINITY;
+      }
+      return m * c2;
+    };
+    // r <- 2^(r*c2 - m) (0 beyond `valid`), returns the sum
+    auto half_exp = [&](int valid, float m) -> float {
+      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+      if (valid == HC) {
+#pragma unroll
+        for (int c = 0; c < NCH; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const float e0 = ex2_approx(fmaf(__uint_as_float(r[c][i]), c2, -m));
+            const float e1 = ex2_approx(fmaf(__uint_as_float(r[c][i + 1]), c2, -m));
+            const float e2 = ex2_approx(fmaf(__uint_as_float(r[c][i + 2]), c2, -m));
+            const float e3 = ex2_approx(fmaf(__uint_as_float(r[c][i + 3]), c2, -m));
+            s0 += e0; s1 += e1; s2 += e2; s3 += e3;
+            r[c][i] = __float_as_uint(e0); r[c][i + 1] = __float_as_uint(e1);
+            r[c][i + 2] = __float_as_uint(e2); r[c][i + 3] = __float_as_uint(e3);
+          }
+      } else {
+#pragma unroll
+        for (int c = 0; c < NCH; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float e = 0.f;
+            if (c * 32 + i < valid) e = ex2_approx(fmaf(__uint_as_float(r[c][i]), c2, -m));
+            s0 += e;
+            r[c][i] = __float_as_uint(e);
+          }
+      }
+      return (s0 + s1) + (s2 + s3);
+    };
+    auto round_f16 = [&]() {
+      if (p.round_logits_f16) {
+#pragma unroll
+        for (int c = 0; c < NCH; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[c][i] = __float_as_uint(__half2float(__float2half_rn(__uint_as_float(r[c][i]))));
+      }
+    };
+
+    // The two groups must not march in step (both in the exp phase, then both storing): the
+    // second group starts its first tile only when the first group has finished its first
+    // exp phase, and the offset then persists.
+    if (grp == 1 && first + stride < p.num_items && p.stagger) {
+      if (!mbar_wait(stagger_bar, 0)) record_failure(p.status, WTC_DEV_TIMEOUT_ACCUM);
+    }
+    for (int it = grp; first + it * stride < p.num_items; it += 2) {
+      const int w = first + it * stride;
+      int b, rb, nb; decode(w, b, rb, nb);
+      const int ab = grp;                                  // it & 1
+      const uint32_t tile_phase = (it >> 1) & 1;           // accum_full / accum_empty phase of this buffer
+      const int sset = grp * 2 + ((it >> 1) & 1);          // statistics set: two per group, alternating
+      const uint32_t stats_phase = (it >> 2) & 1;
+      if (CLUSTER && lead) mbar_expect_tx(&stats_bar[sset], cluster_n * BM * 8);
+      if (!mbar_wait(&accum_full[ab], tile_phase)) { record_failure(p.status, WTC_DEV_TIMEOUT_ACCUM); break; }
+      tc_fence_after_sync();
+      if (stamper && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 1);
+      if (stamper) stamp_tile(p, it >> 1, 0);
+      const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ab * BN;
+      const int col0 = nb * BN;
+      const int valid0 = max(0, min(HC, p.N - col0));
+      const int valid1 = max(0, min(HC, p.N - col0 - HC));
+      const int row0 = rb * BM + q * 32;
+      const bool rows_live = row0 < p.M;
+
+      // ---- first half: exp against its own maximum, parked in TMEM ----
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        if (c * 32 < valid0) tmem_ld_32x32b_x32(tbase + c * 32, r[c]);
+        else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[c][i] = 0u;
+        }
+      }
+      tmem_ld_wait();
+      round_f16();
+      const float m0 = half_max(valid0);
+      const float l0 = half_exp(valid0, m0);
+#pragma unroll
+      for (int c = 0; c < NCH; ++c)
+        if (c * 32 < valid0) tmem_st_32x32b_x32(tbase + c * 32, r[c]);
+      // ---- second half: stays in registers ----
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        if (c * 32 < valid1) tmem_ld_32x32b_x32(tbase + HC + c * 32, r[c]);
+        else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[c][i] = 0u;
+        }
+      }
+      tmem_ld_wait();
+      round_f16();
+      const float m1 = half_max(valid1);
+      const float l1 = half_exp(valid1, m1);
+      if (it == 0) mbar_arrive(stagger_bar);               // group 0 only: lets group 1 start
+      if (stamper && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 2);
+      if (stamper) stamp_tile(p, it >> 1, 1);
+      const float lm = fmaxf(m0, m1);
+      float f0, f1;
+      if (CLUSTER) {
+        const float ll = l0 * ex2_approx(m0 - lm) + (valid1 > 0 ? l1 * ex2_approx(m1 - lm) : 0.f);
+        const uint32_t slot = smem_u32(&stats[(sset * kMaxCluster + cta_rank) * BM + row_in_tile]);
+        const uint32_t bar = smem_u32(&stats_bar[sset]);
+        for (uint32_t peer = 0; peer < cluster_n; ++peer)
+          st_async_f32x2(map_to_cta(slot, peer), lm, ll, map_to_cta(bar, peer));
+        if (!mbar_wait_cluster(&stats_bar[sset], stats_phase)) { record_failure(p.status, WTC_DEV_TIMEOUT_STATS); break; }
+        if (stamper && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 3);
+        if (stamper) stamp_tile(p, it >> 1, 2);
+        float gm = -INFINITY;
+        for (uint32_t peer = 0; peer < cluster_n; ++peer)
+          gm = fmaxf(gm, stats[(sset * kMaxCluster + peer) * BM + row_in_tile].x);
+        float gl = 0.f;
+        for (uint32_t peer = 0; peer < cluster_n; ++peer) {
+          const float2 st = stats[(sset * kMaxCluster + peer) * BM + row_in_tile];
+          gl += st.y * ex2_approx(st.x - gm);
+        }
+          const float inv = 1.0f / gl;
+        f0 = ex2_approx(m0 - gm) * inv;
+        f1 = ex2_approx(m1 - gm) * inv;
+      } else {
+        f0 = ex2_approx(m0 - lm);
+        f1 = ex2_approx(m1 - lm);
+      }
+
+      float sum_r = 0.f;
+      // p = e * f -> f16 -> global memory (straight from registers, or staged for TMA)
+      const int row = rb * BM + row_in_tile;
+      __half *orow = static_cast<__half *>(p.out) + static_cast<long long>(b) * p.o_batch_stride + static_cast<long long>(row) * p.ldo;
+      auto write_half = [&](int valid, float f, int col_base) {
+        if (OUT_TILES == 0) {
+#pragma unroll
+          for (int c = 0; c < NCH; ++c) {
+            if (c * 32 < valid) {
+              uint32_t h[16];
+#pragma unroll
+              for (int i = 0; i < 32; i += 2) {
+                const __half2 hh = __floats2half2_rn(__uint_as_float(r[c][i]) * f, __uint_as_float(r[c][i + 1]) * f);
+                if (!CLUSTER) { const float2 back = __half22float2(hh); sum_r += back.x + back.y; }
+                h[i >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
+              }
+              if (row < p.M && !(p.debug_flags & 1)) st_global_row32(orow + col_base + c * 32, h, p.out_align32, valid - c * 32);
+              if ((p.debug_flags & 1) && h[0] == 0x12345678u && row < p.M) st_global_row32(orow + col_base + c * 32, h, p.out_align32, valid - c * 32);
+            }
+          }
+        } else {
+#pragma unroll
+        for (int g = 0; g < NCH / 2; ++g) {
+          if (g * 64 < valid) {
+            if (lane == 0) tma_store_wait_read();
+            __syncwarp();
+#pragma unroll
+            for (int hc = 0; hc < 2; ++hc) {
+              const int c = g * 2 + hc;
+              uint32_t h[16];
+#pragma unroll
+              for (int i = 0; i < 32; i += 2) {
+                const __half2 hh = __floats2half2_rn(__uint_as_float(r[c][i]) * f, __uint_as_float(r[c][i + 1]) * f);
+                if (!CLUSTER) { const float2 back = __half22float2(hh); sum_r += back.x + back.y; }
+                h[i >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
+              }
+              stage_row_chunk(stg, lane, hc, h);
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              if (rows_live) tma_store_3d(&tmO, stg, col_base + g * 64, row0, b);
+              tma_store_commit();
+            }
+          }
+        }
+        }
+      };
+      write_half(valid1, f1, col0 + HC);
+      // ---- fetch the parked first half, hand the accumulator back, write it out ----
+      tmem_st_wait();
+#pragma unroll
+      for (int c = 0; c < NCH; ++c)
+        if (c * 32 < valid0) tmem_ld_32x32b_x32(tbase + c * 32, r[c]);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      mbar_arrive(&accum_empty[ab]);
+      write_half(valid0, f0, col0);
+      if (!CLUSTER) {
+        const int row = rb * BM + row_in_tile;
+        if (row < p.M) p.tile_stats[(static_cast<int64_t>(b) * p.M + row) * p.num_nb + nb] = make_float2(lm, sum_r);
+      }
+      if (stamper && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 4);
+      if (stamper) stamp_tile(p, it >> 1, 3);
+    }
+    if (lane == 0) tma_store_wait_all();
+    if (stamper && p.timeline_mode == 0) stamp(p.timeline, 5);
   } else {
     // ======================= softmax epilogue ==============================
     const int q = warp & 3;                      // TMEM lane quarter this warp may read
@@ -235,7 +480,8 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       if (CLUSTER && lead) mbar_expect_tx(&stats_bar[par], cluster_n * BM * 8);
       if (!mbar_wait(&accum_full[ab], tile_phase)) { record_failure(p.status, WTC_DEV_TIMEOUT_ACCUM); break; }
       tc_fence_after_sync();
-      if (lead && it == 0) stamp(p.timeline, 1);
+      if (lead && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 1);
+      if (lead) stamp_tile(p, it, 0);
       const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ab * BN + half * HC;
       const int col0 = nb * BN + half * HC;               // first matrix column of this thread
       const int valid = max(0, min(HC, p.N - col0));      // my columns that exist
@@ -246,12 +492,17 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       //      and the accumulator buffer is handed back to the MMA warp straight away ----
       uint32_t r[NCH][32];
 #pragma unroll
-      for (int c = 0; c < NCH; ++c)
+      for (int c = 0; c < NCH; ++c) {
         if (c * 32 < valid) tmem_ld_32x32b_x32(tbase + c * 32, r[c]);
+        else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[c][i] = 0u;
+        }
+      }
       tmem_ld_wait();
       tc_fence_before_sync();
       mbar_arrive(&accum_empty[ab]);
-      if (lead && it == 0) stamp(p.timeline, 14);
+      if (lead && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 14);
       if (p.round_logits_f16) {
 #pragma unroll
         for (int c = 0; c < NCH; ++c)
@@ -296,7 +547,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         m_half = -INFINITY;
       }
 
-      if (lead && it == 0) stamp(p.timeline, 15);
+      if (lead && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 15);
       // ---- e = 2^(v - m_half) in place, row sum ----
       float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
       if (valid == HC) {
@@ -324,7 +575,8 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           }
       }
       float sum = (s0 + s1) + (s2 + s3);
-      if (lead && it == 0) stamp(p.timeline, 2);
+      if (lead && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 2);
+      if (lead) stamp_tile(p, it, 1);
 
       // ---- the two halves of a row meet through shared memory ----
       *mine = make_float2(m_half, sum);
@@ -344,7 +596,8 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             st_async_f32x2(map_to_cta(slot, peer), lm, ll, map_to_cta(bar, peer));
         }
         if (!mbar_wait_cluster(&stats_bar[par], tile_phase)) { record_failure(p.status, WTC_DEV_TIMEOUT_STATS); break; }
-        if (lead && it == 0) stamp(p.timeline, 3);
+        if (lead && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 3);
+        if (lead) stamp_tile(p, it, 2);
         float gm = -INFINITY;
         for (uint32_t peer = 0; peer < cluster_n; ++peer)
           gm = fmaxf(gm, stats[(par * kMaxCluster + peer) * BM + row_in_tile].x);
@@ -358,19 +611,15 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         f = ex2_approx(m_half - lm);               // tiled: values relative to the tile max, not normalised
       }
 
-      // ---- p = e * f -> f16 -> swizzled staging -> TMA store, 64 columns at a time ----
+      // ---- p = e * f -> f16 -> global memory ----
       float sum_r = 0.f;                           // tiled: sum of what is actually stored
+      if (OUT_TILES == 0) {
+        // straight from registers: each thread owns 256 contiguous bytes of its row
+        const int row = rb * BM + row_in_tile;
+        __half *orow = static_cast<__half *>(p.out) + static_cast<long long>(b) * p.o_batch_stride + static_cast<long long>(row) * p.ldo + col0;
 #pragma unroll
-      for (int g = 0; g < NCH / 2; ++g) {
-        if (g * 64 < valid) {
-          uint8_t *tile = stg + (OUT_TILES == 2 ? (gcount & 1) * 4096 : 0);   // tiles alternate per committed group
-          // the store that last used this staging tile must have read it
-          if (lane == 0) { if (OUT_TILES == 2) tma_store_wait_read1(); else tma_store_wait_read(); }
-          __syncwarp();
-          if (lead && it == 0 && g == 0) stamp(p.timeline, 9);
-#pragma unroll
-          for (int hc = 0; hc < 2; ++hc) {
-            const int c = g * 2 + hc;
+        for (int c = 0; c < NCH; ++c) {
+          if (c * 32 < valid) {
             uint32_t h[16];
 #pragma unroll
             for (int i = 0; i < 32; i += 2) {
@@ -378,18 +627,39 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
               if (!CLUSTER) { const float2 back = __half22float2(hh); sum_r += back.x + back.y; }
               h[i >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
             }
-            stage_row_chunk(tile, lane, hc, h);
+            if (row < p.M && !(p.debug_flags & 1)) st_global_row32(orow + c * 32, h, p.out_align32, valid - c * 32);
+            if ((p.debug_flags & 1) && h[0] == 0x12345678u && row < p.M) st_global_row32(orow + c * 32, h, p.out_align32, valid - c * 32);
           }
-          if (lead && it == 0 && g == 0) stamp(p.timeline, 10);
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lead && it == 0 && g == 0) stamp(p.timeline, 11);
-          if (lane == 0) {
-            if (rows_live) tma_store_3d(&tmO, tile, col0 + g * 64, row0, b);
-            tma_store_commit();
+        }
+      } else {
+        // 128-byte-swizzled staging tiles in shared memory, written out by TMA, 64 columns at a time
+#pragma unroll
+        for (int g = 0; g < NCH / 2; ++g) {
+          if (g * 64 < valid) {
+            uint8_t *tile = stg + (OUT_TILES == 2 ? (gcount & 1) * 4096 : 0);   // tiles alternate per committed group
+            // the store that last used this staging tile must have read it
+            if (lane == 0) { if (OUT_TILES == 2) tma_store_wait_read1(); else tma_store_wait_read(); }
+            __syncwarp();
+#pragma unroll
+            for (int hc = 0; hc < 2; ++hc) {
+              const int c = g * 2 + hc;
+              uint32_t h[16];
+#pragma unroll
+              for (int i = 0; i < 32; i += 2) {
+                const __half2 hh = __floats2half2_rn(__uint_as_float(r[c][i]) * f, __uint_as_float(r[c][i + 1]) * f);
+                if (!CLUSTER) { const float2 back = __half22float2(hh); sum_r += back.x + back.y; }
+                h[i >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
+              }
+              stage_row_chunk(tile, lane, hc, h);
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              if (rows_live) tma_store_3d(&tmO, tile, col0 + g * 64, row0, b);
+              tma_store_commit();
+            }
+            ++gcount;
           }
-          if (lead && it == 0 && g == 0) stamp(p.timeline, 12);
-          ++gcount;
         }
       }
       if (!CLUSTER) {
@@ -401,10 +671,11 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           p.tile_stats[(static_cast<int64_t>(b) * p.M + row) * p.num_nb + nb] = make_float2(lm, sum_r + other->y);
         named_bar_sync(1 + q, 64);
       }
-      if (lead && it == 0) stamp(p.timeline, 4);
+      if (lead && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 4);
+      if (lead) stamp_tile(p, it, 3);
     }
     if (lane == 0) tma_store_wait_all();
-    if (lead) stamp(p.timeline, 5);
+    if (lead && p.timeline_mode == 0) stamp(p.timeline, 5);
   }
 
   // ---- teardown: nothing in flight, peers done with our shared memory, TMEM freed ----
@@ -418,11 +689,11 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
 }
 
-template <int BN, int STAGES, bool CLUSTER, int OUT_TILES>
+template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool PIPE>
 cudaError_t launch_impl(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO, const TcParams &p,
                         int cluster_n, int num_sms, cudaStream_t s, TcLaunchInfo *info) {
-  using L = SmemLayout<BN, STAGES, CLUSTER, OUT_TILES>;
-  auto kern = fused_tc_kernel<BN, STAGES, CLUSTER, OUT_TILES>;
+  using L = SmemLayout<BN, STAGES, CLUSTER, OUT_TILES, PIPE>;
+  auto kern = fused_tc_kernel<BN, STAGES, CLUSTER, OUT_TILES, PIPE>;
   static bool attr_set = false;   // per template instance
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
@@ -478,12 +749,27 @@ cudaError_t launch_fused_cluster(const CUtensorMap &tmA, const CUtensorMap &tmB,
                                  const TcParams &p, int cluster_n, int num_sms, cudaStream_t s,
                                  TcLaunchInfo *info) {
   if (cluster_n < 1 || cluster_n > kMaxCluster) return cudaErrorInvalidValue;
-  return launch_impl<kTcBlockN, 3, true, 2>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+  // With at least two row blocks per resident cluster the tile-pipelined epilogue keeps the
+  // special-function unit busy across tiles; with one tile per CTA all eight epilogue warps
+  // share that tile instead.
+  const bool pipe = p.epilogue_mode == 2 || (p.epilogue_mode == 0 && p.num_items >= 2 * (num_sms / cluster_n));
+  if (p.store_mode == 1) {   // staged TMA stores: three pipeline stages leave room for the staging tiles
+    if (pipe) return launch_impl<kTcBlockN, 3, true, 1, true>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+    return launch_impl<kTcBlockN, 3, true, 2, false>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+  }
+  if (pipe) return launch_impl<kTcBlockN, 4, true, 0, true>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+  return launch_impl<kTcBlockN, 4, true, 0, false>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
 }
 
 cudaError_t launch_tiled_partial(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO,
                                  const TcParams &p, int num_sms, cudaStream_t s, TcLaunchInfo *info) {
-  return launch_impl<kTcBlockN, 4, false, 1>(tmA, tmB, tmO, p, 1, num_sms, s, info);
+  const bool pipe = p.epilogue_mode == 2 || (p.epilogue_mode == 0 && p.num_items >= 2 * num_sms);
+  if (p.store_mode == 1) {
+    if (pipe) return launch_impl<kTcBlockN, 4, false, 1, true>(tmA, tmB, tmO, p, 1, num_sms, s, info);
+    return launch_impl<kTcBlockN, 4, false, 1, false>(tmA, tmB, tmO, p, 1, num_sms, s, info);
+  }
+  if (pipe) return launch_impl<kTcBlockN, 4, false, 0, true>(tmA, tmB, tmO, p, 1, num_sms, s, info);
+  return launch_impl<kTcBlockN, 4, false, 0, false>(tmA, tmB, tmO, p, 1, num_sms, s, info);
 }
 
 } // namespace wtc

@@ -23,11 +23,19 @@ struct TcParams {
   int num_items;   // work items: cluster mode batch*num_rb, tiled mode batch*num_rb*num_nb
   int b_batched;   // B has its own batch dimension
   int group_rb;    // tiled mode: row blocks per rasterisation group
+  void *out;       // output base, row stride and batch stride (elements) for the direct-store epilogue
+  long long ldo, o_batch_stride;
+  int out_align32; // every output row starts on a 32-byte boundary
+  int store_mode;  // 0 direct register->global stores, 1 swizzled shared staging + TMA stores
+  int debug_flags; // bring-up experiments: 1 = drop the epilogue stores
+  int stagger;     // tile-pipelined epilogue: offset the two warp groups by one phase
+  int epilogue_mode;  // 0 choose by tiles per CTA, 1 all warps share a tile, 2 warp groups alternate tiles
   int use_pdl;     // launch with programmatic stream serialisation
   int round_logits_f16;  // chain spelled with an f16 matmul result: round s to f16 before the softmax
   float c2;        // scale * log2(e)
   float2 *tile_stats;    // tiled mode: [batch*M][num_nb] (max in log2 domain, sum of 2^(v-max))
   int *status;     // device status word (0 = ok)
+  int timeline_mode;     // 0: phases of the first tile; 1: four points of the first four tiles
   long long *timeline;   // optional [grid][16] nanosecond stamps of the first tile (bring-up / profiling)
   UmmaGeom geom;
 };

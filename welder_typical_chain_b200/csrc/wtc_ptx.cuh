@@ -290,6 +290,25 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
   return *reinterpret_cast<uint32_t *>(&h);
 }
 
+// ---- direct global stores -------------------------------------------------------
+// One thread writes 32 consecutive f16 (64 bytes) of its own row.  With 32-byte aligned
+// rows each instruction fills a whole 32-byte sector (256-bit stores); otherwise 128-bit.
+// `lim` = how many of the 32 columns exist (a multiple of 8).
+__device__ __forceinline__ void st_global_row32(void *dst, const uint32_t (&h)[16], bool align32, int lim) {
+  if (lim >= 32 && align32) {
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"l"(dst), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]), "r"(h[4]), "r"(h[5]), "r"(h[6]), "r"(h[7]) : "memory");
+    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"l"(static_cast<char *>(dst) + 32), "r"(h[8]), "r"(h[9]), "r"(h[10]), "r"(h[11]), "r"(h[12]), "r"(h[13]), "r"(h[14]), "r"(h[15]) : "memory");
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (j * 8 < lim)
+        asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};"
+                     ::"l"(static_cast<char *>(dst) + j * 16), "r"(h[4 * j]), "r"(h[4 * j + 1]), "r"(h[4 * j + 2]), "r"(h[4 * j + 3]) : "memory");
+  }
+}
+
 // ---- named barrier among a subset of warps ------------------------------------
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
