@@ -45,10 +45,10 @@ constexpr int kMaxCluster = 8;
 
 // OUT_TILES: 32-row x 64-column f16 staging tiles per epilogue warp (2 = the warp's two
 // column groups never wait for each other's TMA read; 1 = smaller, leaves room for a stage).
-template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool PIPE>
+template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool PIPE, bool PAIR>
 struct SmemLayout {
   static constexpr int kABytes = BM * BK * 2;
-  static constexpr int kBBytes = BK * BN * 2;
+  static constexpr int kBBytes = BK * BN * 2 / (PAIR ? 2 : 1);     // a CTA pair splits B's columns between its two CTAs
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kHalfCols = BN / 2;                            // columns per epilogue thread
   static constexpr int kOutWarpBytes = OUT_TILES * 32 * 64 * 2;      // 0: the epilogue stores straight from registers
@@ -92,11 +92,11 @@ __device__ __forceinline__ void stamp_tile(const TcParams &p, int seq, int k) {
   if (p.timeline && p.timeline_mode == 1 && seq < 4) stamp(p.timeline, seq * 4 + k);
 }
 
-template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool PIPE>
+template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool PIPE, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmO, const TcParams p) {
-  using L = SmemLayout<BN, STAGES, CLUSTER, OUT_TILES, PIPE>;
+  using L = SmemLayout<BN, STAGES, CLUSTER, OUT_TILES, PIPE, PAIR>;
   constexpr int HC = L::kHalfCols;      // columns per epilogue thread
   constexpr int NCH = HC / 32;          // 32-column chunks per epilogue thread
   // The 128-byte swizzle needs the stage buffers on 1024-byte boundaries.  There is no
@@ -118,26 +118,38 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const uint32_t cta_rank = CLUSTER ? cluster_ctarank() : 0u;
-  const uint32_t cluster_n = CLUSTER ? cluster_nctarank() : 1u;
+  // Cluster geometry.  PAIR: ranks 2j and 2j+1 form one tcgen05 CTA pair (256 rows x BN
+  // columns; the even CTA issues the MMAs); j is the column block.  The CTAs that swap row
+  // statistics are the ones with the same rows: same parity when paired.
+  constexpr bool CLUSTERED = CLUSTER || PAIR;
+  const uint32_t cta_rank = CLUSTERED ? cluster_ctarank() : 0u;
+  const uint32_t cluster_size = CLUSTERED ? cluster_nctarank() : 1u;
+  const uint32_t pair_rank = PAIR ? (cta_rank & 1u) : 0u;
+  const uint32_t leader_rank = PAIR ? (cta_rank & ~1u) : cta_rank;
+  const bool is_leader = pair_rank == 0;
+  const uint32_t col_rank = PAIR ? (cta_rank >> 1) : cta_rank;               // my column block inside the cluster
+  const uint32_t cluster_n = CLUSTER ? (PAIR ? cluster_size / 2 : cluster_size) : 1u;   // CTAs that share my rows
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&accum_full[i], 1);
-      mbar_init(&accum_empty[i], PIPE ? kEpiThreads / 2 : kEpiThreads);
+      mbar_init(&accum_empty[i], (PIPE ? kEpiThreads / 2 : kEpiThreads) * (PAIR ? 2 : 1));
     }
     for (int i = 0; i < 4; ++i) mbar_init(&stats_bar[i], 1);
     mbar_init(stagger_bar, kEpiThreads / 2);
     mbar_fence_init();
     tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); tma_prefetch_desc(&tmO);
   }
-  if (warp == 1) { tmem_alloc(tmem_slot, 2 * BN); tmem_relinquish(); }
+  if (warp == 1) {
+    if (PAIR) { tmem_alloc_pair(tmem_slot, 2 * BN); tmem_relinquish_pair(); }
+    else { tmem_alloc(tmem_slot, 2 * BN); tmem_relinquish(); }
+  }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  if (CLUSTER) cluster_sync_all();   // every peer's barriers exist before anyone signals them
+  if (CLUSTERED) cluster_sync_all();   // every peer's barriers exist before anyone signals them
   // Programmatic dependent launch: everything above overlapped the tail of the previous
   // kernel on the stream; from here on global memory is touched, so wait for that kernel
   // to finish, and let the next one start its own set-up as our CTAs retire.
@@ -147,24 +159,37 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
   // ---- work distribution --------------------------------------------------
   int first, stride;
-  if (CLUSTER) { first = blockIdx.x / cluster_n; stride = gridDim.x / cluster_n; }
+  if (CLUSTERED) { first = blockIdx.x / cluster_size; stride = gridDim.x / cluster_size; }
   else { first = blockIdx.x; stride = gridDim.x; }
 
+  // Work items count "row units": one 128-row block, or one 256-row pair of blocks.
   auto decode = [&](int w, int &b, int &rb, int &nb) {
-    if (CLUSTER) { b = w / p.num_rb; rb = w - b * p.num_rb; nb = cta_rank; return; }
-    const int per_batch = p.num_rb * p.num_nb;
-    b = w / per_batch;
-    int t = w - b * per_batch;
-    // groups of `group_rb` row blocks; inside a group the column block is the
-    // slow index, so concurrently running CTAs share B column blocks and the
-    // group's A rows stay in L2.
-    const int per_group = p.group_rb * p.num_nb;
-    const int g = t / per_group;
-    t -= g * per_group;
-    const int rows_here = min(p.group_rb, p.num_rb - g * p.group_rb);
-    nb = t / rows_here;
-    rb = g * p.group_rb + (t - nb * rows_here);
+    int ru;
+    if (CLUSTER) { b = w / p.num_ru; ru = w - b * p.num_ru; nb = col_rank; }
+    else {
+      const int per_batch = p.num_ru * p.num_nb;
+      b = w / per_batch;
+      int t = w - b * per_batch;
+      // groups of `group_rb` row units; inside a group the column block is the slow
+      // index, so concurrently running CTAs share B column blocks and the group's A rows
+      // stay in L2.
+      const int per_group = p.group_rb * p.num_nb;
+      const int g = t / per_group;
+      t -= g * per_group;
+      const int rows_here = min(p.group_rb, p.num_ru - g * p.group_rb);
+      nb = t / rows_here;
+      ru = g * p.group_rb + (t - nb * rows_here);
+    }
+    rb = PAIR ? ru * 2 + static_cast<int>(pair_rank) : ru;
   };
+
+  // hands accumulator buffer `ab` back to the MMA warp (of the pair's even CTA)
+  auto release_accumulator = [&](int ab) {
+    if (PAIR) mbar_arrive_remote_release(map_to_cta(smem_u32(&accum_empty[ab]), leader_rank));
+    else mbar_arrive(&accum_empty[ab]);
+  };
+  // cluster rank of the j-th CTA that holds the same rows as this one
+  auto row_peer = [&](uint32_t j) -> uint32_t { return PAIR ? 2 * j + pair_rank : j; };
 
   if (warp == 0) {
     // ======================= TMA producer ==================================
@@ -179,23 +204,34 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         if (lane == 0) {
           uint8_t *sa = smem + s * L::kStageBytes;
           uint8_t *sb = sa + L::kABytes;
-          mbar_expect_tx(&full[s], L::kStageBytes);
-          tma_load_3d(sa, &tmA, &full[s], kb * BK, rb * BM, b);
+          if (PAIR) {
+            // both CTAs of the pair fill their own stage; all bytes are counted on the even CTA's barrier
+            if (is_leader) mbar_expect_tx(&full[s], 2 * L::kStageBytes);
+            tma_load_3d_pair(sa, &tmA, &full[s], kb * BK, rb * BM, b);
 #pragma unroll
-          for (int j = 0; j < BN / 64; ++j)
-            tma_load_3d(sb + j * (BK * 128), &tmB, &full[s], nb * BN + j * 64, kb * BK, p.b_batched ? b : 0);
+            for (int j = 0; j < BN / 128; ++j)
+              tma_load_3d_pair(sb + j * (BK * 128), &tmB, &full[s], nb * BN + static_cast<int>(pair_rank) * (BN / 2) + j * 64, kb * BK,
+                               p.b_batched ? b : 0);
+          } else {
+            mbar_expect_tx(&full[s], L::kStageBytes);
+            tma_load_3d(sa, &tmA, &full[s], kb * BK, rb * BM, b);
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_3d(sb + j * (BK * 128), &tmB, &full[s], nb * BN + j * 64, kb * BK, p.b_batched ? b : 0);
+          }
           if (n == 0 && p.timeline_mode == 0) stamp(p.timeline, 6);
         }
         __syncwarp();
       }
     }
   } else if (warp == 1) {
-    // ======================= MMA issuer ====================================
-    constexpr uint32_t idesc = umma_idesc_f16_f32(BM, BN, /*a_mn_major=*/0, /*b_mn_major=*/1);
+    // ======================= MMA issuer (the even CTA of a pair only) =======
+    constexpr uint32_t idesc = umma_idesc_f16_f32(PAIR ? 2 * BM : BM, BN, /*a_mn_major=*/0, /*b_mn_major=*/1);
+    const uint16_t pair_mask = static_cast<uint16_t>(3u << leader_rank);
     uint32_t n = 0;
     int it = 0;
     bool ok = true;
-    for (int w = first; w < p.num_items && ok; w += stride, ++it) {
+    for (int w = first; w < p.num_items && ok && is_leader; w += stride, ++it) {
       const int ab = it & 1;
       if (!mbar_wait(&accum_empty[ab], ((it >> 1) & 1) ^ 1)) { record_failure(p.status, WTC_DEV_TIMEOUT_TMEM); ok = false; break; }
       tc_fence_after_sync();
@@ -213,13 +249,20 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           for (int k = 0; k < BK / 16; ++k) {
             const uint64_t da = umma_smem_desc_sw128(sa + k * p.geom.a_kstep, p.geom.a_lbo, p.geom.a_sbo);
             const uint64_t db = umma_smem_desc_sw128(sb + k * p.geom.b_kstep, p.geom.b_lbo, p.geom.b_sbo);
-            umma_f16_ss(d_tmem, da, db, idesc, (kb | k) != 0);
+            if (PAIR) umma_f16_ss_pair(d_tmem, da, db, idesc, (kb | k) != 0);
+            else umma_f16_ss(d_tmem, da, db, idesc, (kb | k) != 0);
           }
-          umma_commit(&empty[s]);   // frees the stage once these MMAs have read it
+          // frees the stage (in both CTAs of a pair) once these MMAs have read it
+          if (PAIR) umma_commit_pair(&empty[s], pair_mask);
+          else umma_commit(&empty[s]);
         }
         __syncwarp();
       }
-      if (ok && lane == 0) { umma_commit(&accum_full[ab]); if (it == 0 && p.timeline_mode == 0) stamp(p.timeline, 8); }
+      if (ok && lane == 0) {
+        if (PAIR) umma_commit_pair(&accum_full[ab], pair_mask);
+        else umma_commit(&accum_full[ab]);
+        if (it == 0 && p.timeline_mode == 0) stamp(p.timeline, 8);
+      }
       __syncwarp();
     }
   } else if (PIPE) {
@@ -369,10 +412,10 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       float f0, f1;
       if (CLUSTER) {
         const float ll = l0 * ex2_approx(m0 - lm) + (valid1 > 0 ? l1 * ex2_approx(m1 - lm) : 0.f);
-        const uint32_t slot = smem_u32(&stats[(sset * kMaxCluster + cta_rank) * BM + row_in_tile]);
+        const uint32_t slot = smem_u32(&stats[(sset * kMaxCluster + col_rank) * BM + row_in_tile]);
         const uint32_t bar = smem_u32(&stats_bar[sset]);
         for (uint32_t peer = 0; peer < cluster_n; ++peer)
-          st_async_f32x2(map_to_cta(slot, peer), lm, ll, map_to_cta(bar, peer));
+          st_async_f32x2(map_to_cta(slot, row_peer(peer)), lm, ll, map_to_cta(bar, row_peer(peer)));
         if (!mbar_wait_cluster(&stats_bar[sset], stats_phase)) { record_failure(p.status, WTC_DEV_TIMEOUT_STATS); break; }
         if (stamper && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 3);
         if (stamper) stamp_tile(p, it >> 1, 2);
@@ -448,7 +491,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         if (c * 32 < valid0) tmem_ld_32x32b_x32(tbase + c * 32, r[c]);
       tmem_ld_wait();
       tc_fence_before_sync();
-      mbar_arrive(&accum_empty[ab]);
+      release_accumulator(ab);
       write_half(valid0, f0, col0);
       if (!CLUSTER) {
         const int row = rb * BM + row_in_tile;
@@ -501,7 +544,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       }
       tmem_ld_wait();
       tc_fence_before_sync();
-      mbar_arrive(&accum_empty[ab]);
+      release_accumulator(ab);
       if (lead && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 14);
       if (p.round_logits_f16) {
 #pragma unroll
@@ -590,10 +633,10 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                          (o.x == -INFINITY ? 0.f : o.y * ex2_approx(o.x - lm));
         // ... and the CTAs of the cluster through each other's shared memory
         if (half == 0) {
-          const uint32_t slot = smem_u32(&stats[(par * kMaxCluster + cta_rank) * BM + row_in_tile]);
+          const uint32_t slot = smem_u32(&stats[(par * kMaxCluster + col_rank) * BM + row_in_tile]);
           const uint32_t bar = smem_u32(&stats_bar[par]);
           for (uint32_t peer = 0; peer < cluster_n; ++peer)
-            st_async_f32x2(map_to_cta(slot, peer), lm, ll, map_to_cta(bar, peer));
+            st_async_f32x2(map_to_cta(slot, row_peer(peer)), lm, ll, map_to_cta(bar, row_peer(peer)));
         }
         if (!mbar_wait_cluster(&stats_bar[par], tile_phase)) { record_failure(p.status, WTC_DEV_TIMEOUT_STATS); break; }
         if (lead && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 3);
@@ -685,21 +728,25 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (CLUSTER) cluster_sync_all();
-  if (warp == 1) tmem_dealloc(tmem_base, 2 * BN);
+  if (CLUSTERED) cluster_sync_all();
+  if (warp == 1) { if (PAIR) tmem_dealloc_pair(tmem_base, 2 * BN); else tmem_dealloc(tmem_base, 2 * BN); }
 }
 
-template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool PIPE>
-cudaError_t launch_impl(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO, const TcParams &p,
+template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool PIPE, bool PAIR>
+cudaError_t launch_impl(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO, TcParams p,
                         int cluster_n, int num_sms, cudaStream_t s, TcLaunchInfo *info) {
-  using L = SmemLayout<BN, STAGES, CLUSTER, OUT_TILES, PIPE>;
-  auto kern = fused_tc_kernel<BN, STAGES, CLUSTER, OUT_TILES, PIPE>;
+  using L = SmemLayout<BN, STAGES, CLUSTER, OUT_TILES, PIPE, PAIR>;
+  auto kern = fused_tc_kernel<BN, STAGES, CLUSTER, OUT_TILES, PIPE, PAIR>;
   static bool attr_set = false;   // per template instance
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
+  // work items: row units (128 rows, or 256 for a CTA pair) x (column blocks when tiled)
+  p.num_ru = PAIR ? (p.num_rb + 1) / 2 : p.num_rb;
+  p.num_items = p.batch * p.num_ru * (CLUSTER ? 1 : p.num_nb);
+  const int cluster_size = (CLUSTER ? cluster_n : 1) * (PAIR ? 2 : 1);
 
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(kThreads, 1, 1);
@@ -713,63 +760,81 @@ cudaError_t launch_impl(const CUtensorMap &tmA, const CUtensorMap &tmB, const CU
     ++nattr;
   }
   int grid;
-  if (CLUSTER) {
+  if (CLUSTER || PAIR) {   // always a cluster launch for these variants, even for a cluster of one
     attr[nattr].id = cudaLaunchAttributeClusterDimension;
-    attr[nattr].val.clusterDim.x = cluster_n;
+    attr[nattr].val.clusterDim.x = cluster_size;
     attr[nattr].val.clusterDim.y = 1;
     attr[nattr].val.clusterDim.z = 1;
     ++nattr;
     cfg.attrs = attr;
     cfg.numAttrs = nattr;
-    static int max_clusters_cache[kMaxCluster + 1] = {0};
-    if (!max_clusters_cache[cluster_n]) {
-      cfg.gridDim = dim3(cluster_n, 1, 1);
+    static int max_clusters_cache[2 * kMaxCluster + 1] = {0};   // per template instance, by cluster size
+    if (!max_clusters_cache[cluster_size]) {
+      cfg.gridDim = dim3(cluster_size, 1, 1);
       int mc = 0;
       cudaError_t e = cudaOccupancyMaxActiveClusters(&mc, kern, &cfg);
       if (e != cudaSuccess) return e;
       if (mc < 1) return cudaErrorInvalidConfiguration;
-      max_clusters_cache[cluster_n] = mc;
+      max_clusters_cache[cluster_size] = mc;
     }
-    const int max_clusters = max_clusters_cache[cluster_n];
+    const int max_clusters = max_clusters_cache[cluster_size];
     const int clusters = p.num_items < max_clusters ? p.num_items : max_clusters;
-    grid = clusters * cluster_n;
+    grid = clusters * cluster_size;
   } else {
     grid = p.num_items < num_sms ? p.num_items : num_sms;
     cfg.attrs = nattr ? attr : nullptr;
     cfg.numAttrs = nattr;
   }
   cfg.gridDim = dim3(grid, 1, 1);
-  if (info) { info->grid = grid; info->cluster = CLUSTER ? cluster_n : 1; info->smem_bytes = L::kDynamic; info->threads = kThreads; }
+  if (info) { info->grid = grid; info->cluster = cluster_size; info->smem_bytes = L::kDynamic; info->threads = kThreads; }
   return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmO, p);
 }
 
 } // namespace
 
+// Variant choice.  pair: two CTAs share one 256-row MMA (a third less L2 operand traffic per
+// flop).  Measured on B200 the contraction runs at the same rate either way, and an
+// eight-CTA cluster fits the chip only 15 times, so the cluster flavour pairs only on
+// request; the tiled flavour (clusters of two) pairs when the K loop is long.  pipe: with several tiles per CTA the two epilogue warp groups take
+// alternate tiles; with one tile per CTA all eight warps share it.  store: swizzled staging +
+// TMA stores by default, direct register stores on request.
 cudaError_t launch_fused_cluster(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO,
                                  const TcParams &p, int cluster_n, int num_sms, cudaStream_t s,
                                  TcLaunchInfo *info) {
   if (cluster_n < 1 || cluster_n > kMaxCluster) return cudaErrorInvalidValue;
-  // With at least two row blocks per resident cluster the tile-pipelined epilogue keeps the
-  // special-function unit busy across tiles; with one tile per CTA all eight epilogue warps
-  // share that tile instead.
-  const bool pipe = p.epilogue_mode == 2 || (p.epilogue_mode == 0 && p.num_items >= 2 * (num_sms / cluster_n));
-  if (p.store_mode == 1) {   // staged TMA stores: three pipeline stages leave room for the staging tiles
-    if (pipe) return launch_impl<kTcBlockN, 3, true, 1, true>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
-    return launch_impl<kTcBlockN, 3, true, 2, false>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+  const bool pair = p.pair_mode == 2 && 2 * cluster_n <= kMaxCluster;
+  const int row_units = p.batch * (pair ? (p.num_rb + 1) / 2 : p.num_rb);
+  const int resident = num_sms / (cluster_n * (pair ? 2 : 1));
+  const bool pipe = p.epilogue_mode == 2 || (p.epilogue_mode == 0 && row_units >= 2 * (resident > 0 ? resident : 1));
+  const bool tma = p.store_mode == 1;
+  if (pair) {
+    if (tma) return pipe ? launch_impl<kTcBlockN, 4, true, 1, true, true>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info)
+                         : launch_impl<kTcBlockN, 4, true, 2, false, true>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+    return pipe ? launch_impl<kTcBlockN, 6, true, 0, true, true>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info)
+                : launch_impl<kTcBlockN, 6, true, 0, false, true>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
   }
-  if (pipe) return launch_impl<kTcBlockN, 4, true, 0, true>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
-  return launch_impl<kTcBlockN, 4, true, 0, false>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+  if (tma) return pipe ? launch_impl<kTcBlockN, 3, true, 1, true, false>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info)
+                       : launch_impl<kTcBlockN, 3, true, 2, false, false>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+  return pipe ? launch_impl<kTcBlockN, 4, true, 0, true, false>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info)
+              : launch_impl<kTcBlockN, 4, true, 0, false, false>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
 }
 
 cudaError_t launch_tiled_partial(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO,
                                  const TcParams &p, int num_sms, cudaStream_t s, TcLaunchInfo *info) {
-  const bool pipe = p.epilogue_mode == 2 || (p.epilogue_mode == 0 && p.num_items >= 2 * num_sms);
-  if (p.store_mode == 1) {
-    if (pipe) return launch_impl<kTcBlockN, 4, false, 1, true>(tmA, tmB, tmO, p, 1, num_sms, s, info);
-    return launch_impl<kTcBlockN, 4, false, 1, false>(tmA, tmB, tmO, p, 1, num_sms, s, info);
+  const bool pair = p.pair_mode == 2 || (p.pair_mode == 0 && p.num_rb >= 2 && p.num_kb >= 8);
+  const int items = p.batch * (pair ? (p.num_rb + 1) / 2 : p.num_rb) * p.num_nb;
+  const bool pipe = p.epilogue_mode == 2 || (p.epilogue_mode == 0 && items >= 2 * (pair ? num_sms / 2 : num_sms));
+  const bool tma = p.store_mode == 1;
+  if (pair) {
+    if (tma) return pipe ? launch_impl<kTcBlockN, 6, false, 1, true, true>(tmA, tmB, tmO, p, 1, num_sms, s, info)
+                         : launch_impl<kTcBlockN, 6, false, 1, false, true>(tmA, tmB, tmO, p, 1, num_sms, s, info);
+    return pipe ? launch_impl<kTcBlockN, 6, false, 0, true, true>(tmA, tmB, tmO, p, 1, num_sms, s, info)
+                : launch_impl<kTcBlockN, 6, false, 0, false, true>(tmA, tmB, tmO, p, 1, num_sms, s, info);
   }
-  if (pipe) return launch_impl<kTcBlockN, 4, false, 0, true>(tmA, tmB, tmO, p, 1, num_sms, s, info);
-  return launch_impl<kTcBlockN, 4, false, 0, false>(tmA, tmB, tmO, p, 1, num_sms, s, info);
+  if (tma) return pipe ? launch_impl<kTcBlockN, 4, false, 1, true, false>(tmA, tmB, tmO, p, 1, num_sms, s, info)
+                       : launch_impl<kTcBlockN, 4, false, 1, false, false>(tmA, tmB, tmO, p, 1, num_sms, s, info);
+  return pipe ? launch_impl<kTcBlockN, 4, false, 0, true, false>(tmA, tmB, tmO, p, 1, num_sms, s, info)
+              : launch_impl<kTcBlockN, 4, false, 0, false, false>(tmA, tmB, tmO, p, 1, num_sms, s, info);
 }
 
 } // namespace wtc

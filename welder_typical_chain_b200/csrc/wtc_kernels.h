@@ -20,6 +20,7 @@ struct TcParams {
   int num_rb;      // row blocks of 128 per batch
   int num_nb;      // column blocks of BN per row
   int num_kb;      // K blocks of 64
+  int num_ru;      // row units per batch: row blocks, or pairs of row blocks (set by the launcher)
   int num_items;   // work items: cluster mode batch*num_rb, tiled mode batch*num_rb*num_nb
   int b_batched;   // B has its own batch dimension
   int group_rb;    // tiled mode: row blocks per rasterisation group
@@ -29,6 +30,7 @@ struct TcParams {
   int store_mode;  // 0 direct register->global stores, 1 swizzled shared staging + TMA stores
   int debug_flags; // bring-up experiments: 1 = drop the epilogue stores
   int stagger;     // tile-pipelined epilogue: offset the two warp groups by one phase
+  int pair_mode;   // 0 choose, 1 never pair CTAs, 2 pair whenever the cluster allows
   int epilogue_mode;  // 0 choose by tiles per CTA, 1 all warps share a tile, 2 warp groups alternate tiles
   int use_pdl;     // launch with programmatic stream serialisation
   int round_logits_f16;  // chain spelled with an f16 matmul result: round s to f16 before the softmax
