@@ -42,7 +42,7 @@ L2_BYTES = 126 * 1024 * 1024
 
 # DRAM traffic of the dominant kernel, bytes per launch, from the ncu captures
 # summarised under profiles/ (dram__bytes_read.sum + dram__bytes_write.sum).
-NCU_TRAFFIC = {}
+NCU_TRAFFIC = {"cfg2": 10555648, "cfg3": 550405120, "cfg5": 267214336}
 
 
 def peaks():
@@ -187,15 +187,14 @@ def main():
     shard = wl["shard"]
     scaling = "weak"
     n_local = N
+    from welder_typical_chain_b200 import sharding
     if shard == "batch" and world > 1:           # fixed 64 batches split over the ranks
-        per = [batch // world + (1 if r < batch % world else 0) for r in range(world)]
-        batch = per[rank]
+        b0, b1 = sharding.split_batches(batch, world)[rank]
+        batch = b1 - b0
         scaling = "strong"
     elif shard == "cols" and world > 1:          # N split on 256-column tile boundaries
-        tiles = (N + 255) // 256
-        per = [tiles // world + (1 if r < tiles % world else 0) for r in range(world)]
-        c0 = 256 * sum(per[:rank])
-        n_local = min(N, c0 + 256 * per[rank]) - c0
+        c0, c1 = sharding.split_columns(N, world)[rank]
+        n_local = c1 - c0
         scaling = "strong"
     # rows / replica: every rank runs the whole per-GPU workload (weak scaling)
 
