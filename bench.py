@@ -259,6 +259,27 @@ def main():
         if not parity["ok"]:
             raise SystemExit(f"parity check failed before timing: {parity}")
 
+    if not args.no_parity and col_sharded:
+        # every rank checks its own columns of a few rows: the whole-row (max, sum) comes from
+        # float64 partials of all ranks, exchanged as Python objects
+        step(0)
+        torch.cuda.synchronize()
+        A, B, O = sets[0]
+        idx = sorted(set(int(x) for x in np.linspace(0, M - 1, 8)))
+        v = scale * 1.4426950408889634 * (A[idx].double().cpu().numpy() @ B.double().cpu().numpy())
+        m_loc = v.max(1) if n_local else np.full(len(idx), -np.inf)
+        l_loc = np.exp2(v - m_loc[:, None]).sum(1) if n_local else np.zeros(len(idx))
+        parts = [None] * world
+        dist.all_gather_object(parts, (m_loc, l_loc))
+        gm = np.max([q[0] for q in parts], axis=0)
+        gl = np.sum([q[1] * np.exp2(q[0] - gm) for q in parts], axis=0)
+        ref = np.exp2(v - gm[:, None]) / gl[:, None]
+        got = O[idx].float().cpu().numpy().astype(np.float64)
+        err = float(np.abs(got - ref).max()) if n_local else 0.0
+        parity = dict(ok=bool(err <= 2e-3), max_abs=err, rows_checked=len(idx), note="this rank's columns against the whole-row statistics")
+        if not parity["ok"]:
+            raise SystemExit(f"rank {rank}: column-sharded parity check failed: {parity}")
+
     for i in range(args.warmup):
         step(i)
     wtc.check_device_status()

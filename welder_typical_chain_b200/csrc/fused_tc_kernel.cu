@@ -38,21 +38,21 @@ namespace {
 
 constexpr int BM = kTcBlockM;
 constexpr int BK = kTcBlockK;
-constexpr int kEpiWarps = 8;
-constexpr int kEpiThreads = kEpiWarps * 32;
-constexpr int kThreads = 64 + kEpiThreads;
+// Epilogue warps per CTA: 8 (a thread owns one row x BN/2 columns) or 16 (one row x BN/4:
+// four warps per scheduler hide the TMEM-load and barrier latencies the eight-warp form exposes).
+constexpr int kThreadsFor(int ew) { return 64 + ew * 32; }
 constexpr int kMaxCluster = 8;
 
 // OUT_TILES: 32-row x 64-column f16 staging tiles per epilogue warp (2 = the warp's two
 // column groups never wait for each other's TMA read; 1 = smaller, leaves room for a stage).
-template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool PIPE, bool PAIR>
+template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool PIPE, bool PAIR, int EW>
 struct SmemLayout {
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BK * BN * 2 / (PAIR ? 2 : 1);     // a CTA pair splits B's columns between its two CTAs
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kHalfCols = BN / 2;                            // columns per epilogue thread
+  static constexpr int kHalfCols = PIPE ? BN / 2 : BN * 4 / EW;       // columns per epilogue thread (per step)
   static constexpr int kOutWarpBytes = OUT_TILES * 32 * 64 * 2;      // 0: the epilogue stores straight from registers
-  static constexpr int kOutBytes = kEpiWarps * kOutWarpBytes;
+  static constexpr int kOutBytes = EW * kOutWarpBytes;
   static constexpr int kPairBytes = 2 * BM * 8;                       // [half][row] float2
   static constexpr int kStatsSets = PIPE ? 4 : 2;                      // PIPE: two per epilogue group
   static constexpr int kStatsBytes = CLUSTER ? kStatsSets * kMaxCluster * BM * 8 : 0;
@@ -92,13 +92,17 @@ __device__ __forceinline__ void stamp_tile(const TcParams &p, int seq, int k) {
   if (p.timeline && p.timeline_mode == 1 && seq < 4) stamp(p.timeline, seq * 4 + k);
 }
 
-template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool PIPE, bool PAIR>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool PIPE, bool PAIR, int EW>
+__global__ void __launch_bounds__(kThreadsFor(EW), 1)
 fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmO, const TcParams p) {
-  using L = SmemLayout<BN, STAGES, CLUSTER, OUT_TILES, PIPE, PAIR>;
+  using L = SmemLayout<BN, STAGES, CLUSTER, OUT_TILES, PIPE, PAIR, EW>;
   constexpr int HC = L::kHalfCols;      // columns per epilogue thread
   constexpr int NCH = HC / 32;          // 32-column chunks per epilogue thread
+  constexpr int kEpiThreads = EW * 32;
+  constexpr int PARTS = BN / HC;        // threads that share a row (split epilogue)
+  static_assert(!PIPE || EW == 8, "the tile-pipelined epilogue uses two groups of four warps");
+  static_assert(EW == 8 || (CLUSTER && OUT_TILES == 1 && !PAIR), "sixteen epilogue warps: cluster flavour with staged stores only");
   // The 128-byte swizzle needs the stage buffers on 1024-byte boundaries.  There is no
   // static shared memory in this kernel, so the dynamic window starts aligned; if it ever
   // does not, every thread leaves before any barrier or TMEM state exists.
@@ -505,7 +509,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   } else {
     // ======================= softmax epilogue ==============================
     const int q = warp & 3;                      // TMEM lane quarter this warp may read
-    const int half = (warp - 2) >> 2;            // which half of the tile's columns
+    const int half = (warp - 2) >> 2;            // which part (of PARTS) of the tile's columns
     const int row_in_tile = q * 32 + lane;
     const bool lead = threadIdx.x == 64;         // first epilogue thread: posts expect_tx, stamps
     uint8_t *stg = smem + L::kOffOut + (warp - 2) * L::kOutWarpBytes;   // one 32-row x 64-col f16 tile
@@ -621,16 +625,45 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       if (lead && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 2);
       if (lead) stamp_tile(p, it, 1);
 
-      // ---- the two halves of a row meet through shared memory ----
-      *mine = make_float2(m_half, sum);
-      named_bar_sync(1 + q, 64);
-      const float2 o = *other;
-      named_bar_sync(1 + q, 64);                   // both have read: the slots may be reused
-      const float lm = fmaxf(m_half, o.x);         // tile-row max (log2 domain)
+      float lm;                                    // tile-row max (log2 domain)
+      float2 o = make_float2(-INFINITY, 0.f);      // PARTS == 2: the other half's (max, sum)
+      float ll4 = 0.f;                             // PARTS == 4: the row's sum over the four parts (part 0 only)
+      if (PARTS == 2) {
+        // ---- the two halves of a row meet through shared memory ----
+        *mine = make_float2(m_half, sum);
+        named_bar_sync(1 + q, 64);
+        o = *other;
+        named_bar_sync(1 + q, 64);                 // both have read: the slots may be reused
+        lm = fmaxf(m_half, o.x);
+      } else {
+        // ---- four parts of a row: parts 1..3 leave their (max, sum) in their own warp's
+        //      staging tile (idle now: its last store has been read), part 0 collects.  Only
+        //      part 0 needs the combination; the others just signal and move on. ----
+        if (lane == 0) tma_store_wait_read();
+        __syncwarp();
+        if (half != 0) {
+          *reinterpret_cast<float2 *>(stg + lane * 8) = make_float2(m_half, sum);
+          named_bar_arrive(1 + q, 128);
+          lm = m_half;                             // unused by parts 1..3
+        } else {
+          named_bar_sync(1 + q, 128);
+          lm = m_half;
+          float2 part[3];
+#pragma unroll
+          for (int j = 0; j < 3; ++j) {
+            part[j] = *reinterpret_cast<const float2 *>(smem + L::kOffOut + (4 * (j + 1) + ((q + 2) & 3)) * L::kOutWarpBytes + lane * 8);
+            lm = fmaxf(lm, part[j].x);
+          }
+          ll4 = sum * ex2_approx(m_half - lm);
+#pragma unroll
+          for (int j = 0; j < 3; ++j) ll4 += part[j].x == -INFINITY ? 0.f : part[j].y * ex2_approx(part[j].x - lm);
+        }
+      }
       float f;                                     // what my e values still have to be multiplied by
       if (CLUSTER) {
-        const float ll = (m_half == -INFINITY ? 0.f : sum * ex2_approx(m_half - lm)) +
-                         (o.x == -INFINITY ? 0.f : o.y * ex2_approx(o.x - lm));
+        const float ll = PARTS == 4 ? ll4
+                                    : (m_half == -INFINITY ? 0.f : sum * ex2_approx(m_half - lm)) +
+                                          (o.x == -INFINITY ? 0.f : o.y * ex2_approx(o.x - lm));
         // ... and the CTAs of the cluster through each other's shared memory
         if (half == 0) {
           const uint32_t slot = smem_u32(&stats[(par * kMaxCluster + col_rank) * BM + row_in_tile]);
@@ -732,11 +765,11 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   if (warp == 1) { if (PAIR) tmem_dealloc_pair(tmem_base, 2 * BN); else tmem_dealloc(tmem_base, 2 * BN); }
 }
 
-template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool PIPE, bool PAIR>
+template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool PIPE, bool PAIR, int EW>
 cudaError_t launch_impl(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO, TcParams p,
                         int cluster_n, int num_sms, cudaStream_t s, TcLaunchInfo *info) {
-  using L = SmemLayout<BN, STAGES, CLUSTER, OUT_TILES, PIPE, PAIR>;
-  auto kern = fused_tc_kernel<BN, STAGES, CLUSTER, OUT_TILES, PIPE, PAIR>;
+  using L = SmemLayout<BN, STAGES, CLUSTER, OUT_TILES, PIPE, PAIR, EW>;
+  auto kern = fused_tc_kernel<BN, STAGES, CLUSTER, OUT_TILES, PIPE, PAIR, EW>;
   static bool attr_set = false;   // per template instance
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
@@ -749,7 +782,7 @@ cudaError_t launch_impl(const CUtensorMap &tmA, const CUtensorMap &tmB, const CU
   const int cluster_size = (CLUSTER ? cluster_n : 1) * (PAIR ? 2 : 1);
 
   cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.blockDim = dim3(kThreadsFor(EW), 1, 1);
   cfg.dynamicSmemBytes = L::kDynamic;
   cfg.stream = s;
   cudaLaunchAttribute attr[2];
@@ -786,7 +819,7 @@ cudaError_t launch_impl(const CUtensorMap &tmA, const CUtensorMap &tmB, const CU
     cfg.numAttrs = nattr;
   }
   cfg.gridDim = dim3(grid, 1, 1);
-  if (info) { info->grid = grid; info->cluster = cluster_size; info->smem_bytes = L::kDynamic; info->threads = kThreads; }
+  if (info) { info->grid = grid; info->cluster = cluster_size; info->smem_bytes = L::kDynamic; info->threads = kThreadsFor(EW); }
   return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmO, p);
 }
 
@@ -808,15 +841,21 @@ cudaError_t launch_fused_cluster(const CUtensorMap &tmA, const CUtensorMap &tmB,
   const bool pipe = p.epilogue_mode == 2 || (p.epilogue_mode == 0 && row_units >= 2 * (resident > 0 ? resident : 1));
   const bool tma = p.store_mode == 1;
   if (pair) {
-    if (tma) return pipe ? launch_impl<kTcBlockN, 4, true, 1, true, true>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info)
-                         : launch_impl<kTcBlockN, 4, true, 2, false, true>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
-    return pipe ? launch_impl<kTcBlockN, 6, true, 0, true, true>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info)
-                : launch_impl<kTcBlockN, 6, true, 0, false, true>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+    if (tma) return pipe ? launch_impl<kTcBlockN, 4, true, 1, true, true, 8>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info)
+                         : launch_impl<kTcBlockN, 4, true, 2, false, true, 8>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+    return pipe ? launch_impl<kTcBlockN, 6, true, 0, true, true, 8>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info)
+                : launch_impl<kTcBlockN, 6, true, 0, false, true, 8>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
   }
-  if (tma) return pipe ? launch_impl<kTcBlockN, 3, true, 1, true, false>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info)
-                       : launch_impl<kTcBlockN, 3, true, 2, false, false>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
-  return pipe ? launch_impl<kTcBlockN, 4, true, 0, true, false>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info)
-              : launch_impl<kTcBlockN, 4, true, 0, false, false>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+  if (tma) {
+    // sixteen epilogue warps (a row's columns split four ways) on request: measured on B200 it
+    // does not beat eight (the exp and pack phases are bound by the special-function unit)
+    if (p.epilogue_warps == 16 && p.epilogue_mode != 2)
+      return launch_impl<kTcBlockN, 3, true, 1, false, false, 16>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+    return pipe ? launch_impl<kTcBlockN, 3, true, 1, true, false, 8>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info)
+                : launch_impl<kTcBlockN, 3, true, 2, false, false, 8>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+  }
+  return pipe ? launch_impl<kTcBlockN, 4, true, 0, true, false, 8>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info)
+              : launch_impl<kTcBlockN, 4, true, 0, false, false, 8>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
 }
 
 cudaError_t launch_tiled_partial(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO,
@@ -826,15 +865,15 @@ cudaError_t launch_tiled_partial(const CUtensorMap &tmA, const CUtensorMap &tmB,
   const bool pipe = p.epilogue_mode == 2 || (p.epilogue_mode == 0 && items >= 2 * (pair ? num_sms / 2 : num_sms));
   const bool tma = p.store_mode == 1;
   if (pair) {
-    if (tma) return pipe ? launch_impl<kTcBlockN, 6, false, 1, true, true>(tmA, tmB, tmO, p, 1, num_sms, s, info)
-                         : launch_impl<kTcBlockN, 6, false, 1, false, true>(tmA, tmB, tmO, p, 1, num_sms, s, info);
-    return pipe ? launch_impl<kTcBlockN, 6, false, 0, true, true>(tmA, tmB, tmO, p, 1, num_sms, s, info)
-                : launch_impl<kTcBlockN, 6, false, 0, false, true>(tmA, tmB, tmO, p, 1, num_sms, s, info);
+    if (tma) return pipe ? launch_impl<kTcBlockN, 6, false, 1, true, true, 8>(tmA, tmB, tmO, p, 1, num_sms, s, info)
+                         : launch_impl<kTcBlockN, 6, false, 1, false, true, 8>(tmA, tmB, tmO, p, 1, num_sms, s, info);
+    return pipe ? launch_impl<kTcBlockN, 6, false, 0, true, true, 8>(tmA, tmB, tmO, p, 1, num_sms, s, info)
+                : launch_impl<kTcBlockN, 6, false, 0, false, true, 8>(tmA, tmB, tmO, p, 1, num_sms, s, info);
   }
-  if (tma) return pipe ? launch_impl<kTcBlockN, 4, false, 1, true, false>(tmA, tmB, tmO, p, 1, num_sms, s, info)
-                       : launch_impl<kTcBlockN, 4, false, 1, false, false>(tmA, tmB, tmO, p, 1, num_sms, s, info);
-  return pipe ? launch_impl<kTcBlockN, 4, false, 0, true, false>(tmA, tmB, tmO, p, 1, num_sms, s, info)
-              : launch_impl<kTcBlockN, 4, false, 0, false, false>(tmA, tmB, tmO, p, 1, num_sms, s, info);
+  if (tma) return pipe ? launch_impl<kTcBlockN, 4, false, 1, true, false, 8>(tmA, tmB, tmO, p, 1, num_sms, s, info)
+                       : launch_impl<kTcBlockN, 4, false, 1, false, false, 8>(tmA, tmB, tmO, p, 1, num_sms, s, info);
+  return pipe ? launch_impl<kTcBlockN, 4, false, 0, true, false, 8>(tmA, tmB, tmO, p, 1, num_sms, s, info)
+              : launch_impl<kTcBlockN, 4, false, 0, false, false, 8>(tmA, tmB, tmO, p, 1, num_sms, s, info);
 }
 
 } // namespace wtc

@@ -30,6 +30,7 @@ struct TcParams {
   int store_mode;  // 0 direct register->global stores, 1 swizzled shared staging + TMA stores
   int debug_flags; // bring-up experiments: 1 = drop the epilogue stores
   int stagger;     // tile-pipelined epilogue: offset the two warp groups by one phase
+  int epilogue_warps;  // 0 choose, 8 or 16 (cluster flavour with staged stores)
   int pair_mode;   // 0 choose, 1 never pair CTAs, 2 pair whenever the cluster allows
   int epilogue_mode;  // 0 choose by tiles per CTA, 1 all warps share a tile, 2 warp groups alternate tiles
   int use_pdl;     // launch with programmatic stream serialisation

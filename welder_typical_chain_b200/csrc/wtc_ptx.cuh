@@ -349,6 +349,10 @@ __device__ __forceinline__ void st_global_row32(void *dst, const uint32_t (&h)[1
 }
 
 // ---- named barrier among a subset of warps ------------------------------------
+// Counts this thread on the barrier without waiting for it.
+__device__ __forceinline__ void named_bar_arrive(uint32_t id, uint32_t nthreads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
 __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
