@@ -91,6 +91,10 @@ __device__ __forceinline__ void stamp(long long *timeline, int slot) {
 __device__ __forceinline__ void stamp_tile(const TcParams &p, int seq, int k) {
   if (p.timeline && p.timeline_mode == 1 && seq < 4) stamp(p.timeline, seq * 4 + k);
 }
+// Third layout (timeline_mode 2): eight points of the second and third tile one thread sees.
+__device__ __forceinline__ void stamp_fine(const TcParams &p, int seq, int k) {
+  if (p.timeline && p.timeline_mode == 2 && (seq == 1 || seq == 2)) stamp(p.timeline, (seq - 1) * 8 + k);
+}
 
 template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool PIPE, bool PAIR, int EW>
 __global__ void __launch_bounds__(kThreadsFor(EW), 1)
@@ -194,6 +198,20 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   };
   // cluster rank of the j-th CTA that holds the same rows as this one
   auto row_peer = [&](uint32_t j) -> uint32_t { return PAIR ? 2 * j + pair_rank : j; };
+
+  // (row max, 1 / row sum) from the pairs the CTAs of the cluster sent for statistics set
+  // `set`: all loads first, then a max tree, independent exps, a sum tree.
+  auto combine_cluster_stats = [&](int set, int row, float &gm, float &inv_gl) {
+    float2 st[kMaxCluster];
+#pragma unroll
+    for (int j = 0; j < kMaxCluster; ++j)
+      st[j] = static_cast<uint32_t>(j) < cluster_n ? stats[(set * kMaxCluster + j) * BM + row] : make_float2(-INFINITY, 0.f);
+    gm = fmaxf(fmaxf(max3(st[0].x, st[1].x, st[2].x), max3(st[3].x, st[4].x, st[5].x)), fmaxf(st[6].x, st[7].x));
+    float t[kMaxCluster];
+#pragma unroll
+    for (int j = 0; j < kMaxCluster; ++j) t[j] = st[j].y * ex2_approx(st[j].x - gm);
+    inv_gl = rcp_approx(((t[0] + t[1]) + (t[2] + t[3])) + ((t[4] + t[5]) + (t[6] + t[7])));
+  };
 
   if (warp == 0) {
     // ======================= TMA producer ==================================
@@ -423,15 +441,8 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         if (!mbar_wait_cluster(&stats_bar[sset], stats_phase)) { record_failure(p.status, WTC_DEV_TIMEOUT_STATS); break; }
         if (stamper && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 3);
         if (stamper) stamp_tile(p, it >> 1, 2);
-        float gm = -INFINITY;
-        for (uint32_t peer = 0; peer < cluster_n; ++peer)
-          gm = fmaxf(gm, stats[(sset * kMaxCluster + peer) * BM + row_in_tile].x);
-        float gl = 0.f;
-        for (uint32_t peer = 0; peer < cluster_n; ++peer) {
-          const float2 st = stats[(sset * kMaxCluster + peer) * BM + row_in_tile];
-          gl += st.y * ex2_approx(st.x - gm);
-        }
-          const float inv = 1.0f / gl;
+        float gm, inv;
+        combine_cluster_stats(sset, row_in_tile, gm, inv);
         f0 = ex2_approx(m0 - gm) * inv;
         f1 = ex2_approx(m1 - gm) * inv;
       } else {
@@ -528,7 +539,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       if (!mbar_wait(&accum_full[ab], tile_phase)) { record_failure(p.status, WTC_DEV_TIMEOUT_ACCUM); break; }
       tc_fence_after_sync();
       if (lead && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 1);
-      if (lead) stamp_tile(p, it, 0);
+      if (lead) { stamp_tile(p, it, 0); stamp_fine(p, it, 0); }
       const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ab * BN + half * HC;
       const int col0 = nb * BN + half * HC;               // first matrix column of this thread
       const int valid = max(0, min(HC, p.N - col0));      // my columns that exist
@@ -550,6 +561,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       tc_fence_before_sync();
       release_accumulator(ab);
       if (lead && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 14);
+      if (lead) stamp_fine(p, it, 1);
       if (p.round_logits_f16) {
 #pragma unroll
         for (int c = 0; c < NCH; ++c)
@@ -566,18 +578,22 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
           for (int c = 0; c < NCH; ++c)
 #pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-              m0 = fmaxf(m0, __uint_as_float(r[c][i]));     m1 = fmaxf(m1, __uint_as_float(r[c][i + 1]));
-              m2 = fmaxf(m2, __uint_as_float(r[c][i + 2])); m3 = fmaxf(m3, __uint_as_float(r[c][i + 3]));
+            for (int i = 0; i < 32; i += 8) {
+              m0 = max3(m0, __uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1]));
+              m1 = max3(m1, __uint_as_float(r[c][i + 2]), __uint_as_float(r[c][i + 3]));
+              m2 = max3(m2, __uint_as_float(r[c][i + 4]), __uint_as_float(r[c][i + 5]));
+              m3 = max3(m3, __uint_as_float(r[c][i + 6]), __uint_as_float(r[c][i + 7]));
             }
           m_half = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
         } else {
 #pragma unroll
           for (int c = 0; c < NCH; ++c)
 #pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-              m0 = fminf(m0, __uint_as_float(r[c][i]));     m1 = fminf(m1, __uint_as_float(r[c][i + 1]));
-              m2 = fminf(m2, __uint_as_float(r[c][i + 2])); m3 = fminf(m3, __uint_as_float(r[c][i + 3]));
+            for (int i = 0; i < 32; i += 8) {
+              m0 = min3(m0, __uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1]));
+              m1 = min3(m1, __uint_as_float(r[c][i + 2]), __uint_as_float(r[c][i + 3]));
+              m2 = min3(m2, __uint_as_float(r[c][i + 4]), __uint_as_float(r[c][i + 5]));
+              m3 = min3(m3, __uint_as_float(r[c][i + 6]), __uint_as_float(r[c][i + 7]));
             }
           m_half = fminf(fminf(m0, m1), fminf(m2, m3));
         }
@@ -595,6 +611,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       }
 
       if (lead && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 15);
+      if (lead) stamp_fine(p, it, 2);
       // ---- e = 2^(v - m_half) in place, row sum ----
       float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
       if (valid == HC) {
@@ -623,7 +640,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       }
       float sum = (s0 + s1) + (s2 + s3);
       if (lead && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 2);
-      if (lead) stamp_tile(p, it, 1);
+      if (lead) { stamp_tile(p, it, 1); stamp_fine(p, it, 3); }
 
       float lm;                                    // tile-row max (log2 domain)
       float2 o = make_float2(-INFINITY, 0.f);      // PARTS == 2: the other half's (max, sum)
@@ -673,20 +690,15 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
         if (!mbar_wait_cluster(&stats_bar[par], tile_phase)) { record_failure(p.status, WTC_DEV_TIMEOUT_STATS); break; }
         if (lead && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 3);
-        if (lead) stamp_tile(p, it, 2);
-        float gm = -INFINITY;
-        for (uint32_t peer = 0; peer < cluster_n; ++peer)
-          gm = fmaxf(gm, stats[(par * kMaxCluster + peer) * BM + row_in_tile].x);
-        float gl = 0.f;
-        for (uint32_t peer = 0; peer < cluster_n; ++peer) {
-          const float2 st = stats[(par * kMaxCluster + peer) * BM + row_in_tile];
-          gl += st.y * ex2_approx(st.x - gm);
-        }
-        f = ex2_approx(m_half - gm) / gl;
+        if (lead) { stamp_tile(p, it, 2); stamp_fine(p, it, 4); }
+        float gm, inv_gl;
+        combine_cluster_stats(par, row_in_tile, gm, inv_gl);
+        f = ex2_approx(m_half - gm) * inv_gl;
       } else {
         f = ex2_approx(m_half - lm);               // tiled: values relative to the tile max, not normalised
       }
 
+      if (lead) stamp_fine(p, it, 5);              // row statistics combined, factor known
       // ---- p = e * f -> f16 -> global memory ----
       float sum_r = 0.f;                           // tiled: sum of what is actually stored
       if (OUT_TILES == 0) {
@@ -728,6 +740,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
               }
               stage_row_chunk(tile, lane, hc, h);
             }
+            if (lead && g == NCH / 2 - 1) stamp_fine(p, it, 6);    // last group packed and staged
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
@@ -748,7 +761,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         named_bar_sync(1 + q, 64);
       }
       if (lead && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 4);
-      if (lead) stamp_tile(p, it, 3);
+      if (lead) { stamp_tile(p, it, 3); stamp_fine(p, it, 7); }
     }
     if (lane == 0) tma_store_wait_all();
     if (lead && p.timeline_mode == 0) stamp(p.timeline, 5);
@@ -838,7 +851,9 @@ cudaError_t launch_fused_cluster(const CUtensorMap &tmA, const CUtensorMap &tmB,
   const bool pair = p.pair_mode == 2 && 2 * cluster_n <= kMaxCluster;
   const int row_units = p.batch * (pair ? (p.num_rb + 1) / 2 : p.num_rb);
   const int resident = num_sms / (cluster_n * (pair ? 2 : 1));
-  const bool pipe = p.epilogue_mode == 2 || (p.epilogue_mode == 0 && row_units >= 2 * (resident > 0 ? resident : 1));
+  // measured on B200 (config 3): split 275 us, tile-pipelined 281 us -- split is the default
+  const bool pipe = p.epilogue_mode == 2;
+  (void)row_units; (void)resident;
   const bool tma = p.store_mode == 1;
   if (pair) {
     if (tma) return pipe ? launch_impl<kTcBlockN, 4, true, 1, true, true, 8>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info)
@@ -862,7 +877,8 @@ cudaError_t launch_tiled_partial(const CUtensorMap &tmA, const CUtensorMap &tmB,
                                  const TcParams &p, int num_sms, cudaStream_t s, TcLaunchInfo *info) {
   const bool pair = p.pair_mode == 2 || (p.pair_mode == 0 && p.num_rb >= 2 && p.num_kb >= 8);
   const int items = p.batch * (pair ? (p.num_rb + 1) / 2 : p.num_rb) * p.num_nb;
-  const bool pipe = p.epilogue_mode == 2 || (p.epilogue_mode == 0 && items >= 2 * (pair ? num_sms / 2 : num_sms));
+  const bool pipe = p.epilogue_mode == 2;
+  (void)items;
   const bool tma = p.store_mode == 1;
   if (pair) {
     if (tma) return pipe ? launch_impl<kTcBlockN, 6, false, 1, true, true, 8>(tmA, tmB, tmO, p, 1, num_sms, s, info)

@@ -26,6 +26,7 @@ __device__ __forceinline__ float2 warp_lse(float2 v) {
 // one warp per row
 __global__ void row_stats_kernel(const float2 *__restrict__ tile_stats, float2 *__restrict__ row_stats,
                                  int64_t rows, int num_nb) {
+  grid_dependency_wait();
   const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
   const int lane = threadIdx.x & 31;
@@ -43,6 +44,7 @@ rescale_rows_kernel(__half *__restrict__ out, int N, int64_t ld_out, int BN, int
   extern __shared__ float factor[];          // [num_nb]
   __shared__ float2 warp_part[8];
   __shared__ float2 row_total;
+  grid_dependency_wait();                    // launched behind the tiled kernel with programmatic serialisation
   const int64_t row = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
@@ -95,17 +97,34 @@ cudaError_t launch_row_stats(const float2 *tile_stats, float2 *row_stats_out, in
   if (rows <= 0) return cudaSuccess;
   const int warps = 8;
   const unsigned grid = static_cast<unsigned>((rows + warps - 1) / warps);
-  row_stats_kernel<<<grid, warps * 32, 0, s>>>(tile_stats, row_stats_out, rows, num_nb);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(warps * 32, 1, 1);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, row_stats_kernel, tile_stats, row_stats_out, rows, num_nb);
 }
 
 cudaError_t launch_rescale_rows(void *out_f16, int64_t rows, int N, int64_t ld_out, int BN, int num_nb,
                                 const float2 *tile_stats, const float2 *global_stats, int num_parts,
                                 cudaStream_t s) {
   if (rows <= 0) return cudaSuccess;
-  rescale_rows_kernel<<<static_cast<unsigned>(rows), 256, num_nb * sizeof(float), s>>>(
-      static_cast<__half *>(out_f16), N, ld_out, BN, num_nb, tile_stats, global_stats, num_parts, rows);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(rows), 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.dynamicSmemBytes = num_nb * sizeof(float);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, rescale_rows_kernel, static_cast<__half *>(out_f16), N, ld_out, BN, num_nb, tile_stats,
+                            global_stats, num_parts, rows);
 }
 
 } // namespace wtc
