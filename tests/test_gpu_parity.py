@@ -251,3 +251,31 @@ def test_linearity_and_shift_properties(w, cuda_dev):
     w.check_device_status()
     assert float((pp.float() - p[:, perm].float()).abs().max()) <= 2e-3
     assert float((p.float().sum(-1) - 1).abs().max()) <= 1e-3
+
+
+# ---------------------------------------------------------------- kernel variants
+
+@pytest.mark.parametrize("env", [
+    {"WTC_EPILOGUE": "pipe"},                       # two warp groups alternate tiles, first half parked in TMEM
+    {"WTC_EW": "16"},                               # sixteen epilogue warps, a row split four ways
+    {"WTC_STORE": "direct"},                        # 256-bit register->global stores instead of staged TMA stores
+    {"WTC_STORE": "direct", "WTC_EPILOGUE": "pipe"},
+    {"WTC_PAIR": "1"},                              # tcgen05 cta_group::2 in the cluster flavour too
+    {"WTC_PAIR": "1", "WTC_EPILOGUE": "pipe"},
+    {"WTC_PAIR": "0"},                              # never pair
+    {"WTC_NO_STAGGER": "1", "WTC_STAGGER": "0", "WTC_EPILOGUE": "pipe"},
+])
+def test_every_kernel_variant_matches_the_checker(w, cuda_dev, monkeypatch, env):
+    for k, v in env.items():
+        monkeypatch.setenv(k, v)
+    cases = [
+        (777, 1024, 136, 0.07, 0),                  # cluster of 4, ragged M and K, several tiles per cluster
+        (9000, 2048, 64, 0.125, 0),                 # cluster of 8, many tiles per CTA
+        (200, 520, 72, 0.2, 0),                     # ragged N
+        (300, 1024, 256, 1 / 16, w.FLAG_FORCE_TILED),
+        (2500, 2304, 520, 0.05, 0),                 # tiled, long K (pairs by default)
+    ]
+    for M, N, K, scale, flags in cases:
+        A = oracle.normal((M, K), M)
+        B = oracle.normal((K, N), N)
+        _check(_run(w, cuda_dev, A, B, scale, flags=flags), oracle.chain(A, B, scale))
