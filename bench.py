@@ -225,22 +225,20 @@ def main():
         row_stats = torch.empty((rows_total, 2), device=dev, dtype=torch.float32)
         all_stats = torch.empty((world * rows_total, 2), device=dev, dtype=torch.float32)   # rank-major [world][rows][2]
 
-    prepared = None
-    if not col_sharded:
-        prepared = [wtc.PreparedCall(A, B, O, scale, workspace=ws) for (A, B, O) in sets]
     sptr = wtc.current_stream_ptr()
+    if col_sharded:
+        shard_calls = [wtc.PreparedShardCall(A, B, O, scale, ws, row_stats, all_stats, world) for (A, B, O) in sets]
 
-    def step(i):
-        if prepared is not None:
-            prepared[i % nsets].launch(sptr)
-            return
-        A, B, O = sets[i % nsets]
-        if col_sharded:
-            d = wtc.matmul_softmax_partial(A, B, scale, O, ws, row_stats)
+        def step(i):
+            c = shard_calls[i % nsets]
+            c.partial(sptr)
             dist.all_gather_into_tensor(all_stats, row_stats)      # [M,2] f32 per rank over NVLink
-            wtc.matmul_softmax_finish(d, O, ws, all_stats, world)
-        else:
-            wtc.matmul_softmax(A, B, scale, out=O, workspace=ws)
+            c.finish(sptr)
+    else:
+        prepared = [wtc.PreparedCall(A, B, O, scale, workspace=ws) for (A, B, O) in sets]
+
+        def step(i):
+            prepared[i % nsets].launch(sptr)
 
     # ---- parity spot check on this rank's first buffer set (sampled rows, CPU checker) ----
     parity = None

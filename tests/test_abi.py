@@ -68,6 +68,10 @@ def test_plan_fallbacks_and_variants(wtc_lib):
     # tile hints: legal ones pass, others are replaced and flagged
     assert w.plan_query(w.make_desc(1, 4096, 1024, 1024, tile_m=128, tile_n=256, tile_k=64)).tile_substituted == 0
     assert w.plan_query(w.make_desc(1, 4096, 1024, 1024, tile_m=64, tile_n=128, tile_k=32)).tile_substituted == 1
+    # the second legal column tile is honoured as given: 128 columns per CTA, eight CTAs per cluster
+    p = w.plan_query(w.make_desc(1, 4096, 1024, 1024, tile_m=128, tile_n=128, tile_k=64))
+    assert (p.tile_n, p.cluster_n, p.tile_substituted, p.tmem_columns) == (128, 8, 0, 256)
+    assert w.plan_query(w.make_desc(1, 4096, 2048, 1024, tile_n=128)).kernel == w.KERNEL_TC_TILED   # 16 column blocks
 
 
 @pytest.mark.parametrize("kw", [dict(batch=0), dict(M=-1), dict(in_dtype=7), dict(variant=3), dict(tile_m=-2),

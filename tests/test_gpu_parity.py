@@ -253,6 +253,17 @@ def test_linearity_and_shift_properties(w, cuda_dev):
     assert float((p.float().sum(-1) - 1).abs().max()) <= 1e-3
 
 
+def test_tile_choice_from_best_json_is_honoured(w, cuda_dev):
+    """tileN = 128 selects the 128-column kernels (cluster of 8 for N = 1024; tiled beyond)."""
+    for M, N, K in ((4096, 1024, 1024), (300, 520, 72), (256, 2304, 128)):
+        A = oracle.normal((M, K), 61)
+        B = oracle.normal((K, N), 62)
+        ref = oracle.chain(A, B, 1 / 32)
+        _check(_run(w, cuda_dev, A, B, 1 / 32, tiles=(128, 128, 64)), ref)
+        _check(_run(w, cuda_dev, A, B, 1 / 32, tiles=(128, 256, 64)), ref)
+        _check(_run(w, cuda_dev, A, B, 1 / 32, tiles=(64, 128, 32)), ref)     # tileM / tileK replaced, tileN honoured
+
+
 # ---------------------------------------------------------------- kernel variants
 
 @pytest.mark.parametrize("env", [

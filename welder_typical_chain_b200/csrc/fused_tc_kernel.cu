@@ -845,9 +845,11 @@ cudaError_t launch_impl(const CUtensorMap &tmA, const CUtensorMap &tmB, const CU
 // alternate tiles; with one tile per CTA all eight warps share it.  store: swizzled staging +
 // TMA stores by default, direct register stores on request.
 cudaError_t launch_fused_cluster(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO,
-                                 const TcParams &p, int cluster_n, int num_sms, cudaStream_t s,
+                                 const TcParams &p, int bn, int cluster_n, int num_sms, cudaStream_t s,
                                  TcLaunchInfo *info) {
   if (cluster_n < 1 || cluster_n > kMaxCluster) return cudaErrorInvalidValue;
+  // 128-column tiles (a tile choice of best.json): the default schedule only
+  if (bn == 128) return launch_impl<128, 4, true, 2, false, false, 8>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
   const bool pair = p.pair_mode == 2 && 2 * cluster_n <= kMaxCluster;
   const int row_units = p.batch * (pair ? (p.num_rb + 1) / 2 : p.num_rb);
   const int resident = num_sms / (cluster_n * (pair ? 2 : 1));
@@ -874,7 +876,8 @@ cudaError_t launch_fused_cluster(const CUtensorMap &tmA, const CUtensorMap &tmB,
 }
 
 cudaError_t launch_tiled_partial(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO,
-                                 const TcParams &p, int num_sms, cudaStream_t s, TcLaunchInfo *info) {
+                                 const TcParams &p, int bn, int num_sms, cudaStream_t s, TcLaunchInfo *info) {
+  if (bn == 128) return launch_impl<128, 6, false, 1, false, false, 8>(tmA, tmB, tmO, p, 1, num_sms, s, info);
   const bool pair = p.pair_mode == 2 || (p.pair_mode == 0 && p.num_rb >= 2 && p.num_kb >= 8);
   const int items = p.batch * (pair ? (p.num_rb + 1) / 2 : p.num_rb) * p.num_nb;
   const bool pipe = p.epilogue_mode == 2;

@@ -50,12 +50,12 @@ struct TcLaunchInfo {
 // Fused cluster kernel: a cluster of ceil(N/BN) CTAs owns 128 full rows, exchanges
 // per-row (max, sum) through distributed shared memory and writes probabilities.
 cudaError_t launch_fused_cluster(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO,
-                                 const TcParams &p, int cluster_n, int num_sms, cudaStream_t s,
+                                 const TcParams &p, int bn, int cluster_n, int num_sms, cudaStream_t s,
                                  TcLaunchInfo *info);
 // Tiled kernel: independent 128 x BN tiles write exp(v - tile max) and per-tile
 // (max, sum); rescale_rows() then normalises the rows.
 cudaError_t launch_tiled_partial(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO,
-                                 const TcParams &p, int num_sms, cudaStream_t s, TcLaunchInfo *info);
+                                 const TcParams &p, int bn, int num_sms, cudaStream_t s, TcLaunchInfo *info);
 
 // rows = batch*M.  tile_stats [rows][num_nb].  row_stats_out (optional) receives
 // the per-row combination over this launch's tiles.  global_stats (optional):

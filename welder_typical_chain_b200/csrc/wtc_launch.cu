@@ -47,6 +47,7 @@ const int g_use_pdl = [] { const char *e = getenv("WTC_NO_PDL"); return (e && e[
 struct Resolved {
   wtc_chain_desc d;  // strides filled in
   wtc_plan_info plan;
+  int bn;            // column tile of the tensor-core kernels: 256, or 128 when best.json asks for it
   int num_rb, num_nb, num_kb;
   bool b_batched;
   bool tc_ok;
@@ -83,7 +84,9 @@ int resolve(const wtc_chain_desc *in, Resolved &r) {
   memset(&p, 0, sizeof(p));
   p.cluster_n = 1;
   r.num_rb = static_cast<int>((d.M + wtc::kTcBlockM - 1) / wtc::kTcBlockM);
-  r.num_nb = static_cast<int>((d.N + wtc::kTcBlockN - 1) / wtc::kTcBlockN);
+  // tileN = 128 is the second legal column tile; everything else resolves to 256
+  r.bn = d.tile_n == 128 ? 128 : wtc::kTcBlockN;
+  r.num_nb = static_cast<int>((d.N + r.bn - 1) / r.bn);
   r.num_kb = static_cast<int>((d.K + wtc::kTcBlockK - 1) / wtc::kTcBlockK);
 
   const bool tc_shape = d.in_dtype == WTC_F16 && d.out_dtype == WTC_F16 && d.M > 0 && d.N > 0 && d.K > 0 &&
@@ -100,9 +103,9 @@ int resolve(const wtc_chain_desc *in, Resolved &r) {
     p.workspace_bytes = (2 * rows * d.N + 2 * rows) * sizeof(float);
     p.tile_m = 8; p.tile_n = static_cast<int32_t>(d.N); p.tile_k = 64;
   } else if (r.tc_ok) {
-    p.tile_m = wtc::kTcBlockM; p.tile_n = wtc::kTcBlockN; p.tile_k = wtc::kTcBlockK;
+    p.tile_m = wtc::kTcBlockM; p.tile_n = r.bn; p.tile_k = wtc::kTcBlockK;
     p.threads = 320;
-    p.tmem_columns = 2 * wtc::kTcBlockN;
+    p.tmem_columns = 2 * r.bn;
     if (r.num_nb <= 8 && !(d.flags & WTC_FLAG_FORCE_TILED)) {
       p.kernel = WTC_KERNEL_TC_CLUSTER;
       p.launches = 1;
@@ -279,7 +282,7 @@ int launch_resolved(Resolved &r, const void *A, const void *B, void *Out, void *
     cudaError_t e;
     if (!tiled) {
       p.num_items = d.batch * r.num_rb;
-      e = wtc::launch_fused_cluster(tmA, tmB, tmO, p, r.num_nb, sms, s, &info);
+      e = wtc::launch_fused_cluster(tmA, tmB, tmO, p, r.bn, r.num_nb, sms, s, &info);
       if (e != cudaSuccess) return cuda_fail(e, "fused cluster kernel launch");
       return WTC_OK;
     }
@@ -287,7 +290,7 @@ int launch_resolved(Resolved &r, const void *A, const void *B, void *Out, void *
     if (!ws || ws_bytes < need) return fail(WTC_E_WORKSPACE, "tiled schedule needs %zu workspace bytes, got %zu", need, ws_bytes);
     p.num_items = d.batch * r.num_rb * r.num_nb;
     p.tile_stats = static_cast<float2 *>(ws);
-    e = wtc::launch_tiled_partial(tmA, tmB, tmO, p, sms, s, &info);
+    e = wtc::launch_tiled_partial(tmA, tmB, tmO, p, r.bn, sms, s, &info);
     if (e != cudaSuccess) return cuda_fail(e, "tiled kernel launch");
     const int64_t rows = static_cast<int64_t>(d.batch) * d.M;
     if (mode == 1) {
@@ -297,7 +300,7 @@ int launch_resolved(Resolved &r, const void *A, const void *B, void *Out, void *
       return e == cudaSuccess ? WTC_OK : cuda_fail(e, "row statistics launch");
     }
     if (d.o_batch_stride != d.M * d.ldo && d.batch > 1) return fail(WTC_E_UNSUPPORTED, "tiled schedule needs densely stacked output batches");
-    e = wtc::launch_rescale_rows(Out, rows, (int)d.N, d.ldo, wtc::kTcBlockN, r.num_nb, p.tile_stats, nullptr, 0, s);
+    e = wtc::launch_rescale_rows(Out, rows, (int)d.N, d.ldo, r.bn, r.num_nb, p.tile_stats, nullptr, 0, s);
     return e == cudaSuccess ? WTC_OK : cuda_fail(e, "row rescale launch");
   }
 
@@ -365,7 +368,7 @@ int wtc_matmul_softmax_finish_launch(const wtc_chain_desc *desc, void *Out, cons
   if (r.d.M == 0 || r.d.N == 0) return WTC_OK;
   if (!Out || !workspace || !all_stats || num_parts < 1) return fail(WTC_E_ARG, "null pointer or num_parts < 1");
   const int64_t rows = static_cast<int64_t>(r.d.batch) * r.d.M;
-  cudaError_t e = wtc::launch_rescale_rows(Out, rows, (int)r.d.N, r.d.ldo, wtc::kTcBlockN, r.num_nb,
+  cudaError_t e = wtc::launch_rescale_rows(Out, rows, (int)r.d.N, r.d.ldo, r.bn, r.num_nb,
                                            static_cast<const float2 *>(workspace), static_cast<const float2 *>(all_stats),
                                            num_parts, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? WTC_OK : cuda_fail(e, "row rescale launch");

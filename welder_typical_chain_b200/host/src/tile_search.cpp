@@ -94,7 +94,7 @@ std::vector<Candidate> enumerateCandidates(const ir::ChainSpec &spec, const Arch
         c.threadTileM = 1; c.threadTileN = std::max<int64_t>(1, tn / 2);   // one epilogue thread: one row x half the tile
         c.stages = static_cast<int>(stages);
         c.clusterN = twoPass ? 1 : static_cast<int>(clusterN);
-        c.implemented = f16 && tm == 128 && tn == 256 && tk == 64;
+        c.implemented = f16 && tm == 128 && (tn == 256 || tn == 128) && tk == 64;   // tile shapes the kernel library has
         c.bytesA = bytesA; c.bytesB = bytesB; c.bytesC = bytesC; c.bytesCut = bytesCut;
         c.score = (bytesA + bytesB + bytesC + bytesCut) * waves;
         // latency model: the slowest of tensor time (M=64 MMAs run at half rate), L2 operand feed,

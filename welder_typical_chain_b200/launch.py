@@ -245,6 +245,33 @@ class PreparedCall:
             _check(rc)
 
 
+class PreparedShardCall:
+    """One column shard of the chain with every argument converted once: partial(stream)
+    leaves exp values in `out` and the shard's per-row (max, sum) in `row_stats`;
+    finish(stream) normalises `out` against the gathered pairs of all shards."""
+
+    def __init__(self, A, B, out, scale, workspace, row_stats, all_stats, num_parts, acc_dtype: int = F32):
+        self.desc = _desc_for(A, B, F16, scale, acc_dtype, VARIANT_FUSED, 0, None)
+        self._keep = (A, B, out, workspace, row_stats, all_stats)
+        L = lib()
+        self._partial, self._finish = L.wtc_matmul_softmax_partial_launch, L.wtc_matmul_softmax_finish_launch
+        ws_len = workspace.numel() * workspace.element_size()
+        self._pargs = (C.byref(self.desc), C.c_void_p(A.data_ptr()), C.c_void_p(B.data_ptr()), C.c_void_p(out.data_ptr()),
+                       C.c_void_p(workspace.data_ptr()), ws_len, C.c_void_p(row_stats.data_ptr()))
+        self._fargs = (C.byref(self.desc), C.c_void_p(out.data_ptr()), C.c_void_p(workspace.data_ptr()),
+                       C.c_void_p(all_stats.data_ptr()), num_parts)
+
+    def partial(self, stream_ptr) -> None:
+        rc = self._partial(*self._pargs, stream_ptr, None)
+        if rc != 0:
+            _check(rc)
+
+    def finish(self, stream_ptr) -> None:
+        rc = self._finish(*self._fargs, stream_ptr)
+        if rc != 0:
+            _check(rc)
+
+
 def current_stream_ptr():
     return _stream_ptr()
 
