@@ -59,7 +59,8 @@ def test_plan_fallbacks_and_variants(wtc_lib):
     assert w.plan_query(w.make_desc(1, 128, 128, 128, w.F32, w.F32)).kernel == w.KERNEL_SIMT_FUSED
     assert w.plan_query(w.make_desc(1, 100, 70, 64)).kernel == w.KERNEL_SIMT_FUSED        # N % 8 != 0
     assert w.plan_query(w.make_desc(1, 100, 72, 60)).kernel == w.KERNEL_SIMT_FUSED        # K % 8 != 0
-    assert w.plan_query(w.make_desc(1, 100, 72, 64, out_dtype=w.F32)).kernel == w.KERNEL_SIMT_FUSED
+    assert w.plan_query(w.make_desc(1, 100, 72, 64, out_dtype=w.F32)).kernel == w.KERNEL_TC_CLUSTER   # f16 in, f32 out
+    assert w.plan_query(w.make_desc(1, 100, 72, 64, out_dtype=w.F32, tile_n=128)).tile_n == 256       # f32 output: 256-column tiles only
     assert w.plan_query(w.make_desc(1, 100, 72, 64, flags=w.FLAG_FORCE_SIMT)).kernel == w.KERNEL_SIMT_FUSED
     assert w.plan_query(w.make_desc(1, 100, 512, 64, flags=w.FLAG_FORCE_TILED)).kernel == w.KERNEL_TC_TILED
     p = w.plan_query(w.make_desc(2, 100, 72, 64, variant=w.VARIANT_BASELINE))

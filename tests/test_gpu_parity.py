@@ -253,6 +253,20 @@ def test_linearity_and_shift_properties(w, cuda_dev):
     assert float((p.float().sum(-1) - 1).abs().max()) <= 1e-3
 
 
+@pytest.mark.parametrize("M,N,K,flags", [(8192, 128, 64, 0), (777, 1024, 136, 0), (200, 520, 72, 0), (300, 1024, 256, "tiled"),
+                                           (64, 4096, 128, 0)])
+def test_f32_probabilities_on_the_tensor_core_path(w, cuda_dev, M, N, K, flags):
+    """f16 operands, f32 result (the reference's f16-native chain returns f32)."""
+    fl = w.FLAG_FORCE_TILED if flags == "tiled" else 0
+    assert w.plan_query(w.make_desc(1, M, N, K, out_dtype=w.F32, flags=fl)).kernel in (w.KERNEL_TC_CLUSTER, w.KERNEL_TC_TILED)
+    A = oracle.normal((M, K), 71)
+    B = oracle.normal((K, N), 72)
+    out = _run(w, cuda_dev, A, B, 0.11, out_dtype=w.F32, flags=fl)
+    assert out.dtype == np.float32
+    r = _check(out, oracle.chain(A, B, 0.11))
+    assert r["max_abs"] < 2e-5          # no f16 rounding of the result
+
+
 def test_tile_choice_from_best_json_is_honoured(w, cuda_dev):
     """tileN = 128 selects the 128-column kernels (cluster of 8 for N = 1024; tiled beyond)."""
     for M, N, K in ((4096, 1024, 1024), (300, 520, 72), (256, 2304, 128)):

@@ -81,7 +81,7 @@ def test_named_softmax_is_decomposed(tmp_path):
 def test_every_shipped_chain_compiles_to_the_expected_kernel(tmp_path):
     expect = {"cfg1_decomposed_f32_128": "simt_fused", "cfg2_f16_native_4096x1024x1024": "tc_cluster",
               "cfg3_batched_attention_named": "tc_cluster", "cfg4_vocab_logits": "tc_tiled", "cfg5_skinny_decode": "tc_tiled",
-              "matmul_softmax_chain": "simt_fused", "matmul_softmax_chain_f16_native": "simt_fused",
+              "matmul_softmax_chain": "simt_fused", "matmul_softmax_chain_f16_native": "tc_cluster",
               "matmul_softmax_chain_named_softmax": "simt_fused"}
     for stem, kernel in expect.items():
         out = tmp_path / stem

@@ -45,7 +45,7 @@ constexpr int kMaxCluster = 8;
 
 // OUT_TILES: 32-row x 64-column f16 staging tiles per epilogue warp (2 = the warp's two
 // column groups never wait for each other's TMA read; 1 = smaller, leaves room for a stage).
-template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool PIPE, bool PAIR, int EW>
+template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool PIPE, bool PAIR, int EW, bool OUT32 = false>
 struct SmemLayout {
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BK * BN * 2 / (PAIR ? 2 : 1);     // a CTA pair splits B's columns between its two CTAs
@@ -83,6 +83,17 @@ __device__ __forceinline__ void stage_row_chunk(uint8_t *tile, int lane, int hal
   }
 }
 
+// f32 output: one thread's 32 consecutive f32 columns (128 B) fill its whole row of a
+// 128-byte-swizzled 32-row x 32-column staging tile.
+__device__ __forceinline__ void stage_row_f32(uint8_t *tile, int lane, const float (&v)[32]) {
+  uint8_t *row = tile + lane * 128;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int phys = (j ^ (lane & 7)) * 16;
+    *reinterpret_cast<float4 *>(row + phys) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+  }
+}
+
 __device__ __forceinline__ void stamp(long long *timeline, int slot) {
   if (timeline) timeline[static_cast<size_t>(blockIdx.x) * 16 + slot] = static_cast<long long>(globaltimer_ns());
 }
@@ -96,16 +107,17 @@ __device__ __forceinline__ void stamp_fine(const TcParams &p, int seq, int k) {
   if (p.timeline && p.timeline_mode == 2 && (seq == 1 || seq == 2)) stamp(p.timeline, (seq - 1) * 8 + k);
 }
 
-template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool PIPE, bool PAIR, int EW>
+template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool PIPE, bool PAIR, int EW, bool OUT32 = false>
 __global__ void __launch_bounds__(kThreadsFor(EW), 1)
 fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmO, const TcParams p) {
-  using L = SmemLayout<BN, STAGES, CLUSTER, OUT_TILES, PIPE, PAIR, EW>;
+  using L = SmemLayout<BN, STAGES, CLUSTER, OUT_TILES, PIPE, PAIR, EW, OUT32>;
   constexpr int HC = L::kHalfCols;      // columns per epilogue thread
   constexpr int NCH = HC / 32;          // 32-column chunks per epilogue thread
   constexpr int kEpiThreads = EW * 32;
   constexpr int PARTS = BN / HC;        // threads that share a row (split epilogue)
   static_assert(!PIPE || EW == 8, "the tile-pipelined epilogue uses two groups of four warps");
+  static_assert(!OUT32 || (!PIPE && !PAIR && EW == 8 && OUT_TILES >= 1), "f32 output: the eight-warp split epilogue with staged stores");
   static_assert(EW == 8 || (CLUSTER && OUT_TILES == 1 && !PAIR), "sixteen epilogue warps: cluster flavour with staged stores only");
   // The 128-byte swizzle needs the stage buffers on 1024-byte boundaries.  There is no
   // static shared memory in this kernel, so the dynamic window starts aligned; if it ever
@@ -701,7 +713,28 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       if (lead) stamp_fine(p, it, 5);              // row statistics combined, factor known
       // ---- p = e * f -> f16 -> global memory ----
       float sum_r = 0.f;                           // tiled: sum of what is actually stored
-      if (OUT_TILES == 0) {
+      if (OUT32) {
+        // f32 probabilities: 32 columns (one 128-byte row) per staging tile and TMA store
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+          if (c * 32 < valid) {
+            uint8_t *tile = stg + (OUT_TILES == 2 ? (gcount & 1) * 4096 : 0);
+            if (lane == 0) { if (OUT_TILES == 2) tma_store_wait_read1(); else tma_store_wait_read(); }
+            __syncwarp();
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) { v[i] = __uint_as_float(r[c][i]) * f; if (!CLUSTER) sum_r += v[i]; }
+            stage_row_f32(tile, lane, v);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              if (rows_live) tma_store_3d(&tmO, tile, col0 + c * 32, row0, b);
+              tma_store_commit();
+            }
+            ++gcount;
+          }
+        }
+      } else if (OUT_TILES == 0) {
         // straight from registers: each thread owns 256 contiguous bytes of its row
         const int row = rb * BM + row_in_tile;
         __half *orow = static_cast<__half *>(p.out) + static_cast<long long>(b) * p.o_batch_stride + static_cast<long long>(row) * p.ldo + col0;
@@ -778,11 +811,11 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   if (warp == 1) { if (PAIR) tmem_dealloc_pair(tmem_base, 2 * BN); else tmem_dealloc(tmem_base, 2 * BN); }
 }
 
-template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool PIPE, bool PAIR, int EW>
+template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool PIPE, bool PAIR, int EW, bool OUT32 = false>
 cudaError_t launch_impl(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO, TcParams p,
                         int cluster_n, int num_sms, cudaStream_t s, TcLaunchInfo *info) {
-  using L = SmemLayout<BN, STAGES, CLUSTER, OUT_TILES, PIPE, PAIR, EW>;
-  auto kern = fused_tc_kernel<BN, STAGES, CLUSTER, OUT_TILES, PIPE, PAIR, EW>;
+  using L = SmemLayout<BN, STAGES, CLUSTER, OUT_TILES, PIPE, PAIR, EW, OUT32>;
+  auto kern = fused_tc_kernel<BN, STAGES, CLUSTER, OUT_TILES, PIPE, PAIR, EW, OUT32>;
   static bool attr_set = false;   // per template instance
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
@@ -848,6 +881,7 @@ cudaError_t launch_fused_cluster(const CUtensorMap &tmA, const CUtensorMap &tmB,
                                  const TcParams &p, int bn, int cluster_n, int num_sms, cudaStream_t s,
                                  TcLaunchInfo *info) {
   if (cluster_n < 1 || cluster_n > kMaxCluster) return cudaErrorInvalidValue;
+  if (p.out_f32) return launch_impl<kTcBlockN, 3, true, 2, false, false, 8, true>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
   // 128-column tiles (a tile choice of best.json): the default schedule only
   if (bn == 128) return launch_impl<128, 4, true, 2, false, false, 8>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
   const bool pair = p.pair_mode == 2 && 2 * cluster_n <= kMaxCluster;
@@ -877,6 +911,7 @@ cudaError_t launch_fused_cluster(const CUtensorMap &tmA, const CUtensorMap &tmB,
 
 cudaError_t launch_tiled_partial(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO,
                                  const TcParams &p, int bn, int num_sms, cudaStream_t s, TcLaunchInfo *info) {
+  if (p.out_f32) return launch_impl<kTcBlockN, 4, false, 1, false, false, 8, true>(tmA, tmB, tmO, p, 1, num_sms, s, info);
   if (bn == 128) return launch_impl<128, 6, false, 1, false, false, 8>(tmA, tmB, tmO, p, 1, num_sms, s, info);
   const bool pair = p.pair_mode == 2 || (p.pair_mode == 0 && p.num_rb >= 2 && p.num_kb >= 8);
   const int items = p.batch * (pair ? (p.num_rb + 1) / 2 : p.num_rb) * p.num_nb;

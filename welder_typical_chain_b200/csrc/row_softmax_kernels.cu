@@ -38,7 +38,7 @@ __global__ void row_stats_kernel(const float2 *__restrict__ tile_stats, float2 *
 
 // one CTA per row
 __global__ void __launch_bounds__(256)
-rescale_rows_kernel(__half *__restrict__ out, int N, int64_t ld_out, int BN, int num_nb,
+rescale_rows_kernel(void *__restrict__ out_v, int out_f32, int N, int64_t ld_out, int BN, int num_nb,
                     const float2 *__restrict__ tile_stats, const float2 *__restrict__ global_stats,
                     int num_parts, int64_t rows) {
   extern __shared__ float factor[];          // [num_nb]
@@ -69,6 +69,22 @@ rescale_rows_kernel(__half *__restrict__ out, int N, int64_t ld_out, int BN, int
     factor[t] = ex2_approx(tile_stats[row * num_nb + t].x - gm) * inv;
   __syncthreads();
 
+  if (out_f32) {
+    float *frow = static_cast<float *>(out_v) + row * ld_out;
+    if ((N % 4 == 0) && (ld_out % 4 == 0) && ((reinterpret_cast<uintptr_t>(out_v) & 15) == 0) && (BN % 4 == 0)) {
+      float4 *o4 = reinterpret_cast<float4 *>(frow);
+      for (int j = threadIdx.x; j < N / 4; j += blockDim.x) {
+        const float fct = factor[(j * 4) / BN];
+        float4 x = o4[j];
+        x.x *= fct; x.y *= fct; x.z *= fct; x.w *= fct;
+        o4[j] = x;
+      }
+    } else {
+      for (int j = threadIdx.x; j < N; j += blockDim.x) frow[j] *= factor[j / BN];
+    }
+    return;
+  }
+  __half *out = static_cast<__half *>(out_v);
   __half *orow = out + row * ld_out;
   const bool vec_ok = (N % 8 == 0) && (ld_out % 8 == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0) && (BN % 8 == 0);
   if (vec_ok) {
@@ -109,7 +125,7 @@ cudaError_t launch_row_stats(const float2 *tile_stats, float2 *row_stats_out, in
   return cudaLaunchKernelEx(&cfg, row_stats_kernel, tile_stats, row_stats_out, rows, num_nb);
 }
 
-cudaError_t launch_rescale_rows(void *out_f16, int64_t rows, int N, int64_t ld_out, int BN, int num_nb,
+cudaError_t launch_rescale_rows(void *out, int out_f32, int64_t rows, int N, int64_t ld_out, int BN, int num_nb,
                                 const float2 *tile_stats, const float2 *global_stats, int num_parts,
                                 cudaStream_t s) {
   if (rows <= 0) return cudaSuccess;
@@ -123,7 +139,7 @@ cudaError_t launch_rescale_rows(void *out_f16, int64_t rows, int N, int64_t ld_o
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, rescale_rows_kernel, static_cast<__half *>(out_f16), N, ld_out, BN, num_nb, tile_stats,
+  return cudaLaunchKernelEx(&cfg, rescale_rows_kernel, out, out_f32, N, ld_out, BN, num_nb, tile_stats,
                             global_stats, num_parts, rows);
 }
 

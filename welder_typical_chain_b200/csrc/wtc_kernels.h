@@ -26,6 +26,7 @@ struct TcParams {
   int group_rb;    // tiled mode: row blocks per rasterisation group
   void *out;       // output base, row stride and batch stride (elements) for the direct-store epilogue
   long long ldo, o_batch_stride;
+  int out_f32;     // f32 probabilities (else f16)
   int out_align32; // every output row starts on a 32-byte boundary
   int store_mode;  // 0 direct register->global stores, 1 swizzled shared staging + TMA stores
   int debug_flags; // bring-up experiments: 1 = drop the epilogue stores
@@ -63,7 +64,7 @@ cudaError_t launch_tiled_partial(const CUtensorMap &tmA, const CUtensorMap &tmB,
 // given, rows are normalised against their combination instead of the local one.
 cudaError_t launch_row_stats(const float2 *tile_stats, float2 *row_stats_out, int64_t rows, int num_nb,
                              cudaStream_t s);
-cudaError_t launch_rescale_rows(void *out_f16, int64_t rows, int N, int64_t ld_out, int BN, int num_nb,
+cudaError_t launch_rescale_rows(void *out, int out_f32, int64_t rows, int N, int64_t ld_out, int BN, int num_nb,
                                 const float2 *tile_stats, const float2 *global_stats, int num_parts,
                                 cudaStream_t s);
 

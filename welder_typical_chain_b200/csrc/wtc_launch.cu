@@ -85,11 +85,11 @@ int resolve(const wtc_chain_desc *in, Resolved &r) {
   p.cluster_n = 1;
   r.num_rb = static_cast<int>((d.M + wtc::kTcBlockM - 1) / wtc::kTcBlockM);
   // tileN = 128 is the second legal column tile; everything else resolves to 256
-  r.bn = d.tile_n == 128 ? 128 : wtc::kTcBlockN;
+  r.bn = (d.tile_n == 128 && d.out_dtype == WTC_F16) ? 128 : wtc::kTcBlockN;
   r.num_nb = static_cast<int>((d.N + r.bn - 1) / r.bn);
   r.num_kb = static_cast<int>((d.K + wtc::kTcBlockK - 1) / wtc::kTcBlockK);
 
-  const bool tc_shape = d.in_dtype == WTC_F16 && d.out_dtype == WTC_F16 && d.M > 0 && d.N > 0 && d.K > 0 &&
+  const bool tc_shape = d.in_dtype == WTC_F16 && d.M > 0 && d.N > 0 && d.K > 0 &&
                         mult8(d.K) && mult8(d.N) && mult8(d.lda) && mult8(d.ldb) && mult8(d.ldo) &&
                         mult8(d.a_batch_stride) && mult8(d.b_batch_stride) && mult8(d.o_batch_stride) &&
                         static_cast<int64_t>(d.batch) * r.num_rb * r.num_nb < 0x7fffffff;
@@ -162,8 +162,8 @@ constexpr size_t kMaxMaps = 256;
 
 // rank-3 f16 tensor (d0 innermost, contiguous), 128-byte swizzle, zero fill
 int get_map(const void *ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1_bytes, uint64_t s2_bytes, uint32_t b0,
-            uint32_t b1, CUtensorMap *out) {
-  MapKey key{ptr, d0, d1, d2, s1_bytes, s2_bytes, b0, b1};
+            uint32_t b1, CUtensorMap *out, bool f32 = false) {
+  MapKey key{ptr, d0, d1, d2, s1_bytes, s2_bytes, b0 | (f32 ? 0x80000000u : 0u), b1};
   std::lock_guard<std::mutex> lk(g_mu);
   for (size_t i = g_maps.size(); i-- > 0;)
     if (g_maps[i].key == key) { *out = g_maps[i].map; return WTC_OK; }
@@ -174,7 +174,7 @@ int get_map(const void *ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1_
   cuuint32_t box[3] = {b0, b1, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUtensorMap m;
-  CUresult cr = g_encode(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(ptr), dims, strides, box, estr,
+  CUresult cr = g_encode(&m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(ptr), dims, strides, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (cr != CUDA_SUCCESS)
@@ -251,7 +251,9 @@ int launch_resolved(Resolved &r, const void *A, const void *B, void *Out, void *
     rc = get_map(B, d.N, d.K, r.b_batched ? d.batch : 1, d.ldb * 2, (r.b_batched ? d.b_batch_stride : d.K * d.ldb) * 2, 64,
                  wtc::kTcBlockK, &tmB);
     if (rc) return rc;
-    rc = get_map(Out, d.N, d.M, d.batch, d.ldo * 2, d.o_batch_stride * 2, 64, 32, &tmO);
+    const bool out32 = d.out_dtype == WTC_F32;
+    rc = out32 ? get_map(Out, d.N, d.M, d.batch, d.ldo * 4, d.o_batch_stride * 4, 32, 32, &tmO, true)
+               : get_map(Out, d.N, d.M, d.batch, d.ldo * 2, d.o_batch_stride * 2, 64, 32, &tmO);
     if (rc) return rc;
 
     wtc::TcParams p;
@@ -266,6 +268,8 @@ int launch_resolved(Resolved &r, const void *A, const void *B, void *Out, void *
     p.geom = g_geom;
     p.timeline = g_timeline;
     p.use_pdl = g_use_pdl;
+    p.out_f32 = out32;
+    if (out32) r.bn = wtc::kTcBlockN;   // (resolve() already forces 256 for f32 output)
     p.out = Out; p.ldo = d.ldo; p.o_batch_stride = d.o_batch_stride;
     p.out_align32 = ((reinterpret_cast<uintptr_t>(Out) & 31) == 0) && ((d.ldo & 15) == 0) && ((d.o_batch_stride & 15) == 0);
     p.stagger = 1;
@@ -300,7 +304,7 @@ int launch_resolved(Resolved &r, const void *A, const void *B, void *Out, void *
       return e == cudaSuccess ? WTC_OK : cuda_fail(e, "row statistics launch");
     }
     if (d.o_batch_stride != d.M * d.ldo && d.batch > 1) return fail(WTC_E_UNSUPPORTED, "tiled schedule needs densely stacked output batches");
-    e = wtc::launch_rescale_rows(Out, rows, (int)d.N, d.ldo, r.bn, r.num_nb, p.tile_stats, nullptr, 0, s);
+    e = wtc::launch_rescale_rows(Out, d.out_dtype == WTC_F32, rows, (int)d.N, d.ldo, r.bn, r.num_nb, p.tile_stats, nullptr, 0, s);
     return e == cudaSuccess ? WTC_OK : cuda_fail(e, "row rescale launch");
   }
 
@@ -355,7 +359,7 @@ int wtc_matmul_softmax_partial_launch(const wtc_chain_desc *desc, const void *A,
   Resolved r;
   int rc = resolve(desc, r);
   if (rc) return rc;
-  if (!r.tc_ok) return fail(WTC_E_UNSUPPORTED, "the sharded form needs f16 operands/output with 16-byte aligned rows");
+  if (!r.tc_ok) return fail(WTC_E_UNSUPPORTED, "the sharded form needs f16 operands with 16-byte aligned rows");
   return launch_resolved(r, A, B, Out, workspace, workspace_bytes, row_stats, 1, static_cast<cudaStream_t>(stream), device_status);
 }
 
@@ -368,7 +372,7 @@ int wtc_matmul_softmax_finish_launch(const wtc_chain_desc *desc, void *Out, cons
   if (r.d.M == 0 || r.d.N == 0) return WTC_OK;
   if (!Out || !workspace || !all_stats || num_parts < 1) return fail(WTC_E_ARG, "null pointer or num_parts < 1");
   const int64_t rows = static_cast<int64_t>(r.d.batch) * r.d.M;
-  cudaError_t e = wtc::launch_rescale_rows(Out, rows, (int)r.d.N, r.d.ldo, r.bn, r.num_nb,
+  cudaError_t e = wtc::launch_rescale_rows(Out, r.d.out_dtype == WTC_F32, rows, (int)r.d.N, r.d.ldo, r.bn, r.num_nb,
                                            static_cast<const float2 *>(workspace), static_cast<const float2 *>(all_stats),
                                            num_parts, static_cast<cudaStream_t>(stream));
   return e == cudaSuccess ? WTC_OK : cuda_fail(e, "row rescale launch");
