@@ -48,6 +48,7 @@ __device__ __forceinline__ void matmul_rows(const void *A, const void *B, const 
       }
       __syncthreads();
       if (j < p.N) {
+#pragma unroll 8
         for (int k = 0; k < kc; ++k) {
           const float bv = ld_elem<F16>(B, b_off + static_cast<int64_t>(k0 + k) * p.ldb + j);
 #pragma unroll
@@ -157,12 +158,18 @@ __global__ void div_kernel(const float *__restrict__ E, const float *__restrict_
 }
 
 int pick_rows(const SimtParams &p, size_t smem_limit) {
-  // largest R in {16,8,4,2,1} whose logits tile fits shared memory
+  // largest R in {16,8,4,2,1} whose logits tile fits shared memory; small problems trade rows
+  // per CTA for more CTAs (latency-bound: fill the 148 SMs before deepening the per-CTA work)
+  int best = 0;
   for (int R = 16; R >= 1; R >>= 1) {
     const size_t need = (static_cast<size_t>(R) * kKChunk + static_cast<size_t>(R) * p.N) * sizeof(float);
-    if (need <= smem_limit) return R;
+    if (need > smem_limit) continue;
+    if (!best) best = R;
+    const int64_t blocks = static_cast<int64_t>(p.batch) * ((p.M + R - 1) / R);
+    if (blocks >= 148) return R;
+    best = R;
   }
-  return 0;
+  return best;
 }
 
 template <int R>
