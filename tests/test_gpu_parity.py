@@ -288,7 +288,7 @@ def test_tile_choice_from_best_json_is_honoured(w, cuda_dev):
     {"WTC_PAIR": "1"},                              # tcgen05 cta_group::2 in the cluster flavour too
     {"WTC_PAIR": "1", "WTC_EPILOGUE": "pipe"},
     {"WTC_PAIR": "0"},                              # never pair
-    {"WTC_NO_STAGGER": "1", "WTC_STAGGER": "0", "WTC_EPILOGUE": "pipe"},
+    {"WTC_STAGGER": "0", "WTC_EPILOGUE": "pipe"},
 ])
 def test_every_kernel_variant_matches_the_checker(w, cuda_dev, monkeypatch, env):
     for k, v in env.items():

@@ -478,8 +478,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 if (!CLUSTER) { const float2 back = __half22float2(hh); sum_r += back.x + back.y; }
                 h[i >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
               }
-              if (row < p.M && !(p.debug_flags & 1)) st_global_row32(orow + col_base + c * 32, h, p.out_align32, valid - c * 32);
-              if ((p.debug_flags & 1) && h[0] == 0x12345678u && row < p.M) st_global_row32(orow + col_base + c * 32, h, p.out_align32, valid - c * 32);
+              if (row < p.M) st_global_row32(orow + col_base + c * 32, h, p.out_align32, valid - c * 32);
             }
           }
         } else {
@@ -748,8 +747,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
               if (!CLUSTER) { const float2 back = __half22float2(hh); sum_r += back.x + back.y; }
               h[i >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
             }
-            if (row < p.M && !(p.debug_flags & 1)) st_global_row32(orow + c * 32, h, p.out_align32, valid - c * 32);
-            if ((p.debug_flags & 1) && h[0] == 0x12345678u && row < p.M) st_global_row32(orow + c * 32, h, p.out_align32, valid - c * 32);
+            if (row < p.M) st_global_row32(orow + c * 32, h, p.out_align32, valid - c * 32);
           }
         }
       } else {

@@ -29,7 +29,6 @@ struct TcParams {
   int out_f32;     // f32 probabilities (else f16)
   int out_align32; // every output row starts on a 32-byte boundary
   int store_mode;  // 0 direct register->global stores, 1 swizzled shared staging + TMA stores
-  int debug_flags; // bring-up experiments: 1 = drop the epilogue stores
   int stagger;     // tile-pipelined epilogue: offset the two warp groups by one phase
   int epilogue_warps;  // 0 choose, 8 or 16 (cluster flavour with staged stores)
   int pair_mode;   // 0 choose, 1 never pair CTAs, 2 pair whenever the cluster allows

@@ -273,8 +273,6 @@ int launch_resolved(Resolved &r, const void *A, const void *B, void *Out, void *
     p.out = Out; p.ldo = d.ldo; p.o_batch_stride = d.o_batch_stride;
     p.out_align32 = ((reinterpret_cast<uintptr_t>(Out) & 31) == 0) && ((d.ldo & 15) == 0) && ((d.o_batch_stride & 15) == 0);
     p.stagger = 1;
-    if (const char *e = getenv("WTC_DEBUG_FLAGS")) p.debug_flags = atoi(e);
-    if (const char *e = getenv("WTC_DEBUG_NOALIGN32")) { if (e[0] == '1') p.out_align32 = 0; }
     if (const char *e = getenv("WTC_TL_MODE")) p.timeline_mode = atoi(e);
     if (const char *e = getenv("WTC_STAGGER")) p.stagger = e[0] != '0';
     p.store_mode = 1;
