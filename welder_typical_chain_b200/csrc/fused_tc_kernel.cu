@@ -751,17 +751,15 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           }
         }
       } else {
-        // 128-byte-swizzled staging tiles in shared memory, written out by TMA, 64 columns at a time
+        // 128-byte-swizzled staging tiles in shared memory, written out by TMA.
+        if (OUT_TILES * 2 >= NCH) {
+          // the warp's whole share of the tile fits its staging tiles: pack and stage
+          // everything, then ONE proxy fence and warp barrier, then all stores back to back
+          if (lane == 0) tma_store_wait_read();    // the previous tile's stores have read the staging tiles
+          __syncwarp();
 #pragma unroll
-        for (int g = 0; g < NCH / 2; ++g) {
-          if (g * 64 < valid) {
-            uint8_t *tile = stg + (OUT_TILES == 2 ? (gcount & 1) * 4096 : 0);   // tiles alternate per committed group
-            // the store that last used this staging tile must have read it
-            if (lane == 0) { if (OUT_TILES == 2) tma_store_wait_read1(); else tma_store_wait_read(); }
-            __syncwarp();
-#pragma unroll
-            for (int hc = 0; hc < 2; ++hc) {
-              const int c = g * 2 + hc;
+          for (int c = 0; c < NCH; ++c) {
+            if (c * 32 < valid) {
               uint32_t h[16];
 #pragma unroll
               for (int i = 0; i < 32; i += 2) {
@@ -769,16 +767,47 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 if (!CLUSTER) { const float2 back = __half22float2(hh); sum_r += back.x + back.y; }
                 h[i >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
               }
-              stage_row_chunk(tile, lane, hc, h);
+              stage_row_chunk(stg + (c >> 1) * 4096, lane, c & 1, h);
             }
-            if (lead && g == NCH / 2 - 1) stamp_fine(p, it, 6);    // last group packed and staged
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              if (rows_live) tma_store_3d(&tmO, tile, col0 + g * 64, row0, b);
-              tma_store_commit();
+          }
+          if (lead) stamp_fine(p, it, 6);          // packed and staged
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (rows_live) {
+#pragma unroll
+              for (int g = 0; g < NCH / 2; ++g)
+                if (g * 64 < valid) tma_store_3d(&tmO, stg + g * 4096, col0 + g * 64, row0, b);
             }
-            ++gcount;
+            tma_store_commit();
+          }
+        } else {
+          // fewer staging tiles than column groups: 64 columns at a time through one tile
+#pragma unroll
+          for (int g = 0; g < NCH / 2; ++g) {
+            if (g * 64 < valid) {
+              if (lane == 0) tma_store_wait_read();
+              __syncwarp();
+#pragma unroll
+              for (int hc = 0; hc < 2; ++hc) {
+                const int c = g * 2 + hc;
+                uint32_t h[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                  const __half2 hh = __floats2half2_rn(__uint_as_float(r[c][i]) * f, __uint_as_float(r[c][i + 1]) * f);
+                  if (!CLUSTER) { const float2 back = __half22float2(hh); sum_r += back.x + back.y; }
+                  h[i >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
+                }
+                stage_row_chunk(stg, lane, hc, h);
+              }
+              if (lead && g == NCH / 2 - 1) stamp_fine(p, it, 6);
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                if (rows_live) tma_store_3d(&tmO, stg, col0 + g * 64, row0, b);
+                tma_store_commit();
+              }
+            }
           }
         }
       }
