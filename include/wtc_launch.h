@@ -189,11 +189,10 @@ int wtc_matmul_softmax_time(const wtc_chain_desc *desc, const void *A, const voi
 /*
  * Kernel variants.  The launch layer picks the schedule; these environment variables,
  * read at every launch, override the choice for experiments and for the variant tests:
- *   WTC_EPILOGUE=split|pipe   all eight epilogue warps share a tile | two groups alternate tiles
+ *   WTC_EPILOGUE=split|relay  eight epilogue warps share a tile | two groups of eight overlap consecutive tiles
  *   WTC_EW=16                 sixteen epilogue warps (cluster flavour, staged stores)
  *   WTC_STORE=direct          256-bit register stores instead of staged TMA stores
  *   WTC_PAIR=0|1              never | always pair CTAs for tcgen05 cta_group::2
- *   WTC_STAGGER=0             do not offset the two groups of the pipelined epilogue
  *   WTC_NO_PDL=1              (read once at load) no programmatic dependent launch
  *   WTC_TL_MODE=0|1|2         layout of the profiling stamps (wtc_debug_set_timeline)
  */

@@ -281,14 +281,12 @@ def test_tile_choice_from_best_json_is_honoured(w, cuda_dev):
 # ---------------------------------------------------------------- kernel variants
 
 @pytest.mark.parametrize("env", [
-    {"WTC_EPILOGUE": "pipe"},                       # two warp groups alternate tiles, first half parked in TMEM
+    {"WTC_EPILOGUE": "relay"},                      # two warp groups overlap consecutive tiles, exp values parked in TMEM
     {"WTC_EW": "16"},                               # sixteen epilogue warps, a row split four ways
     {"WTC_STORE": "direct"},                        # 256-bit register->global stores instead of staged TMA stores
-    {"WTC_STORE": "direct", "WTC_EPILOGUE": "pipe"},
     {"WTC_PAIR": "1"},                              # tcgen05 cta_group::2 in the cluster flavour too
-    {"WTC_PAIR": "1", "WTC_EPILOGUE": "pipe"},
     {"WTC_PAIR": "0"},                              # never pair
-    {"WTC_STAGGER": "0", "WTC_EPILOGUE": "pipe"},
+    {"WTC_EPILOGUE": "split"},
 ])
 def test_every_kernel_variant_matches_the_checker(w, cuda_dev, monkeypatch, env):
     for k, v in env.items():

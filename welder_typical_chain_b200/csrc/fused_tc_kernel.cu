@@ -40,27 +40,32 @@ constexpr int BM = kTcBlockM;
 constexpr int BK = kTcBlockK;
 // Epilogue warps per CTA: 8 (a thread owns one row x BN/2 columns) or 16 (one row x BN/4:
 // four warps per scheduler hide the TMEM-load and barrier latencies the eight-warp form exposes).
-constexpr int kThreadsFor(int ew) { return 64 + ew * 32; }
+constexpr int kThreadsFor(int ew, bool relay = false) { return relay ? 640 : 64 + ew * 32; }
 constexpr int kMaxCluster = 8;
+// tiles per CTA from which the relay epilogue is chosen unless a form is asked for: with one tile
+// per CTA its two groups cannot overlap (measured equal to the split form on config 2)
+constexpr int kRelayMinTiles = 2;
 
 // OUT_TILES: 32-row x 64-column f16 staging tiles per epilogue warp (2 = the warp's two
 // column groups never wait for each other's TMA read; 1 = smaller, leaves room for a stage).
-template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool PIPE, bool PAIR, int EW, bool OUT32 = false>
+template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool RELAY, bool PAIR, int EW, bool OUT32 = false>
 struct SmemLayout {
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BK * BN * 2 / (PAIR ? 2 : 1);     // a CTA pair splits B's columns between its two CTAs
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kHalfCols = PIPE ? BN / 2 : BN * 4 / EW;       // columns per epilogue thread (per step)
+  static constexpr int kHalfCols = RELAY ? BN / 2 : BN * 4 / EW;       // columns per epilogue thread (per step)
   static constexpr int kOutWarpBytes = OUT_TILES * 32 * 64 * 2;      // 0: the epilogue stores straight from registers
-  static constexpr int kOutBytes = EW * kOutWarpBytes;
+  static constexpr int kOutBytes = (RELAY ? 8 : EW) * kOutWarpBytes;   // relay: only the storing group stages
   static constexpr int kPairBytes = 2 * BM * 8;                       // [half][row] float2
-  static constexpr int kStatsSets = PIPE ? 4 : 2;                      // PIPE: two per epilogue group
+  static constexpr int kStatsSets = RELAY ? 4 : 2;                     // relay: a peer may run up to three tiles ahead of this CTA's storing group
   static constexpr int kStatsBytes = CLUSTER ? kStatsSets * kMaxCluster * BM * 8 : 0;
   static constexpr int kOffOut = STAGES * kStageBytes;
   static constexpr int kOffPair = kOffOut + kOutBytes;
   static constexpr int kOffStats = kOffPair + kPairBytes;
-  static constexpr int kOffBars = kOffStats + kStatsBytes;
-  static constexpr int kNumBars = 2 * STAGES + 4 + 4 + 1;
+  static constexpr int kMhBytes = RELAY ? 2 * 2 * BM * 4 : 0;         // relay: [tile parity][half][row] half-row maxima
+  static constexpr int kOffMh = kOffStats + kStatsBytes;
+  static constexpr int kOffBars = kOffMh + kMhBytes;
+  static constexpr int kNumBars = 2 * STAGES + 4 + 4 + 2;
   static constexpr int kOffTmemSlot = kOffBars + kNumBars * 8;
   static constexpr int kTotal = kOffTmemSlot + 16;
   static constexpr int kDynamic = kTotal;
@@ -101,23 +106,24 @@ __device__ __forceinline__ void stamp(long long *timeline, int slot) {
 // Second stamp layout (timeline_mode 1): four points of the first four tiles one thread sees.
 __device__ __forceinline__ void stamp_tile(const TcParams &p, int seq, int k) {
   if (p.timeline && p.timeline_mode == 1 && seq < 4) stamp(p.timeline, seq * 4 + k);
+  if (p.timeline && p.timeline_mode == 3 && seq >= 20 && seq < 24) stamp(p.timeline, (seq - 20) * 4 + k);   // same, steady state
 }
 // Third layout (timeline_mode 2): eight points of the second and third tile one thread sees.
 __device__ __forceinline__ void stamp_fine(const TcParams &p, int seq, int k) {
   if (p.timeline && p.timeline_mode == 2 && (seq == 1 || seq == 2)) stamp(p.timeline, (seq - 1) * 8 + k);
 }
 
-template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool PIPE, bool PAIR, int EW, bool OUT32 = false>
-__global__ void __launch_bounds__(kThreadsFor(EW), 1)
+template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool RELAY, bool PAIR, int EW, bool OUT32 = false>
+__global__ void __launch_bounds__(kThreadsFor(EW, RELAY), 1)
 fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmO, const TcParams p) {
-  using L = SmemLayout<BN, STAGES, CLUSTER, OUT_TILES, PIPE, PAIR, EW, OUT32>;
+  using L = SmemLayout<BN, STAGES, CLUSTER, OUT_TILES, RELAY, PAIR, EW, OUT32>;
   constexpr int HC = L::kHalfCols;      // columns per epilogue thread
   constexpr int NCH = HC / 32;          // 32-column chunks per epilogue thread
   constexpr int kEpiThreads = EW * 32;
   constexpr int PARTS = BN / HC;        // threads that share a row (split epilogue)
-  static_assert(!PIPE || EW == 8, "the tile-pipelined epilogue uses two groups of four warps");
-  static_assert(!OUT32 || (!PIPE && !PAIR && EW == 8 && OUT_TILES >= 1), "f32 output: the eight-warp split epilogue with staged stores");
+  static_assert(!RELAY || (EW == 16 && CLUSTER && !PAIR && OUT_TILES == 1 && !OUT32), "relay epilogue: cluster flavour, f16 staged stores, sixteen warps");
+  static_assert(!OUT32 || (!RELAY && !PAIR && EW == 8 && OUT_TILES >= 1), "f32 output: the eight-warp split epilogue with staged stores");
   static_assert(EW == 8 || (CLUSTER && OUT_TILES == 1 && !PAIR), "sixteen epilogue warps: cluster flavour with staged stores only");
   // The 128-byte swizzle needs the stage buffers on 1024-byte boundaries.  There is no
   // static shared memory in this kernel, so the dynamic window starts aligned; if it ever
@@ -131,7 +137,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   uint64_t *accum_full = bars + 2 * STAGES;
   uint64_t *accum_empty = bars + 2 * STAGES + 2;
   uint64_t *stats_bar = bars + 2 * STAGES + 4;
-  uint64_t *stagger_bar = bars + 2 * STAGES + 8;
+  uint64_t *xdone = bars + 2 * STAGES + 8;                         // relay: first group -> second group, per accumulator buffer
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + L::kOffTmemSlot);
   float2 *pair = reinterpret_cast<float2 *>(smem + L::kOffPair);    // [2][BM]
   float2 *stats = reinterpret_cast<float2 *>(smem + L::kOffStats);  // [2][kMaxCluster][BM]
@@ -154,10 +160,10 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&accum_full[i], 1);
-      mbar_init(&accum_empty[i], (PIPE ? kEpiThreads / 2 : kEpiThreads) * (PAIR ? 2 : 1));
+      mbar_init(&accum_empty[i], (RELAY ? kEpiThreads / 2 : kEpiThreads) * (PAIR ? 2 : 1));
+      mbar_init(&xdone[i], kEpiThreads / 2);
     }
     for (int i = 0; i < 4; ++i) mbar_init(&stats_bar[i], 1);
-    mbar_init(stagger_bar, kEpiThreads / 2);
     mbar_fence_init();
     tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); tma_prefetch_desc(&tmO);
   }
@@ -225,6 +231,283 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     inv_gl = rcp_approx(((t[0] + t[1]) + (t[2] + t[3])) + ((t[4] + t[5]) + (t[6] + t[7])));
   };
 
+  // Relay epilogue: register reallocation between aligned groups of four warps.  The exp
+  // group needs a whole row share (128 values) in registers, the others need little; each
+  // role's code sits under its own reallocation so the allocator sees one budget per region.
+  const int relay_role = !RELAY ? 0 : (warp < 4 ? 0 : (warp < 12 ? 1 : 2));
+  if (RELAY && relay_role == 1) {
+    setmaxnreg_inc<152>();
+    // ======================= softmax epilogue, two-stage relay ==============
+    // Two groups of eight epilogue warps work on consecutive tiles at the same time.  The
+    // first group (warps 4-11, 152 registers a thread after the reallocation above) turns
+    // the accumulator into exp values in place in tensor memory and sends the row
+    // statistics round the cluster; the second group (warps 12-19, 64 registers) waits for
+    // the cluster's statistics, reads the exp values back 32 columns at a time, scales,
+    // packs and stores them.  The exchange latency and the store phase of tile i are
+    // hidden behind the exp phase of tile i+1.  Warps 2 and 3 only fill up the first
+    // warpgroup (register reallocation works on aligned groups of four warps).
+    const int q = warp & 3;                       // TMEM lane quarter this warp may touch
+    const int row_in_tile = q * 32 + lane;
+    const float c2 = p.c2;
+    const bool pos = c2 >= 0.f;
+    float *mh = reinterpret_cast<float *>(smem + L::kOffMh);   // [2][2][BM]: each half's own maximum, per tile parity
+    // ---------------- first group: max, exp in place, statistics out ----------------
+    const int half = (warp - 4) >> 2;
+    const bool stamper = threadIdx.x == 128;
+    float2 *mine = &pair[half * BM + row_in_tile];
+    const float2 *other = &pair[(half ^ 1) * BM + row_in_tile];
+    for (int it = 0; first + it * stride < p.num_items; ++it) {
+      const int w = first + it * stride;
+      int b, rb, nb; decode(w, b, rb, nb);
+      const int ab = it & 1;
+      const uint32_t tile_phase = (it >> 1) & 1;
+      const int sset = it & 3;
+      if (!mbar_wait(&accum_full[ab], tile_phase)) { record_failure(p.status, WTC_DEV_TIMEOUT_ACCUM); break; }
+      tc_fence_after_sync();
+      if (stamper && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 1);
+      if (stamper) { stamp_tile(p, it, 0); stamp_fine(p, it, 0); }
+      const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ab * BN + half * HC;
+      const int col0 = nb * BN + half * HC;
+      const int valid = max(0, min(HC, p.N - col0));
+      uint32_t r[NCH][32];
+      float m_half;
+      if (valid == HC && !p.round_logits_f16) {
+        // whole share, no rounding: the second half of the loads is in flight while the
+        // extreme of the first half is taken
+        float m0, m1, m2, m3;
+        auto fold = [&](const uint32_t (&v)[32]) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            if (pos) {
+              m0 = max3(m0, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+              m1 = max3(m1, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+              m2 = max3(m2, __uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+              m3 = max3(m3, __uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+            } else {
+              m0 = min3(m0, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+              m1 = min3(m1, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+              m2 = min3(m2, __uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+              m3 = min3(m3, __uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+            }
+          }
+        };
+#pragma unroll
+        for (int c = 0; c < NCH / 2; ++c) tmem_ld_32x32b_x32(tbase + c * 32, r[c]);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = NCH / 2; c < NCH; ++c) tmem_ld_32x32b_x32(tbase + c * 32, r[c]);
+        m0 = __uint_as_float(r[0][0]); m1 = __uint_as_float(r[0][1]); m2 = __uint_as_float(r[0][2]); m3 = __uint_as_float(r[0][3]);
+#pragma unroll
+        for (int c = 0; c < NCH / 2; ++c) fold(r[c]);
+        tmem_ld_wait();
+        if (stamper) stamp_fine(p, it, 1);
+#pragma unroll
+        for (int c = NCH / 2; c < NCH; ++c) fold(r[c]);
+        m_half = (pos ? fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) : fminf(fminf(m0, m1), fminf(m2, m3))) * c2;
+      } else {
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+          if (c * 32 < valid) tmem_ld_32x32b_x32(tbase + c * 32, r[c]);
+          else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[c][i] = 0u;
+          }
+        }
+        tmem_ld_wait();
+        if (stamper) stamp_fine(p, it, 1);
+        if (p.round_logits_f16) {
+#pragma unroll
+          for (int c = 0; c < NCH; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[c][i] = __float_as_uint(__half2float(__float2half_rn(__uint_as_float(r[c][i]))));
+        }
+        // ---- extreme of the raw accumulators (max if scale >= 0, else min), four chains ----
+        if (valid == HC) {
+          float m0 = __uint_as_float(r[0][0]), m1 = __uint_as_float(r[0][1]);
+          float m2 = __uint_as_float(r[0][2]), m3 = __uint_as_float(r[0][3]);
+          if (pos) {
+#pragma unroll
+            for (int c = 0; c < NCH; ++c)
+#pragma unroll
+              for (int i = 0; i < 32; i += 8) {
+                m0 = max3(m0, __uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1]));
+                m1 = max3(m1, __uint_as_float(r[c][i + 2]), __uint_as_float(r[c][i + 3]));
+                m2 = max3(m2, __uint_as_float(r[c][i + 4]), __uint_as_float(r[c][i + 5]));
+                m3 = max3(m3, __uint_as_float(r[c][i + 6]), __uint_as_float(r[c][i + 7]));
+              }
+            m_half = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+          } else {
+#pragma unroll
+            for (int c = 0; c < NCH; ++c)
+#pragma unroll
+              for (int i = 0; i < 32; i += 8) {
+                m0 = min3(m0, __uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1]));
+                m1 = min3(m1, __uint_as_float(r[c][i + 2]), __uint_as_float(r[c][i + 3]));
+                m2 = min3(m2, __uint_as_float(r[c][i + 4]), __uint_as_float(r[c][i + 5]));
+                m3 = min3(m3, __uint_as_float(r[c][i + 6]), __uint_as_float(r[c][i + 7]));
+              }
+            m_half = fminf(fminf(m0, m1), fminf(m2, m3));
+          }
+          m_half *= c2;
+        } else if (valid > 0) {
+          float m = __uint_as_float(r[0][0]);
+#pragma unroll
+          for (int c = 0; c < NCH; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (c * 32 + i < valid) m = pos ? fmaxf(m, __uint_as_float(r[c][i])) : fminf(m, __uint_as_float(r[c][i]));
+          m_half = m * c2;
+        } else {
+          m_half = -INFINITY;
+        }
+      }
+      if (stamper) stamp_fine(p, it, 2);
+      // ---- e = 2^(v - m_half) in place, row sum; each chunk goes back over its logits ----
+      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+      if (valid == HC) {
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const float e0 = ex2_approx(fmaf(__uint_as_float(r[c][i]), c2, -m_half));
+            const float e1 = ex2_approx(fmaf(__uint_as_float(r[c][i + 1]), c2, -m_half));
+            const float e2 = ex2_approx(fmaf(__uint_as_float(r[c][i + 2]), c2, -m_half));
+            const float e3 = ex2_approx(fmaf(__uint_as_float(r[c][i + 3]), c2, -m_half));
+            s0 += e0; s1 += e1; s2 += e2; s3 += e3;
+            r[c][i] = __float_as_uint(e0); r[c][i + 1] = __float_as_uint(e1);
+            r[c][i + 2] = __float_as_uint(e2); r[c][i + 3] = __float_as_uint(e3);
+          }
+          tmem_st_32x32b_x32(tbase + c * 32, r[c]);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float e = 0.f;
+            if (c * 32 + i < valid) e = ex2_approx(fmaf(__uint_as_float(r[c][i]), c2, -m_half));
+            s0 += e;
+            r[c][i] = __float_as_uint(e);
+          }
+          if (c * 32 < valid) tmem_st_32x32b_x32(tbase + c * 32, r[c]);
+        }
+      }
+      const float sum = (s0 + s1) + (s2 + s3);
+      if (stamper && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 2);
+      if (stamper) { stamp_tile(p, it, 1); stamp_fine(p, it, 3); }
+      // ---- the two halves of a row meet through shared memory, the CTAs through the cluster ----
+      *mine = make_float2(m_half, sum);
+      mh[((it & 1) * 2 + half) * BM + row_in_tile] = m_half;
+      named_bar_sync(1 + q, 64);
+      const float2 o = *other;
+      named_bar_sync(1 + q, 64);
+      if (half == 0) {
+        const float lm = fmaxf(m_half, o.x);
+        const float ll = (m_half == -INFINITY ? 0.f : sum * ex2_approx(m_half - lm)) +
+                         (o.x == -INFINITY ? 0.f : o.y * ex2_approx(o.x - lm));
+        const uint32_t slot = smem_u32(&stats[(sset * kMaxCluster + col_rank) * BM + row_in_tile]);
+        const uint32_t bar = smem_u32(&stats_bar[sset]);
+        for (uint32_t peer = 0; peer < cluster_n; ++peer)
+          st_async_f32x2(map_to_cta(slot, row_peer(peer)), lm, ll, map_to_cta(bar, row_peer(peer)));
+      }
+      tmem_st_wait();
+      tc_fence_before_sync();
+      mbar_arrive(&xdone[ab]);                    // exp values parked, maxima published
+      if (stamper) stamp_tile(p, it, 2);
+    }
+  } else if (RELAY && relay_role == 2) {
+    setmaxnreg_dec<64>();
+    const int q = warp & 3;                       // TMEM lane quarter this warp may touch
+    const int row_in_tile = q * 32 + lane;
+    float *mh = reinterpret_cast<float *>(smem + L::kOffMh);   // [2][2][BM]: each half's own maximum, per tile parity
+    const int yw = warp - 12;
+    const int half = yw >> 2;
+    const bool lead = threadIdx.x == 384;
+    uint8_t *stg = smem + L::kOffOut + yw * L::kOutWarpBytes;
+    for (int it = 0; first + it * stride < p.num_items; ++it) {
+      const int w = first + it * stride;
+      int b, rb, nb; decode(w, b, rb, nb);
+      const int ab = it & 1;
+      const uint32_t tile_phase = (it >> 1) & 1;
+      const int sset = it & 3;
+      if (lead) mbar_expect_tx(&stats_bar[sset], cluster_n * BM * 8);
+      if (!mbar_wait(&xdone[ab], tile_phase)) { record_failure(p.status, WTC_DEV_TIMEOUT_ACCUM); break; }
+      tc_fence_after_sync();
+      if (lead) stamp_fine(p, it, 4);
+      if (!mbar_wait_cluster(&stats_bar[sset], (it >> 2) & 1)) { record_failure(p.status, WTC_DEV_TIMEOUT_STATS); break; }
+      if (lead && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 3);
+      if (lead) stamp_fine(p, it, 5);
+      float gm, inv_gl;
+      combine_cluster_stats(sset, row_in_tile, gm, inv_gl);
+      const float f = ex2_approx(mh[((it & 1) * 2 + half) * BM + row_in_tile] - gm) * inv_gl;
+      const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ab * BN + half * HC;
+      const int col0 = nb * BN + half * HC;
+      const int valid = max(0, min(HC, p.N - col0));
+      const int row0 = rb * BM + q * 32;
+      const bool rows_live = row0 < p.M;
+      // 32 columns at a time through one register buffer (the scheduler's other warps cover
+      // the load latency).  The first 64 columns are staged as they are packed, the last 64
+      // wait packed in registers, so the accumulator buffer goes back to the MMA warp after
+      // the fourth load and before anything waits for a store.
+      static_assert(!RELAY || NCH == 4, "relay epilogue: a thread owns 128 columns");
+      if (valid == 0) { tc_fence_before_sync(); release_accumulator(ab); }
+      if (lane == 0) tma_store_wait_read();         // the previous tile's store has read the staging tile
+      __syncwarp();
+      uint32_t h[2][16];
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        uint32_t hc[16];
+        if (c * 32 < valid) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(tbase + c * 32, r);
+          tmem_ld_wait();
+          if ((c + 1) * 32 >= valid) {                // that was my last read of this accumulator buffer
+            tc_fence_before_sync();
+            release_accumulator(ab);
+          }
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const __half2 hh = __floats2half2_rn(__uint_as_float(r[i]) * f, __uint_as_float(r[i + 1]) * f);
+            hc[i >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) hc[i] = 0u;
+        }
+        if (c < 2) stage_row_chunk(stg, lane, c, hc);
+        else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) h[c - 2][i] = hc[i];
+        }
+      }
+      if (valid > 0) {
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (rows_live) tma_store_3d(&tmO, stg, col0, row0, b);
+          tma_store_commit();
+        }
+      }
+      if (valid > 64) {
+        if (lane == 0) tma_store_wait_read();
+        __syncwarp();
+        stage_row_chunk(stg, lane, 0, h[0]);
+        stage_row_chunk(stg, lane, 1, h[1]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (rows_live) tma_store_3d(&tmO, stg, col0 + 64, row0, b);
+          tma_store_commit();
+        }
+      }
+      if (lead && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 4);
+      if (lead) { stamp_tile(p, it, 3); stamp_fine(p, it, 7); }
+    }
+    if (lane == 0) tma_store_wait_all();
+    if (lead && p.timeline_mode == 0) stamp(p.timeline, 5);
+    
+  } else {
+  if (RELAY) setmaxnreg_dec<48>();
   if (warp == 0) {
     // ======================= TMA producer ==================================
     uint32_t n = 0;
@@ -299,236 +582,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       }
       __syncwarp();
     }
-  } else if (PIPE) {
-    // ======================= softmax epilogue, tile-pipelined ==============
-    // Two groups of four warps take alternate tiles (group = accumulator buffer), so
-    // while one group is in its MUFU-bound exp phase the other loads, scales, packs and
-    // stores: the SM's special-function unit stays busy across tiles.  A thread owns a
-    // whole row of the tile and walks it in two halves of HC columns: the first half's
-    // exp values (taken against that half's own maximum) are parked in TMEM over the
-    // logits they came from, the second half's stay in registers.
-    const int q = warp & 3;
-    const int grp = (warp - 2) >> 2;
-    const int row_in_tile = q * 32 + lane;
-    const bool lead = lane == 0 && q == 2;       // one thread per group posts expect_tx (warps 2 and 6)
-    const bool stamper = threadIdx.x == 64;
-    uint8_t *stg = smem + L::kOffOut + (warp - 2) * L::kOutWarpBytes;
-    const float c2 = p.c2;
-    const bool pos = c2 >= 0.f;
-    uint32_t r[NCH][32];
-
-    // extreme of r over the first `valid` columns (log2 domain), four chains
-    auto half_max = [&](int valid) -> float {
-      float m;
-      if (valid == HC) {
-        float m0 = __uint_as_float(r[0][0]), m1 = __uint_as_float(r[0][1]), m2 = __uint_as_float(r[0][2]), m3 = __uint_as_float(r[0][3]);
-#pragma unroll
-        for (int c = 0; c < NCH; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            if (pos) {
-              m0 = fmaxf(m0, __uint_as_float(r[c][i]));     m1 = fmaxf(m1, __uint_as_float(r[c][i + 1]));
-              m2 = fmaxf(m2, __uint_as_float(r[c][i + 2])); m3 = fmaxf(m3, __uint_as_float(r[c][i + 3]));
-            } else {
-              m0 = fminf(m0, __uint_as_float(r[c][i]));     m1 = fminf(m1, __uint_as_float(r[c][i + 1]));
-              m2 = fminf(m2, __uint_as_float(r[c][i + 2])); m3 = fminf(m3, __uint_as_float(r[c][i + 3]));
-            }
-          }
-        m = pos ? fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) : fminf(fminf(m0, m1), fminf(m2, m3));
-      } else if (valid > 0) {
-        m = __uint_as_float(r[0][0]);
-#pragma unroll
-        for (int c = 0; c < NCH; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (c * 32 + i < valid) m = pos ? fmaxf(m, __uint_as_float(r[c][i])) : fminf(m, __uint_as_float(r[c][i]));
-      } else {
-        return -INFINITY;
-      }
-      return m * c2;
-    };
-    // r <- 2^(r*c2 - m) (0 beyond `valid`), returns the sum
-    auto half_exp = [&](int valid, float m) -> float {
-      float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-      if (valid == HC) {
-#pragma unroll
-        for (int c = 0; c < NCH; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            const float e0 = ex2_approx(fmaf(__uint_as_float(r[c][i]), c2, -m));
-            const float e1 = ex2_approx(fmaf(__uint_as_float(r[c][i + 1]), c2, -m));
-            const float e2 = ex2_approx(fmaf(__uint_as_float(r[c][i + 2]), c2, -m));
-            const float e3 = ex2_approx(fmaf(__uint_as_float(r[c][i + 3]), c2, -m));
-            s0 += e0; s1 += e1; s2 += e2; s3 += e3;
-            r[c][i] = __float_as_uint(e0); r[c][i + 1] = __float_as_uint(e1);
-            r[c][i + 2] = __float_as_uint(e2); r[c][i + 3] = __float_as_uint(e3);
-          }
-      } else {
-#pragma unroll
-        for (int c = 0; c < NCH; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float e = 0.f;
-            if (c * 32 + i < valid) e = ex2_approx(fmaf(__uint_as_float(r[c][i]), c2, -m));
-            s0 += e;
-            r[c][i] = __float_as_uint(e);
-          }
-      }
-      return (s0 + s1) + (s2 + s3);
-    };
-    auto round_f16 = [&]() {
-      if (p.round_logits_f16) {
-#pragma unroll
-        for (int c = 0; c < NCH; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; ++i) r[c][i] = __float_as_uint(__half2float(__float2half_rn(__uint_as_float(r[c][i]))));
-      }
-    };
-
-    // The two groups must not march in step (both in the exp phase, then both storing): the
-    // second group starts its first tile only when the first group has finished its first
-    // exp phase, and the offset then persists.
-    if (grp == 1 && first + stride < p.num_items && p.stagger) {
-      if (!mbar_wait(stagger_bar, 0)) record_failure(p.status, WTC_DEV_TIMEOUT_ACCUM);
-    }
-    for (int it = grp; first + it * stride < p.num_items; it += 2) {
-      const int w = first + it * stride;
-      int b, rb, nb; decode(w, b, rb, nb);
-      const int ab = grp;                                  // it & 1
-      const uint32_t tile_phase = (it >> 1) & 1;           // accum_full / accum_empty phase of this buffer
-      const int sset = grp * 2 + ((it >> 1) & 1);          // statistics set: two per group, alternating
-      const uint32_t stats_phase = (it >> 2) & 1;
-      if (CLUSTER && lead) mbar_expect_tx(&stats_bar[sset], cluster_n * BM * 8);
-      if (!mbar_wait(&accum_full[ab], tile_phase)) { record_failure(p.status, WTC_DEV_TIMEOUT_ACCUM); break; }
-      tc_fence_after_sync();
-      if (stamper && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 1);
-      if (stamper) stamp_tile(p, it >> 1, 0);
-      const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ab * BN;
-      const int col0 = nb * BN;
-      const int valid0 = max(0, min(HC, p.N - col0));
-      const int valid1 = max(0, min(HC, p.N - col0 - HC));
-      const int row0 = rb * BM + q * 32;
-      const bool rows_live = row0 < p.M;
-
-      // ---- first half: exp against its own maximum, parked in TMEM ----
-#pragma unroll
-      for (int c = 0; c < NCH; ++c) {
-        if (c * 32 < valid0) tmem_ld_32x32b_x32(tbase + c * 32, r[c]);
-        else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) r[c][i] = 0u;
-        }
-      }
-      tmem_ld_wait();
-      round_f16();
-      const float m0 = half_max(valid0);
-      const float l0 = half_exp(valid0, m0);
-#pragma unroll
-      for (int c = 0; c < NCH; ++c)
-        if (c * 32 < valid0) tmem_st_32x32b_x32(tbase + c * 32, r[c]);
-      // ---- second half: stays in registers ----
-#pragma unroll
-      for (int c = 0; c < NCH; ++c) {
-        if (c * 32 < valid1) tmem_ld_32x32b_x32(tbase + HC + c * 32, r[c]);
-        else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) r[c][i] = 0u;
-        }
-      }
-      tmem_ld_wait();
-      round_f16();
-      const float m1 = half_max(valid1);
-      const float l1 = half_exp(valid1, m1);
-      if (it == 0) mbar_arrive(stagger_bar);               // group 0 only: lets group 1 start
-      if (stamper && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 2);
-      if (stamper) stamp_tile(p, it >> 1, 1);
-      const float lm = fmaxf(m0, m1);
-      float f0, f1;
-      if (CLUSTER) {
-        const float ll = l0 * ex2_approx(m0 - lm) + (valid1 > 0 ? l1 * ex2_approx(m1 - lm) : 0.f);
-        const uint32_t slot = smem_u32(&stats[(sset * kMaxCluster + col_rank) * BM + row_in_tile]);
-        const uint32_t bar = smem_u32(&stats_bar[sset]);
-        for (uint32_t peer = 0; peer < cluster_n; ++peer)
-          st_async_f32x2(map_to_cta(slot, row_peer(peer)), lm, ll, map_to_cta(bar, row_peer(peer)));
-        if (!mbar_wait_cluster(&stats_bar[sset], stats_phase)) { record_failure(p.status, WTC_DEV_TIMEOUT_STATS); break; }
-        if (stamper && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 3);
-        if (stamper) stamp_tile(p, it >> 1, 2);
-        float gm, inv;
-        combine_cluster_stats(sset, row_in_tile, gm, inv);
-        f0 = ex2_approx(m0 - gm) * inv;
-        f1 = ex2_approx(m1 - gm) * inv;
-      } else {
-        f0 = ex2_approx(m0 - lm);
-        f1 = ex2_approx(m1 - lm);
-      }
-
-      float sum_r = 0.f;
-      // p = e * f -> f16 -> global memory (straight from registers, or staged for TMA)
-      const int row = rb * BM + row_in_tile;
-      __half *orow = static_cast<__half *>(p.out) + static_cast<long long>(b) * p.o_batch_stride + static_cast<long long>(row) * p.ldo;
-      auto write_half = [&](int valid, float f, int col_base) {
-        if (OUT_TILES == 0) {
-#pragma unroll
-          for (int c = 0; c < NCH; ++c) {
-            if (c * 32 < valid) {
-              uint32_t h[16];
-#pragma unroll
-              for (int i = 0; i < 32; i += 2) {
-                const __half2 hh = __floats2half2_rn(__uint_as_float(r[c][i]) * f, __uint_as_float(r[c][i + 1]) * f);
-                if (!CLUSTER) { const float2 back = __half22float2(hh); sum_r += back.x + back.y; }
-                h[i >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
-              }
-              if (row < p.M) st_global_row32(orow + col_base + c * 32, h, p.out_align32, valid - c * 32);
-            }
-          }
-        } else {
-#pragma unroll
-        for (int g = 0; g < NCH / 2; ++g) {
-          if (g * 64 < valid) {
-            if (lane == 0) tma_store_wait_read();
-            __syncwarp();
-#pragma unroll
-            for (int hc = 0; hc < 2; ++hc) {
-              const int c = g * 2 + hc;
-              uint32_t h[16];
-#pragma unroll
-              for (int i = 0; i < 32; i += 2) {
-                const __half2 hh = __floats2half2_rn(__uint_as_float(r[c][i]) * f, __uint_as_float(r[c][i + 1]) * f);
-                if (!CLUSTER) { const float2 back = __half22float2(hh); sum_r += back.x + back.y; }
-                h[i >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
-              }
-              stage_row_chunk(stg, lane, hc, h);
-            }
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              if (rows_live) tma_store_3d(&tmO, stg, col_base + g * 64, row0, b);
-              tma_store_commit();
-            }
-          }
-        }
-        }
-      };
-      write_half(valid1, f1, col0 + HC);
-      // ---- fetch the parked first half, hand the accumulator back, write it out ----
-      tmem_st_wait();
-#pragma unroll
-      for (int c = 0; c < NCH; ++c)
-        if (c * 32 < valid0) tmem_ld_32x32b_x32(tbase + c * 32, r[c]);
-      tmem_ld_wait();
-      tc_fence_before_sync();
-      release_accumulator(ab);
-      write_half(valid0, f0, col0);
-      if (!CLUSTER) {
-        const int row = rb * BM + row_in_tile;
-        if (row < p.M) p.tile_stats[(static_cast<int64_t>(b) * p.M + row) * p.num_nb + nb] = make_float2(lm, sum_r);
-      }
-      if (stamper && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 4);
-      if (stamper) stamp_tile(p, it >> 1, 3);
-    }
-    if (lane == 0) tma_store_wait_all();
-    if (stamper && p.timeline_mode == 0) stamp(p.timeline, 5);
-  } else {
+  } else if (!RELAY) {
     // ======================= softmax epilogue ==============================
     const int q = warp & 3;                      // TMEM lane quarter this warp may read
     const int half = (warp - 2) >> 2;            // which part (of PARTS) of the tile's columns
@@ -827,6 +881,8 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     if (lead && p.timeline_mode == 0) stamp(p.timeline, 5);
   }
 
+  }   // warps 0-3 of the relay form, every warp of the others
+
   // ---- teardown: nothing in flight, peers done with our shared memory, TMEM freed ----
   if (p.status && *reinterpret_cast<volatile int *>(p.status) != 0) {
     // a wait gave up somewhere: give copies that were already issued time to land
@@ -838,11 +894,11 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   if (warp == 1) { if (PAIR) tmem_dealloc_pair(tmem_base, 2 * BN); else tmem_dealloc(tmem_base, 2 * BN); }
 }
 
-template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool PIPE, bool PAIR, int EW, bool OUT32 = false>
+template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool RELAY, bool PAIR, int EW, bool OUT32 = false>
 cudaError_t launch_impl(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO, TcParams p,
                         int cluster_n, int num_sms, cudaStream_t s, TcLaunchInfo *info) {
-  using L = SmemLayout<BN, STAGES, CLUSTER, OUT_TILES, PIPE, PAIR, EW, OUT32>;
-  auto kern = fused_tc_kernel<BN, STAGES, CLUSTER, OUT_TILES, PIPE, PAIR, EW, OUT32>;
+  using L = SmemLayout<BN, STAGES, CLUSTER, OUT_TILES, RELAY, PAIR, EW, OUT32>;
+  auto kern = fused_tc_kernel<BN, STAGES, CLUSTER, OUT_TILES, RELAY, PAIR, EW, OUT32>;
   static bool attr_set = false;   // per template instance
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
@@ -855,7 +911,7 @@ cudaError_t launch_impl(const CUtensorMap &tmA, const CUtensorMap &tmB, const CU
   const int cluster_size = (CLUSTER ? cluster_n : 1) * (PAIR ? 2 : 1);
 
   cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(kThreadsFor(EW), 1, 1);
+  cfg.blockDim = dim3(kThreadsFor(EW, RELAY), 1, 1);
   cfg.dynamicSmemBytes = L::kDynamic;
   cfg.stream = s;
   cudaLaunchAttribute attr[2];
@@ -892,7 +948,7 @@ cudaError_t launch_impl(const CUtensorMap &tmA, const CUtensorMap &tmB, const CU
     cfg.numAttrs = nattr;
   }
   cfg.gridDim = dim3(grid, 1, 1);
-  if (info) { info->grid = grid; info->cluster = cluster_size; info->smem_bytes = L::kDynamic; info->threads = kThreadsFor(EW); }
+  if (info) { info->grid = grid; info->cluster = cluster_size; info->smem_bytes = L::kDynamic; info->threads = kThreadsFor(EW, RELAY); }
   return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmO, p);
 }
 
@@ -901,9 +957,9 @@ cudaError_t launch_impl(const CUtensorMap &tmA, const CUtensorMap &tmB, const CU
 // Variant choice.  pair: two CTAs share one 256-row MMA (a third less L2 operand traffic per
 // flop).  Measured on B200 the contraction runs at the same rate either way, and an
 // eight-CTA cluster fits the chip only 15 times, so the cluster flavour pairs only on
-// request; the tiled flavour (clusters of two) pairs when the K loop is long.  pipe: with several tiles per CTA the two epilogue warp groups take
-// alternate tiles; with one tile per CTA all eight warps share it.  store: swizzled staging +
-// TMA stores by default, direct register stores on request.
+// request; the tiled flavour (clusters of two) pairs when the K loop is long.  relay: sixteen
+// epilogue warps in two groups that overlap consecutive tiles (cluster flavour, f16, staged
+// stores).  store: swizzled staging + TMA stores by default, direct register stores on request.
 cudaError_t launch_fused_cluster(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO,
                                  const TcParams &p, int bn, int cluster_n, int num_sms, cudaStream_t s,
                                  TcLaunchInfo *info) {
@@ -912,28 +968,24 @@ cudaError_t launch_fused_cluster(const CUtensorMap &tmA, const CUtensorMap &tmB,
   // 128-column tiles (a tile choice of best.json): the default schedule only
   if (bn == 128) return launch_impl<128, 4, true, 2, false, false, 8>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
   const bool pair = p.pair_mode == 2 && 2 * cluster_n <= kMaxCluster;
-  const int row_units = p.batch * (pair ? (p.num_rb + 1) / 2 : p.num_rb);
-  const int resident = num_sms / (cluster_n * (pair ? 2 : 1));
-  // measured on B200 (config 3): split 275 us, tile-pipelined 281 us -- split is the default
-  const bool pipe = p.epilogue_mode == 2;
-  (void)row_units; (void)resident;
   const bool tma = p.store_mode == 1;
   if (pair) {
-    if (tma) return pipe ? launch_impl<kTcBlockN, 4, true, 1, true, true, 8>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info)
-                         : launch_impl<kTcBlockN, 4, true, 2, false, true, 8>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
-    return pipe ? launch_impl<kTcBlockN, 6, true, 0, true, true, 8>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info)
-                : launch_impl<kTcBlockN, 6, true, 0, false, true, 8>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+    if (tma) return launch_impl<kTcBlockN, 4, true, 2, false, true, 8>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+    return launch_impl<kTcBlockN, 6, true, 0, false, true, 8>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
   }
   if (tma) {
+    // the relay pays when a CTA sees several tiles: its two groups then overlap
+    const int resident = num_sms / cluster_n;
+    const int tiles_per_cta = (p.batch * p.num_rb + resident - 1) / (resident > 0 ? resident : 1);
+    const bool relay = p.epilogue_mode == 2 || (p.epilogue_mode == 0 && tiles_per_cta >= kRelayMinTiles);
+    if (relay) return launch_impl<kTcBlockN, 3, true, 1, true, false, 16>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
     // sixteen epilogue warps (a row's columns split four ways) on request: measured on B200 it
     // does not beat eight (the exp and pack phases are bound by the special-function unit)
-    if (p.epilogue_warps == 16 && p.epilogue_mode != 2)
+    if (p.epilogue_warps == 16)
       return launch_impl<kTcBlockN, 3, true, 1, false, false, 16>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
-    return pipe ? launch_impl<kTcBlockN, 3, true, 1, true, false, 8>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info)
-                : launch_impl<kTcBlockN, 3, true, 2, false, false, 8>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+    return launch_impl<kTcBlockN, 3, true, 2, false, false, 8>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
   }
-  return pipe ? launch_impl<kTcBlockN, 4, true, 0, true, false, 8>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info)
-              : launch_impl<kTcBlockN, 4, true, 0, false, false, 8>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+  return launch_impl<kTcBlockN, 4, true, 0, false, false, 8>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
 }
 
 cudaError_t launch_tiled_partial(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO,
@@ -941,20 +993,13 @@ cudaError_t launch_tiled_partial(const CUtensorMap &tmA, const CUtensorMap &tmB,
   if (p.out_f32) return launch_impl<kTcBlockN, 4, false, 1, false, false, 8, true>(tmA, tmB, tmO, p, 1, num_sms, s, info);
   if (bn == 128) return launch_impl<128, 6, false, 1, false, false, 8>(tmA, tmB, tmO, p, 1, num_sms, s, info);
   const bool pair = p.pair_mode == 2 || (p.pair_mode == 0 && p.num_rb >= 2 && p.num_kb >= 8);
-  const int items = p.batch * (pair ? (p.num_rb + 1) / 2 : p.num_rb) * p.num_nb;
-  const bool pipe = p.epilogue_mode == 2;
-  (void)items;
   const bool tma = p.store_mode == 1;
   if (pair) {
-    if (tma) return pipe ? launch_impl<kTcBlockN, 6, false, 1, true, true, 8>(tmA, tmB, tmO, p, 1, num_sms, s, info)
-                         : launch_impl<kTcBlockN, 6, false, 1, false, true, 8>(tmA, tmB, tmO, p, 1, num_sms, s, info);
-    return pipe ? launch_impl<kTcBlockN, 6, false, 0, true, true, 8>(tmA, tmB, tmO, p, 1, num_sms, s, info)
-                : launch_impl<kTcBlockN, 6, false, 0, false, true, 8>(tmA, tmB, tmO, p, 1, num_sms, s, info);
+    if (tma) return launch_impl<kTcBlockN, 6, false, 1, false, true, 8>(tmA, tmB, tmO, p, 1, num_sms, s, info);
+    return launch_impl<kTcBlockN, 6, false, 0, false, true, 8>(tmA, tmB, tmO, p, 1, num_sms, s, info);
   }
-  if (tma) return pipe ? launch_impl<kTcBlockN, 4, false, 1, true, false, 8>(tmA, tmB, tmO, p, 1, num_sms, s, info)
-                       : launch_impl<kTcBlockN, 4, false, 1, false, false, 8>(tmA, tmB, tmO, p, 1, num_sms, s, info);
-  return pipe ? launch_impl<kTcBlockN, 4, false, 0, true, false, 8>(tmA, tmB, tmO, p, 1, num_sms, s, info)
-              : launch_impl<kTcBlockN, 4, false, 0, false, false, 8>(tmA, tmB, tmO, p, 1, num_sms, s, info);
+  if (tma) return launch_impl<kTcBlockN, 4, false, 1, false, false, 8>(tmA, tmB, tmO, p, 1, num_sms, s, info);
+  return launch_impl<kTcBlockN, 4, false, 0, false, false, 8>(tmA, tmB, tmO, p, 1, num_sms, s, info);
 }
 
 } // namespace wtc

@@ -29,10 +29,9 @@ struct TcParams {
   int out_f32;     // f32 probabilities (else f16)
   int out_align32; // every output row starts on a 32-byte boundary
   int store_mode;  // 0 direct register->global stores, 1 swizzled shared staging + TMA stores
-  int stagger;     // tile-pipelined epilogue: offset the two warp groups by one phase
   int epilogue_warps;  // 0 choose, 8 or 16 (cluster flavour with staged stores)
   int pair_mode;   // 0 choose, 1 never pair CTAs, 2 pair whenever the cluster allows
-  int epilogue_mode;  // 0 choose by tiles per CTA, 1 all warps share a tile, 2 warp groups alternate tiles
+  int epilogue_mode;  // 0 choose by tiles per CTA, 1 all warps share a tile, 2 two warp groups relay consecutive tiles
   int use_pdl;     // launch with programmatic stream serialisation
   int round_logits_f16;  // chain spelled with an f16 matmul result: round s to f16 before the softmax
   float c2;        // scale * log2(e)

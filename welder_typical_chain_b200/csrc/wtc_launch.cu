@@ -272,14 +272,12 @@ int launch_resolved(Resolved &r, const void *A, const void *B, void *Out, void *
     if (out32) r.bn = wtc::kTcBlockN;   // (resolve() already forces 256 for f32 output)
     p.out = Out; p.ldo = d.ldo; p.o_batch_stride = d.o_batch_stride;
     p.out_align32 = ((reinterpret_cast<uintptr_t>(Out) & 31) == 0) && ((d.ldo & 15) == 0) && ((d.o_batch_stride & 15) == 0);
-    p.stagger = 1;
     if (const char *e = getenv("WTC_TL_MODE")) p.timeline_mode = atoi(e);
-    if (const char *e = getenv("WTC_STAGGER")) p.stagger = e[0] != '0';
     p.store_mode = 1;
     if (const char *e = getenv("WTC_EW")) p.epilogue_warps = atoi(e);
     if (const char *e = getenv("WTC_STORE")) p.store_mode = !strcmp(e, "direct") ? 0 : 1;
     if (const char *e = getenv("WTC_PAIR")) p.pair_mode = e[0] == '0' ? 1 : (e[0] == '1' ? 2 : 0);
-    if (const char *e = getenv("WTC_EPILOGUE")) p.epilogue_mode = !strcmp(e, "split") ? 1 : (!strcmp(e, "pipe") ? 2 : 0);
+    if (const char *e = getenv("WTC_EPILOGUE")) p.epilogue_mode = !strcmp(e, "split") ? 1 : (!strcmp(e, "relay") ? 2 : 0);
     wtc::TcLaunchInfo info;
     cudaError_t e;
     if (!tiled) {
