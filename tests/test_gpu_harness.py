@@ -33,3 +33,20 @@ def test_run_ab_with_verification(tmp_path, wtc_lib, cuda_dev, mlir, pattern, ro
     assert rows_[0].split("\t")[:3] == ["case", "avg_ms", "kernels"] and len(rows_) == 3
     assert rows_[1].split("\t")[2] == "5"                                  # the unfused pipeline is five launches
     assert float(open(tmp_path / "ab" / "speedup.tsv").read().split("\t")[1]) > 0
+
+
+def test_search_with_on_device_profiling(tmp_path, wtc_lib, cuda_dev):
+    """welder-solver --enable-profiling on the GPU: both tile shapes the kernel library has are
+    compiled, timed by welder-profiler and cached; a second run is answered by the cache."""
+    env = dict(os.environ, OUT_BASE=str(tmp_path / "sp"), PROFILE_WARMUP="3", PROFILE_ITERS="20")
+    script = os.path.join(PKG, "bench", "run_search_profile.sh")
+    r = subprocess.run(["bash", script], capture_output=True, text=True, env=env)
+    assert r.returncode == 0 and "PASS" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("[wtc.profile] measured") == 2, r.stdout[-3000:]
+    rows = [l.split("\t") for l in open(tmp_path / "sp" / "search" / "candidates.tsv").read().splitlines()]
+    col = rows[0].index("profiledMs")
+    ms = [float(x[col]) for x in rows[1:3]]
+    assert 0 < ms[0] <= ms[1] < 1.0, ms                     # config 2 runs in tens of microseconds
+    assert len(open(tmp_path / "sp" / "profile_cache.tsv").read().splitlines()) == 2
+    r = subprocess.run(["bash", script], capture_output=True, text=True, env=env)
+    assert r.returncode == 0 and r.stdout.count("[wtc.profile] cache hit") == 2, r.stdout[-3000:]

@@ -65,6 +65,7 @@ struct Candidate {
   bool implemented;            // the kernel library has this tile shape
   double score;                // L2->SM operand bytes x waves (lower is better)
   double estimatedLatencyUs;
+  double profiledMs = -1.0;    // measured on the device by the profiling pass; -1: not measured
   double bytesA, bytesB, bytesC, bytesCut;
 };
 
@@ -80,10 +81,28 @@ std::vector<Candidate> enumerateCandidates(const ir::ChainSpec &spec, const Arch
 bool writeBestSummaryJson(const ir::ChainSpec &spec, const ArchModel &arch, const std::vector<Candidate> &sorted,
                           const std::string &path, std::string &error);
 bool writeCandidatesTsv(const std::vector<Candidate> &sorted, const std::string &path, std::string &error);
-// parse + enumerate + write; the shared body of the solver C API and CLI.
+// On-device profiling of the best-ranked candidates (the reference's `d.Profile` step:
+// solver/WelderSolver.cpp:202-213,479-513; compile + run welder-profiler per candidate,
+// solver/WelderSolverProfileCompileAndRun.h:137-2453; append-only `key<TAB>ms` cache,
+// solver/WelderSolverProfileRetryHelpers.h:796-833).
+struct ProfileOptions {
+  bool enable = false;
+  int64_t topK = 8;            // --schedule-topk: how many implemented candidates are measured
+  int warmup = 10, iters = 100;
+  std::string profilerBin;     // empty: welder-profiler beside this module
+  std::string cachePath;       // empty: no disk cache
+  bool verbose = false;        // keeps the temporary plans
+};
+// Fills `profiledMs` of up to topK implemented candidates (cache first, then compile the
+// plan and run the profiler binary), then moves the measured ones to the front ordered by
+// time.  Returns how many carry a measurement; candidates whose run fails stay unmeasured.
+int profileCandidates(const std::string &inputMlir, const ir::ChainSpec &spec, int64_t maxConnectLevel,
+                      const ProfileOptions &opts, std::vector<Candidate> &sorted, std::string &log);
+std::string buildProfileKey(const ir::ChainSpec &spec, const Candidate &c, int64_t maxConnectLevel);
+// parse + enumerate (+ profile) + write; the shared body of the solver C API and CLI.
 int solveTypicalChain(const std::string &inputMlir, const std::string &bestSummaryJson,
                       const std::string &candidatesTsv, int64_t maxConnectLevel, SearchResult &best,
-                      std::string &error);
+                      std::string &error, const ProfileOptions *profile = nullptr);
 
 } // namespace scheduler
 

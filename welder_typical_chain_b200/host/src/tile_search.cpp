@@ -10,7 +10,13 @@
 // The artifacts keep the reference's schema (solver/WelderSolverCAPI.cpp:40-100).
 #include "wtc_host.h"
 
+#include <dlfcn.h>
+#include <unistd.h>
+
 #include <algorithm>
+#include <cstdio>
+#include <cstdlib>
+#include <map>
 #include <cmath>
 #include <filesystem>
 #include <fstream>
@@ -119,6 +125,138 @@ std::vector<Candidate> enumerateCandidates(const ir::ChainSpec &spec, const Arch
   return out;
 }
 
+
+// ---- on-device profiling of the top-k candidates ------------------------------------------
+
+std::string buildProfileKey(const ir::ChainSpec &spec, const Candidate &c, int64_t maxConnectLevel) {
+  std::ostringstream k;
+  k << "wtc_b200_chain|batch=" << spec.batch << "|m=" << spec.M << "|n=" << spec.N << "|k=" << spec.K << "|bb=" << (spec.bBatched ? 1 : 0)
+    << "|in=" << spec.inType << "|acc=" << spec.accType << "|out=" << spec.outType << "|scale=" << spec.scale
+    << "|tile=" << c.tileM << "x" << c.tileN << "x" << c.tileK << "|level=" << maxConnectLevel
+    // raised when the kernels behind a tile change enough to make old timings misleading
+    << "|profile_key_rev=sm100a_relay_v2";
+  return k.str();
+}
+
+namespace {
+
+// directory that holds the module this code is linked into (the solver binary or C-API library)
+std::string moduleDir() {
+  Dl_info info;
+  if (dladdr(reinterpret_cast<const void *>(&moduleDir), &info) && info.dli_fname) {
+    std::error_code ec;
+    const std::filesystem::path p = std::filesystem::canonical(info.dli_fname, ec);
+    if (!ec) return p.parent_path().string();
+  }
+  return ".";
+}
+
+void loadProfileCache(const std::string &path, std::map<std::string, double> &cache) {
+  if (path.empty()) return;
+  std::ifstream in(path);
+  std::string line;
+  while (std::getline(in, line)) {
+    const size_t tab = line.find('\t');
+    if (line.empty() || tab == std::string::npos) continue;
+    const double ms = std::strtod(line.c_str() + tab + 1, nullptr);
+    if (ms > 0.0) cache[line.substr(0, tab)] = ms;   // later lines win
+  }
+}
+
+void appendProfileCache(const std::string &path, const std::string &key, double ms) {
+  if (path.empty()) return;
+  std::ofstream out(path, std::ios::out | std::ios::app);
+  if (out) out << key << "\t" << ms << "\n";
+}
+
+// runs `cmd`, returns its stdout; rc gets the exit status
+std::string captureCommand(const std::string &cmd, int &rc) {
+  std::string out;
+  FILE *f = popen(cmd.c_str(), "r");
+  if (!f) { rc = -1; return out; }
+  char buf[512];
+  while (fgets(buf, sizeof buf, f)) out += buf;
+  const int st = pclose(f);
+  rc = st == -1 ? -1 : (WIFEXITED(st) ? WEXITSTATUS(st) : 128);
+  return out;
+}
+
+std::string quote(const std::string &s) {
+  std::string q = "'";
+  for (char ch : s) { if (ch == '\'') q += "'\\''"; else q += ch; }
+  return q + "'";
+}
+
+} // namespace
+
+int profileCandidates(const std::string &inputMlir, const ir::ChainSpec &spec, int64_t maxConnectLevel,
+                      const ProfileOptions &opts, std::vector<Candidate> &sorted, std::string &log) {
+  trace::Span span("profile");
+  std::ostringstream lg;
+  std::map<std::string, double> cache;
+  loadProfileCache(opts.cachePath, cache);
+  const std::string profiler = opts.profilerBin.empty() ? moduleDir() + "/welder-profiler" : opts.profilerBin;
+  std::error_code ec;
+  const std::filesystem::path tmpRoot = std::filesystem::temp_directory_path(ec) / ("wtc_profile_" + std::to_string(static_cast<long long>(getpid())));
+  int measured = 0;
+  int64_t taken = 0;
+  for (size_t i = 0; i < sorted.size() && taken < opts.topK; ++i) {
+    Candidate &c = sorted[i];
+    if (!c.implemented) continue;          // no kernel behind this tile: nothing to run
+    ++taken;
+    const std::string key = buildProfileKey(spec, c, maxConnectLevel);
+    const auto hit = cache.find(key);
+    if (hit != cache.end()) {
+      c.profiledMs = hit->second;
+      ++measured;
+      lg << "[wtc.profile] cache hit  tile " << c.tileM << "x" << c.tileN << "x" << c.tileK << " -> " << c.profiledMs << " ms\n";
+      continue;
+    }
+    transform::CompileRequest req;
+    req.inputMlirPath = inputMlir;
+    req.outDir = (tmpRoot / ("cand_" + std::to_string(i))).string();
+    req.tileM = c.tileM; req.tileN = c.tileN; req.tileK = c.tileK;
+    req.threadTileM = c.threadTileM; req.threadTileN = c.threadTileN;
+    req.maxConnectLevel = maxConnectLevel;
+    req.fused = maxConnectLevel > 0;
+    std::string err;
+    if (transform::compileChainToPlan(req, err) != 0) {
+      lg << "[wtc.profile] compile failed for tile " << c.tileM << "x" << c.tileN << "x" << c.tileK << ": " << err << "\n";
+      continue;
+    }
+    const std::string cmd = quote(profiler) + " --warmup=" + std::to_string(opts.warmup) + " --iters=" + std::to_string(opts.iters) +
+                            " --init=random " + quote(req.outDir + "/05.out.nvvm.runnable.mlir") + " 2>&1";
+    int rc = 0;
+    const std::string out = captureCommand(cmd, rc);
+    std::smatch m;
+    static const std::regex re("avg_ms=([-+0-9.eE]+)");
+    if (rc == 0 && std::regex_search(out, m, re)) {
+      const double ms = std::strtod(m[1].str().c_str(), nullptr);
+      if (ms > 0.0) {
+        c.profiledMs = ms;
+        cache[key] = ms;
+        appendProfileCache(opts.cachePath, key, ms);
+        ++measured;
+        lg << "[wtc.profile] measured   tile " << c.tileM << "x" << c.tileN << "x" << c.tileK << " -> " << ms << " ms\n";
+        continue;
+      }
+    }
+    lg << "[wtc.profile] run failed for tile " << c.tileM << "x" << c.tileN << "x" << c.tileK << " (rc " << rc << "): "
+       << out.substr(0, 300) << "\n";
+  }
+  if (!opts.verbose) std::filesystem::remove_all(tmpRoot, ec);
+  // measured candidates first, fastest first; the rest keep their model order
+  std::stable_sort(sorted.begin(), sorted.end(), [](const Candidate &x, const Candidate &y) {
+    const bool mx = x.profiledMs > 0.0, my = y.profiledMs > 0.0;
+    if (mx != my) return mx;
+    if (mx && my && x.profiledMs != y.profiledMs) return x.profiledMs < y.profiledMs;
+    return false;
+  });
+  if (measured == 0) span.fail();
+  log = lg.str();
+  return measured;
+}
+
 bool writeBestSummaryJson(const ir::ChainSpec &spec, const ArchModel &arch, const std::vector<Candidate> &sorted,
                           const std::string &path, std::string &error) {
   if (sorted.empty()) { error = "empty candidate list"; return false; }
@@ -131,7 +269,7 @@ bool writeBestSummaryJson(const ir::ChainSpec &spec, const ArchModel &arch, cons
     << ", \"elementBytes\": " << (spec.inType == "f16" ? 2 : 4) << ", \"tmemColumns\": " << arch.tmemColumns << ", \"chip\": \"sm_100a\"},\n"
     << "  \"best\": {\"tileM\": " << b.tileM << ", \"tileN\": " << b.tileN << ", \"tileK\": " << b.tileK
     << ", \"threadTileM\": " << b.threadTileM << ", \"threadTileN\": " << b.threadTileN << ", \"score\": " << b.score
-    << ", \"estimatedLatency\": " << b.estimatedLatencyUs << ", \"profiledMs\": -1, \"bytesCut\": " << b.bytesCut
+    << ", \"estimatedLatency\": " << b.estimatedLatencyUs << ", \"profiledMs\": " << b.profiledMs << ", \"bytesCut\": " << b.bytesCut
     << ", \"stages\": " << b.stages << ", \"clusterN\": " << b.clusterN << ", \"implemented\": " << (b.implemented ? "true" : "false") << "}\n"
     << "}\n";
   if (!writeAll(path, o.str())) { error = "failed to open best summary json: " + path; return false; }
@@ -145,7 +283,7 @@ bool writeCandidatesTsv(const std::vector<Candidate> &sorted, const std::string 
   for (size_t i = 0; i < sorted.size(); ++i) {
     const Candidate &c = sorted[i];
     o << i << "\t" << c.tileM << "\t" << c.tileN << "\t" << c.tileK << "\t" << c.threadTileM << "\t" << c.threadTileN << "\t" << c.score
-      << "\t" << c.estimatedLatencyUs << "\t-1\t" << c.bytesA << "\t" << c.bytesB << "\t" << c.bytesC << "\t" << c.bytesCut << "\n";
+      << "\t" << c.estimatedLatencyUs << "\t" << c.profiledMs << "\t" << c.bytesA << "\t" << c.bytesB << "\t" << c.bytesC << "\t" << c.bytesCut << "\n";
   }
   if (!writeAll(path, o.str())) { error = "failed to open candidates tsv: " + path; return false; }
   return true;
@@ -153,13 +291,31 @@ bool writeCandidatesTsv(const std::vector<Candidate> &sorted, const std::string 
 
 // rc: 0 ok, 2 open/parse failure, 3 no candidates, 4 I/O failure (solver/WelderSolverCAPI.cpp:104-196)
 int solveTypicalChain(const std::string &inputMlir, const std::string &bestSummaryJson, const std::string &candidatesTsv,
-                      int64_t maxConnectLevel, SearchResult &best, std::string &error) {
+                      int64_t maxConnectLevel, SearchResult &best, std::string &error, const ProfileOptions *profile) {
   trace::Span span("search");
   ir::ChainSpec spec;
   if (!ir::parseChainFile(inputMlir, spec, error)) { span.fail(); return 2; }
   const ArchModel arch;
-  const std::vector<Candidate> sorted = enumerateCandidates(spec, arch, maxConnectLevel);
+  std::vector<Candidate> sorted = enumerateCandidates(spec, arch, maxConnectLevel);
   if (sorted.empty()) { error = "no legal tile candidate for this chain"; span.fail(); return 3; }
+  // Profiling is asked for by the caller (welder-solver --enable-profiling) or, for callers
+  // that go through the fixed C signature, by WTC_SOLVER_PROFILE=1 (+ _CACHE, _TOPK, _ITERS).
+  ProfileOptions envProfile;
+  if (!profile) {
+    const char *e = std::getenv("WTC_SOLVER_PROFILE");
+    if (e && e[0] == '1') {
+      envProfile.enable = true;
+      if (const char *v = std::getenv("WTC_SOLVER_PROFILE_CACHE")) envProfile.cachePath = v;
+      if (const char *v = std::getenv("WTC_SOLVER_PROFILE_TOPK")) envProfile.topK = std::atoll(v);
+      if (const char *v = std::getenv("WTC_SOLVER_PROFILE_ITERS")) envProfile.iters = std::atoi(v);
+      profile = &envProfile;
+    }
+  }
+  if (profile && profile->enable) {
+    std::string plog;
+    profileCandidates(inputMlir, spec, maxConnectLevel, *profile, sorted, plog);
+    if (profile->verbose || std::getenv("WTC_SOLVER_PROFILE_LOG")) std::fputs(plog.c_str(), stderr);
+  }
   if (!bestSummaryJson.empty() && !writeBestSummaryJson(spec, arch, sorted, bestSummaryJson, error)) { span.fail(); return 4; }
   if (!candidatesTsv.empty() && !writeCandidatesTsv(sorted, candidatesTsv, error)) { span.fail(); return 4; }
   const Candidate &b = sorted.front();
