@@ -42,6 +42,11 @@ extern "C" {
 /* flags */
 #define WTC_FLAG_FORCE_SIMT 0x1   /* never use the tensor-core kernels            */
 #define WTC_FLAG_FORCE_TILED 0x2  /* two-pass tiled kernel even if a cluster fits  */
+/* f32 operands in memory, rounded to f16 (round to nearest even, arith.truncf) before the
+ * contraction: the chain of mlir_pipeline/matmul_softmax_chain_f16_matmul.mlir:18-44 in the
+ * reference.  Needs in_dtype = WTC_F32.  The rounded copies live in the workspace
+ * (wtc_matmul_softmax_workspace_bytes counts them); the single-GPU entry points only. */
+#define WTC_FLAG_MATMUL_F16 0x4
 
 /* error codes */
 #define WTC_OK 0

@@ -75,6 +75,24 @@ def test_plan_fallbacks_and_variants(wtc_lib):
     assert w.plan_query(w.make_desc(1, 4096, 2048, 1024, tile_n=128)).kernel == w.KERNEL_TC_TILED   # 16 column blocks
 
 
+def test_plan_for_f32_operands_rounded_to_f16(wtc_lib):
+    """WTC_FLAG_MATMUL_F16: the plan is the f16 chain's plus two rounding passes, and the
+    workspace holds the rounded copies (each padded to 256 bytes) ahead of the chain's own."""
+    w = wtc_lib
+    p = w.plan_query(w.make_desc(1, 8192, 128, 64, in_dtype=w.F32, out_dtype=w.F32, acc_dtype=w.F16, flags=w.FLAG_MATMUL_F16))
+    assert (p.kernel, p.launches, p.workspace_bytes) == (w.KERNEL_TC_CLUSTER, 3, 8192 * 64 * 2 + 64 * 128 * 2)
+    d = w.make_desc(2, 100, 32000, 64, in_dtype=w.F32, flags=w.FLAG_MATMUL_F16)          # tiled schedule behind the rounding, B per batch
+    p = w.plan_query(d)
+    stage = -(-2 * 100 * 64 * 2 // 256) * 256 + -(-2 * 64 * 32000 * 2 // 256) * 256
+    assert p.kernel == w.KERNEL_TC_TILED and p.launches == 4 and p.workspace_bytes == stage + 2 * 100 * 125 * 8
+    assert w.workspace_bytes(d) == p.workspace_bytes
+    p = w.plan_query(w.make_desc(1, 33, 100, 50, in_dtype=w.F32, out_dtype=w.F32, flags=w.FLAG_MATMUL_F16))
+    assert p.kernel == w.KERNEL_SIMT_FUSED and p.launches == 3
+    with pytest.raises(w.WtcError) as e:                                                   # the flag needs f32 buffers
+        w.plan_query(w.make_desc(1, 16, 16, 16, in_dtype=w.F16, flags=w.FLAG_MATMUL_F16))
+    assert e.value.code == -1
+
+
 @pytest.mark.parametrize("kw", [dict(batch=0), dict(M=-1), dict(in_dtype=7), dict(variant=3), dict(tile_m=-2),
                                 dict(lda=3)])
 def test_bad_descriptors_rejected(wtc_lib, kw):

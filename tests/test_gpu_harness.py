@@ -14,6 +14,7 @@ PKG = os.path.join(ROOT, "welder_typical_chain_b200")
 @pytest.mark.parametrize("mlir,pattern,rows", [
     ("matmul_softmax_chain_f16_native.mlir", "linear", None),       # the reference's default input and pattern
     ("matmul_softmax_chain.mlir", "random", "512"),                 # f32 chain, xorshift inputs
+    ("matmul_softmax_chain_f16_matmul.mlir", "random", "1024"),     # f32 buffers rounded to f16 on the device
     ("cfg2_f16_native_4096x1024x1024.mlir", "linear", None),        # tcgen05 cluster kernel
     ("cfg3_batched_attention_named.mlir", "linear", "2048"),        # named softmax, batched plan (first batch verified)
 ])

@@ -183,6 +183,38 @@ def test_f16_matmul_result_chain(w, cuda_dev):
     assert np.abs(out_tc.astype(np.float64) - ref16).max() < 5e-3
 
 
+def test_f32_arguments_rounded_to_f16_before_the_matmul(w, cuda_dev):
+    """WTC_FLAG_MATMUL_F16: f32 buffers, arith.truncf to f16 on the device, then the f16 chain
+    (mlir_pipeline/matmul_softmax_chain_f16_matmul.mlir in the reference).  Same results as
+    handing the launch layer operands rounded on the host; the checker sees the rounded values."""
+    import torch
+    cases = [(1, 300, 1024, 136, 0.07, 0, w.F32, w.F32),           # cluster kernel, ragged M, f32 probabilities
+             (1, 256, 128, 64, 1.0, 0, w.F16, w.F32),              # the reference file's types: f16 matmul result, f32 out
+             (3, 130, 520, 72, 0.2, 0, w.F32, w.F16),              # batched, B shared
+             (1, 64, 2304, 128, 0.1, 0, w.F32, w.F16),             # two-pass tiled schedule behind the rounding
+             (1, 33, 100, 50, 0.3, 0, w.F32, w.F32),               # K, N not multiples of 8: SIMT kernel on the rounded copies
+             (1, 200, 256, 64, 0.5, w.FLAG_FORCE_SIMT, w.F32, w.F32)]
+    for batch, M, N, K, scale, flags, acc, outd in cases:
+        rng = np.random.default_rng(M + N)
+        A = rng.standard_normal((batch, M, K) if batch > 1 else (M, K)).astype(np.float32)
+        B = rng.standard_normal((K, N)).astype(np.float32)
+        got = _run(w, cuda_dev, A, B, scale, flags=flags | w.FLAG_MATMUL_F16, acc_dtype=acc, out_dtype=outd)
+        same = _run(w, cuda_dev, A.astype(np.float16), B.astype(np.float16), scale, flags=flags, acc_dtype=acc, out_dtype=outd)
+        assert np.array_equal(got, same), (batch, M, N, K)
+        if acc == w.F32:
+            A16, B16 = A.astype(np.float16), B.astype(np.float16)
+            ref = np.stack([oracle.chain(A16[i], B16, scale) for i in range(batch)]) if batch > 1 else oracle.chain(A16, B16, scale)
+            _check(got, ref)
+    # the unfused baseline takes the flag too
+    A = np.random.default_rng(5).standard_normal((96, 64)).astype(np.float32)
+    B = np.random.default_rng(6).standard_normal((64, 128)).astype(np.float32)
+    got = _run(w, cuda_dev, A, B, 1.0, flags=w.FLAG_MATMUL_F16, variant=w.VARIANT_BASELINE)
+    _check(got, oracle.chain(A.astype(np.float16), B.astype(np.float16), 1.0))
+    # f16 buffers with the flag are a caller error
+    with pytest.raises(w.WtcError):
+        w.matmul_softmax(torch.zeros((8, 8), device=cuda_dev).half(), torch.zeros((8, 8), device=cuda_dev).half(), flags=w.FLAG_MATMUL_F16)
+
+
 def test_empty_and_degenerate(w, cuda_dev):
     import torch
     out = w.matmul_softmax(torch.zeros((0, 8), device=cuda_dev).half(), torch.zeros((8, 16), device=cuda_dev).half())

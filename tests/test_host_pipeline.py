@@ -82,12 +82,32 @@ def test_every_shipped_chain_compiles_to_the_expected_kernel(tmp_path):
     expect = {"cfg1_decomposed_f32_128": "simt_fused", "cfg2_f16_native_4096x1024x1024": "tc_cluster",
               "cfg3_batched_attention_named": "tc_cluster", "cfg4_vocab_logits": "tc_tiled", "cfg5_skinny_decode": "tc_tiled",
               "matmul_softmax_chain": "simt_fused", "matmul_softmax_chain_f16_native": "tc_cluster",
-              "matmul_softmax_chain_named_softmax": "simt_fused"}
+              "matmul_softmax_chain_named_softmax": "simt_fused", "matmul_softmax_chain_f16_matmul": "tc_cluster"}
     for stem, kernel in expect.items():
         out = tmp_path / stem
         r = run(["--input", os.path.join(MLIR, stem + ".mlir"), "--out-dir", str(out), "--backend-mode", "api", "--pure-api-full"])
         assert r.returncode == 0, (stem, r.stderr)
         assert f'kernel = "{kernel}"' in open(out / "fused/05.out.nvvm.runnable.mlir").read(), stem
+
+
+def test_f32_arguments_rounded_to_f16_are_recognised(tmp_path):
+    """f32 arguments may reach the matmul through arith.truncf generics (the reference's
+    matmul_softmax_chain_f16_matmul.mlir); the plan then keeps f32 buffers and asks the launch
+    layer to round them.  Any other indirection is still rejected."""
+    out = tmp_path / "o"
+    inp = os.path.join(MLIR, "matmul_softmax_chain_f16_matmul.mlir")
+    r = run(["--input", inp, "--out-dir", str(out), "--backend-mode", "api", "--pure-api-full"])
+    assert r.returncode == 0, r.stderr
+    chain = json.load(open(out / "ir" / "chain.json"))
+    assert (chain["arg_dtype"], chain["in_dtype"], chain["acc_dtype"], chain["out_dtype"]) == ("f32", "f16", "f16", "f32")
+    plan = open(out / "fused" / "05.out.nvvm.runnable.mlir").read()
+    assert 'arg_dtype = "f32", in_dtype = "f16"' in plan and "launches = 3" in plan     # two rounding passes + the fused kernel
+    ws = int(re.search(r"workspace_bytes = (\d+)", plan).group(1))
+    assert ws == 8192 * 64 * 2 + 64 * 128 * 2                                           # the two rounded copies
+    bad = tmp_path / "bad.mlir"
+    bad.write_text(open(inp).read().replace("arith.truncf %x : f32 to f16", "arith.negf %x : f32"))
+    r = run(["--input", str(bad), "--out-dir", str(tmp_path / "b"), "--backend-mode", "api", "--pure-api-full"])
+    assert r.returncode == 1 and "rounded to f16 by arith.truncf" in open(tmp_path / "b" / "ir" / "01.canonicalize.log").read()
 
 
 def test_tile_source_priority_and_overrides(tmp_path):

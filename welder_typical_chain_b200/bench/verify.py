@@ -66,7 +66,7 @@ def plan_attrs(path):
         return m.group(1) if m else d
     m = re.search(r"\bscale\s*=\s*([-+0-9.eE]+)", text)
     return dict(batch=geti("batch", 1), M=geti("M"), N=geti("N"), K=geti("K"), in_dtype=gets("in_dtype", "f32"),
-                acc_dtype=gets("acc_dtype", "f32"), scale=float(m.group(1)) if m else 1.0)
+                arg_dtype=gets("arg_dtype", None), acc_dtype=gets("acc_dtype", "f32"), scale=float(m.group(1)) if m else 1.0)
 
 
 def main():
@@ -99,6 +99,8 @@ def main():
     if args.plan:
         p = plan_attrs(args.plan)
         k, scale, f16 = p["K"], p["scale"], p["in_dtype"] == "f16"
+        if f16 and p["arg_dtype"] == "f32":
+            args.f16_rne = True      # f32 buffers rounded on the device by arith.truncf: round to nearest even
     m = dump_m if args.m <= 0 else args.m
     n = dump_n if args.n <= 0 else args.n
     if m > dump_m or n > dump_n:

@@ -143,4 +143,43 @@ cudaError_t launch_rescale_rows(void *out, int out_f32, int64_t rows, int N, int
                             global_stats, num_parts, rows);
 }
 
+// ---- f32 -> f16 rounding of an operand (the chain that truncates its f32 arguments) --------
+namespace {
+__global__ void round_to_f16_kernel(const float *__restrict__ src, __half *__restrict__ dst, int64_t rows, int64_t cols,
+                                    int64_t ld, int64_t batch_stride, int64_t total_quads, int vec) {
+  // one thread per four consecutive columns of a row (or per element when rows are not 16-byte friendly)
+  for (int64_t q = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; q < total_quads;
+       q += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    if (vec) {
+      const int64_t per_row = cols >> 2;
+      const int64_t row = q / per_row, c = (q - row * per_row) << 2;
+      const int64_t b = row / rows, r = row - b * rows;
+      const float4 v = *reinterpret_cast<const float4 *>(src + b * batch_stride + r * ld + c);
+      const __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+      uint2 o;
+      o.x = *reinterpret_cast<const uint32_t *>(&lo);
+      o.y = *reinterpret_cast<const uint32_t *>(&hi);
+      *reinterpret_cast<uint2 *>(dst + row * cols + c) = o;
+    } else {
+      const int64_t row = q / cols, c = q - row * cols;
+      const int64_t b = row / rows, r = row - b * rows;
+      dst[q] = __float2half_rn(src[b * batch_stride + r * ld + c]);
+    }
+  }
+}
+} // namespace
+
+cudaError_t launch_round_to_f16(const float *src, void *dst, int batch, int64_t rows, int64_t cols, int64_t ld,
+                                int64_t batch_stride, cudaStream_t s) {
+  const int64_t total = static_cast<int64_t>(batch) * rows * cols;
+  if (total == 0) return cudaSuccess;
+  const int vec = (cols % 4 == 0) && (ld % 4 == 0) && (batch_stride % 4 == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0) &&
+                  ((reinterpret_cast<uintptr_t>(dst) & 7) == 0);
+  const int64_t work = vec ? total / 4 : total;
+  const int64_t blocks = (work + 255) / 256;
+  round_to_f16_kernel<<<static_cast<unsigned>(blocks < 148 * 16 ? blocks : 148 * 16), 256, 0, s>>>(
+      src, static_cast<__half *>(dst), rows, cols, ld, batch_stride, work, vec);
+  return cudaGetLastError();
+}
+
 } // namespace wtc

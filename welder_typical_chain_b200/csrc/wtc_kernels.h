@@ -66,6 +66,11 @@ cudaError_t launch_rescale_rows(void *out, int out_f32, int64_t rows, int N, int
                                 const float2 *tile_stats, const float2 *global_stats, int num_parts,
                                 cudaStream_t s);
 
+// dst[b][r][c] (dense f16: row stride cols, batch stride rows * cols) = round-to-nearest-even of
+// src[b * batch_stride + r * ld + c] (f32).
+cudaError_t launch_round_to_f16(const float *src, void *dst, int batch, int64_t rows, int64_t cols, int64_t ld,
+                                int64_t batch_stride, cudaStream_t s);
+
 // SIMT kernels: any shape, f32 or f16 operands, f32 or f16 output.
 struct SimtParams {
   int batch, M, N, K;

@@ -51,7 +51,14 @@ struct Resolved {
   int num_rb, num_nb, num_kb;
   bool b_batched;
   bool tc_ok;
+  // WTC_FLAG_MATMUL_F16: f32 operands are first rounded to dense f16 copies at the head of the
+  // workspace, then `inner` (the same chain on f16 operands) runs on the copies
+  bool trunc = false;
+  size_t stage_a = 0, stage_b = 0;
+  wtc_chain_desc inner;
 };
+
+size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
 
 bool mult8(int64_t v) { return (v & 7) == 0; }
 
@@ -79,6 +86,32 @@ int resolve(const wtc_chain_desc *in, Resolved &r) {
   if (d.b_batch_stride == 0) d.b_batch_stride = d.K * d.ldb;
   if (d.o_batch_stride == 0) d.o_batch_stride = d.M * d.ldo;
   if (!r.b_batched) d.b_batch_stride = 0;
+
+  r.trunc = false;
+  if (d.flags & WTC_FLAG_MATMUL_F16) {
+    if (d.in_dtype != WTC_F32) return fail(WTC_E_ARG, "WTC_FLAG_MATMUL_F16 needs f32 operands (in_dtype = WTC_F32)");
+    wtc_chain_desc inner = d;
+    inner.in_dtype = WTC_F16;
+    inner.flags &= ~WTC_FLAG_MATMUL_F16;
+    inner.lda = d.K; inner.a_batch_stride = d.M * d.K;
+    inner.ldb = d.N; inner.b_batch_stride = r.b_batched ? d.K * d.N : -1;
+    Resolved ri;
+    int rc = resolve(&inner, ri);
+    if (rc) return rc;
+    const wtc_chain_desc outer = d;
+    const bool bb = r.b_batched;
+    r = ri;
+    r.d = outer;
+    r.b_batched = bb;
+    r.inner = inner;
+    r.trunc = true;
+    r.tc_ok = false;          // the sharded and static-scratch entry points take f16 operands only
+    r.stage_a = align256(static_cast<size_t>(d.batch) * d.M * d.K * 2);
+    r.stage_b = align256(static_cast<size_t>(bb ? d.batch : 1) * d.K * d.N * 2);
+    r.plan.workspace_bytes += r.stage_a + r.stage_b;
+    r.plan.launches += 2;
+    return WTC_OK;
+  }
 
   wtc_plan_info &p = r.plan;
   memset(&p, 0, sizeof(p));
@@ -231,6 +264,23 @@ int launch_resolved(Resolved &r, const void *A, const void *B, void *Out, void *
   const wtc_chain_desc &d = r.d;
   if (d.M == 0 || d.N == 0) return WTC_OK;
   if (!Out || (d.K > 0 && (!A || !B))) return fail(WTC_E_ARG, "null operand pointer");
+
+  if (r.trunc) {
+    if (mode != 0) return fail(WTC_E_UNSUPPORTED, "the sharded form takes f16 operands");
+    if (!ws || ws_bytes < r.plan.workspace_bytes)
+      return fail(WTC_E_WORKSPACE, "rounding the f32 operands to f16 needs %zu workspace bytes, got %zu", r.plan.workspace_bytes, ws_bytes);
+    if ((reinterpret_cast<uintptr_t>(ws) & 15) != 0) return fail(WTC_E_ARG, "workspace must be 16-byte aligned");
+    unsigned char *base = static_cast<unsigned char *>(ws);
+    cudaError_t e = wtc::launch_round_to_f16(static_cast<const float *>(A), base, d.batch, d.M, d.K, d.lda, d.a_batch_stride, s);
+    if (e == cudaSuccess)
+      e = wtc::launch_round_to_f16(static_cast<const float *>(B), base + r.stage_a, r.b_batched ? d.batch : 1, d.K, d.N, d.ldb,
+                                   r.b_batched ? d.b_batch_stride : 0, s);
+    if (e != cudaSuccess) return cuda_fail(e, "operand rounding launch");
+    Resolved ri;
+    int rc = resolve(&r.inner, ri);
+    if (rc) return rc;
+    return launch_resolved(ri, base, base + r.stage_a, Out, base + r.stage_a + r.stage_b, ws_bytes - r.stage_a - r.stage_b, row_stats, 0, s, status);
+  }
 
   if (r.plan.kernel == WTC_KERNEL_SIMT_UNFUSED) {
     if (mode != 0) return fail(WTC_E_UNSUPPORTED, "the baseline variant has no sharded form");

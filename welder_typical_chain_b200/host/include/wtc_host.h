@@ -21,7 +21,9 @@ struct ChainSpec {
   int64_t batch = 1, M = 0, N = 0, K = 0;
   bool batched = false;        // linalg.batch_matmul + softmax over the last of 3 dims
   bool bBatched = false;       // B carries the batch dimension too
-  std::string inType = "f32";  // element type of A and B
+  std::string inType = "f32";  // element type of the matmul's operands
+  std::string argType = "f32"; // element type of the function arguments: inType, or f32 when the chain rounds
+                               // its arguments to f16 first (mlir_pipeline/matmul_softmax_chain_f16_matmul.mlir:18-44)
   std::string accType = "f32"; // element type of the matmul's outs
   std::string outType = "f32"; // element type of the function result
   double scale = 1.0;          // product of constant arith.mulf factors between matmul and softmax

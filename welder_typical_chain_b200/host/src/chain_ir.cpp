@@ -1,5 +1,6 @@
 // Chain recogniser for the one operator this build serves:
 //   func @main(%A: tensor<[b x] M x K x T>, %B: tensor<[b x] K x N x T>) -> tensor<[b x] M x N x U>
+//   [two generics arith.truncf f32 -> f16 on %A and %B]
 //   linalg.matmul | linalg.batch_matmul  ins(%A, %B) outs(<fill 0> : tensor<.. x Tacc>)
 //   [generic extf] [generic arith.mulf by a constant = scale]
 //   either  linalg.softmax dimension(last)
@@ -212,7 +213,19 @@ bool parseChain(const std::string &rawText, ChainSpec &spec, std::string &diag) 
   if (b.dims[o] != spec.K) { diag = "K mismatch between A and B"; return false; }
   if (c.dims[o] != spec.M || c.dims[o + 1] != spec.N || (spec.batched && (b.dims[0] != spec.batch || c.dims[0] != spec.batch))) { diag = "matmul result shape does not match its operands"; return false; }
   if (a.elem != b.elem) { diag = "A and B must share an element type"; return false; }
-  if (a.dims != argTypes[0].dims || b.dims != argTypes[1].dims || a.elem != argTypes[0].elem) { diag = "matmul must consume the function arguments directly"; return false; }
+  if (a.dims != argTypes[0].dims || b.dims != argTypes[1].dims) { diag = "matmul must consume the function arguments (shapes differ)"; return false; }
+  if (argTypes[0].elem != argTypes[1].elem) { diag = "A and B arguments must share an element type"; return false; }
+  if (a.elem != argTypes[0].elem) {
+    // the one accepted indirection: f32 arguments rounded to f16 by arith.truncf generics ahead of the matmul
+    static const std::regex truncRe(R"(arith\.truncf\s+%[\w.]+\s*:\s*f32\s+to\s+f16)");
+    const std::string head = text.substr(0, mm);
+    const auto nTrunc = std::distance(std::sregex_iterator(head.begin(), head.end(), truncRe), std::sregex_iterator());
+    if (!(argTypes[0].elem == "f32" && a.elem == "f16" && nTrunc >= 2)) {
+      diag = "matmul must consume the function arguments directly, or f32 arguments rounded to f16 by arith.truncf";
+      return false;
+    }
+  }
+  spec.argType = argTypes[0].elem;
   spec.inType = a.elem;
   spec.accType = c.elem;
   if (resType.dims != c.dims) { diag = "function result shape must equal the matmul result shape"; return false; }
@@ -269,7 +282,7 @@ std::string chainToJson(const ChainSpec &s) {
     << "  \"func\": \"" << s.funcName << "\",\n"
     << "  \"batch\": " << s.batch << ", \"M\": " << s.M << ", \"N\": " << s.N << ", \"K\": " << s.K << ",\n"
     << "  \"batched\": " << (s.batched ? "true" : "false") << ", \"b_batched\": " << (s.bBatched ? "true" : "false") << ",\n"
-    << "  \"in_dtype\": \"" << s.inType << "\", \"acc_dtype\": \"" << s.accType << "\", \"out_dtype\": \"" << s.outType << "\",\n"
+    << "  \"arg_dtype\": \"" << s.argType << "\", \"in_dtype\": \"" << s.inType << "\", \"acc_dtype\": \"" << s.accType << "\", \"out_dtype\": \"" << s.outType << "\",\n"
     << "  \"scale\": " << scale << ",\n"
     << "  \"softmax_form\": \"" << (s.namedSoftmax ? "named" : "decomposed") << "\"\n"
     << "}\n";

@@ -61,7 +61,8 @@ bool queryPlan(const ir::ChainSpec &spec, const CompileRequest &req, PlanResult 
   d.batch = static_cast<int32_t>(spec.batch);
   d.M = spec.M; d.N = spec.N; d.K = spec.K;
   d.b_batch_stride = spec.bBatched || spec.batch == 1 ? 0 : -1;
-  d.in_dtype = dtypeCode(spec.inType);
+  d.in_dtype = dtypeCode(spec.argType);
+  if (spec.argType != spec.inType) d.flags |= WTC_FLAG_MATMUL_F16;   // f32 buffers, rounded to f16 before the contraction
   d.out_dtype = dtypeCode(spec.outType);
   d.acc_dtype = dtypeCode(spec.accType);
   d.scale = static_cast<float>(spec.scale);
@@ -74,7 +75,7 @@ bool queryPlan(const ir::ChainSpec &spec, const CompileRequest &req, PlanResult 
 }
 
 std::string postbufferizeText(const ir::ChainSpec &s, const CompileRequest &req) {
-  const std::string aT = memrefType(s, s.M, s.K, s.inType, s.batched), bT = memrefType(s, s.K, s.N, s.inType, s.bBatched),
+  const std::string aT = memrefType(s, s.M, s.K, s.argType, s.batched), bT = memrefType(s, s.K, s.N, s.argType, s.bBatched),
                     oT = memrefType(s, s.M, s.N, s.outType, s.batched);
   const char *mm = s.batched ? "linalg.batch_matmul" : "linalg.matmul";
   std::ostringstream o;
@@ -172,7 +173,7 @@ std::string runnableText(const ir::ChainSpec &s, const CompileRequest &req, cons
     << "// the runner rebuilds the chain descriptor from the attributes below and calls wtc_matmul_softmax_launch.\n"
     << "module attributes {gpu.container_module, wtc.target = \"sm_100a\"} {\n"
     << "  wtc.chain {batch = " << s.batch << ", M = " << s.M << ", N = " << s.N << ", K = " << s.K << ", b_batched = " << (s.bBatched ? 1 : 0)
-    << ", in_dtype = \"" << s.inType << "\", acc_dtype = \"" << s.accType << "\", out_dtype = \"" << s.outType << "\", scale = " << scale << "}\n"
+    << ", arg_dtype = \"" << s.argType << "\", in_dtype = \"" << s.inType << "\", acc_dtype = \"" << s.accType << "\", out_dtype = \"" << s.outType << "\", scale = " << scale << "}\n"
     << "  wtc.tiles {requested_m = " << req.tileM << ", requested_n = " << req.tileN << ", requested_k = " << req.tileK << ", tile_m = " << p.tile_m
     << ", tile_n = " << p.tile_n << ", tile_k = " << p.tile_k << ", thread_tile_m = " << req.threadTileM << ", thread_tile_n = " << req.threadTileN
     << ", substituted = " << p.tile_substituted << "}\n"

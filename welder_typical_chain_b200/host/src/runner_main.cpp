@@ -156,18 +156,20 @@ int main(int argc, char **argv) {
   const std::string plan = readAll(planPath);
   if (plan.empty()) { std::cerr << "error: cannot open file: " << planPath << "\n"; return 2; }
   long long batch = 1, M = 0, N = 0, K = 0, bBatched = 0, tm = 0, tn = 0, tk = 0;
-  std::string inT, accT, outT, variant = "fused";
+  std::string inT, argT, accT, outT, variant = "fused";
   double scale = 1.0;
   if (!attrInt(plan, "batch", batch) || !attrInt(plan, "M", M) || !attrInt(plan, "N", N) || !attrInt(plan, "K", K) ||
       !attrStr(plan, "in_dtype", inT) || !attrStr(plan, "acc_dtype", accT) || !attrStr(plan, "out_dtype", outT)) {
     std::cerr << "error: " << planPath << " is not a wtc launch plan (no wtc.chain attributes)\n";
     return 2;
   }
+  if (!attrStr(plan, "arg_dtype", argT)) argT = inT;   // buffers hold arg_dtype; f32 buffers with in_dtype f16 are rounded on the device
+  const bool roundOnDevice = argT == "f32" && inT == "f16";
   attrInt(plan, "b_batched", bBatched); attrDouble(plan, "scale", scale); attrStr(plan, "variant", variant);
   attrInt(plan, "requested_m", tm); attrInt(plan, "requested_n", tn); attrInt(plan, "requested_k", tk);
   if (runM > 0 && runM <= M) M = runM;
   if (runBatch > 0 && runBatch <= batch) batch = runBatch;
-  const size_t inSz = inT == "f16" ? 2 : 4, outSz = outT == "f16" ? 2 : 4;
+  const size_t inSz = argT == "f16" ? 2 : 4, outSz = outT == "f16" ? 2 : 4;
   const size_t aElems = static_cast<size_t>(batch) * M * K, bElems = static_cast<size_t>(bBatched ? batch : 1) * K * N,
                oElems = static_cast<size_t>(batch) * M * N;
   if (listMemrefs) {
@@ -200,7 +202,8 @@ int main(int argc, char **argv) {
   d.batch = static_cast<int32_t>(batch);
   d.M = M; d.N = N; d.K = K;
   d.b_batch_stride = (bBatched || batch == 1) ? 0 : -1;
-  d.in_dtype = inT == "f16" ? WTC_F16 : WTC_F32;
+  d.in_dtype = argT == "f16" ? WTC_F16 : WTC_F32;
+  if (roundOnDevice) d.flags |= WTC_FLAG_MATMUL_F16;
   d.out_dtype = outT == "f16" ? WTC_F16 : WTC_F32;
   d.acc_dtype = accT == "f16" ? WTC_F16 : WTC_F32;
   d.scale = static_cast<float>(scale);

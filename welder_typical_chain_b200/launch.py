@@ -15,7 +15,7 @@ _LIB = None
 
 F32, F16 = 0, 1
 VARIANT_FUSED, VARIANT_BASELINE = 0, 1
-FLAG_FORCE_SIMT, FLAG_FORCE_TILED = 0x1, 0x2
+FLAG_FORCE_SIMT, FLAG_FORCE_TILED, FLAG_MATMUL_F16 = 0x1, 0x2, 0x4
 KERNEL_SIMT_FUSED, KERNEL_TC_CLUSTER, KERNEL_TC_TILED, KERNEL_SIMT_UNFUSED = 0, 1, 2, 3
 KERNEL_NAMES = {0: "simt_fused", 1: "tc_cluster", 2: "tc_tiled", 3: "simt_unfused"}
 

@@ -25,20 +25,33 @@ def iters(rank, reduce_last):
     return "[" + ", ".join('"reduction"' if (reduce_last and i == rank - 1) else '"parallel"' for i in range(rank)) + "]"
 
 
-def chain(batch, M, N, K, in_t="f32", acc_t="f32", out_t="f32", scale=1.0, named=False, title=""):
+def chain(batch, M, N, K, in_t="f32", acc_t="f32", out_t="f32", scale=1.0, named=False, title="", arg_t=None):
+    """arg_t: element type of the function arguments when it differs from the matmul's operand
+    type in_t (f32 arguments rounded to f16 ahead of the matmul)."""
     rank = 3 if batch > 1 else 2
     pre = [batch] if batch > 1 else []
     a_t, b_t = ttype(pre + [M, K], in_t), ttype(pre + [K, N], in_t)
+    arg_t = arg_t or in_t
+    a_arg, b_arg = ttype(pre + [M, K], arg_t), ttype(pre + [K, N], arg_t)
     c_acc, c32 = ttype(pre + [M, N], acc_t), ttype(pre + [M, N], "f32")
     red = ttype(pre + [M], "f32")
     res_t = ttype(pre + [M, N], out_t)
     idm, drop = maps(rank)
     mm = "linalg.batch_matmul" if batch > 1 else "linalg.matmul"
-    L = [f"// {title}", "module {", f"  func.func @main(%A: {a_t}, %B: {b_t}) -> {res_t} {{",
-         f"    %zero_acc = arith.constant 0.0 : {acc_t}",
-         f"    %c_empty = tensor.empty() : {c_acc}",
-         f"    %c_init = linalg.fill ins(%zero_acc : {acc_t}) outs(%c_empty : {c_acc}) -> {c_acc}",
-         f"    %C = {mm} ins(%A, %B : {a_t}, {b_t}) outs(%c_init : {c_acc}) -> {c_acc}"]
+    L = [f"// {title}", "module {", f"  func.func @main(%A: {a_arg}, %B: {b_arg}) -> {res_t} {{"]
+    a_val, b_val = "%A", "%B"
+    if arg_t != in_t:
+        for nm, src_t, dst_t in (("A", a_arg, a_t), ("B", b_arg, b_t)):
+            L += [f"    // {nm} rounded to {in_t} for the matmul", f"    %{nm}n_empty = tensor.empty() : {dst_t}",
+                  f"    %{nm}n = linalg.generic {{indexing_maps = [{idm}, {idm}], iterator_types = {iters(rank, False)}}}",
+                  f"        ins(%{nm} : {src_t}) outs(%{nm}n_empty : {dst_t}) {{",
+                  f"      ^bb0(%x: {arg_t}, %o: {in_t}):", f"        %y = arith.truncf %x : {arg_t} to {in_t}", f"        linalg.yield %y : {in_t}",
+                  f"      }} -> {dst_t}"]
+        a_val, b_val = "%An", "%Bn"
+    L += [f"    %zero_acc = arith.constant 0.0 : {acc_t}",
+          f"    %c_empty = tensor.empty() : {c_acc}",
+          f"    %c_init = linalg.fill ins(%zero_acc : {acc_t}) outs(%c_empty : {c_acc}) -> {c_acc}",
+          f"    %C = {mm} ins({a_val}, {b_val} : {a_t}, {b_t}) outs(%c_init : {c_acc}) -> {c_acc}"]
     cur = "%C"
 
     def elementwise(name, body, in_types, out_type, ins, comment):
@@ -95,6 +108,8 @@ FILES = {
     "matmul_softmax_chain.mlir": dict(batch=1, M=8192, N=128, K=64, title="decomposed f32 chain at the reference's shape"),
     "matmul_softmax_chain_f16_native.mlir": dict(batch=1, M=8192, N=128, K=64, in_t="f16", acc_t="f16",
                                                  title="f16 operands, f16 matmul result, f32 softmax, f32 result"),
+    "matmul_softmax_chain_f16_matmul.mlir": dict(batch=1, M=8192, N=128, K=64, arg_t="f32", in_t="f16", acc_t="f16",
+                                                 title="f32 arguments rounded to f16, f16 matmul result, f32 softmax, f32 result"),
     "matmul_softmax_chain_named_softmax.mlir": dict(batch=1, M=8192, N=128, K=64, named=True, title="named linalg.softmax at the reference's shape"),
     # the benchmark configurations
     "cfg1_decomposed_f32_128.mlir": dict(batch=1, M=128, N=128, K=128, title="configuration 1: decomposed f32 chain, 128 cubed"),
