@@ -35,19 +35,19 @@ def test_struct_layout_matches_header(wtc_lib):
     assert e.value.code == -1 and "struct_size" in str(e.value)
 
 
-@pytest.mark.parametrize("shape,kernel,cluster,launches", [
-    ((1, 4096, 1024, 1024), "tc_cluster", 4, 1),      # f16 native chain
-    ((64, 2048, 2048, 128), "tc_cluster", 8, 1),      # batched attention scores
-    ((1, 8192, 32000, 4096), "tc_tiled", 1, 2),       # vocab-wide logits: online two-pass
-    ((1, 16, 32000, 4096), "tc_tiled", 1, 2),         # skinny decode
-    ((1, 8192, 128, 64), "tc_cluster", 1, 1),         # the reference's own shape
+@pytest.mark.parametrize("shape,kernel,cluster,launches,threads,stages", [
+    ((1, 4096, 1024, 1024), "tc_cluster", 4, 1, 320, 3),      # f16 native chain: one tile per CTA, split epilogue
+    ((64, 2048, 2048, 128), "tc_cluster", 8, 1, 640, 3),      # batched attention scores: many tiles per CTA, relay epilogue
+    ((1, 8192, 32000, 4096), "tc_tiled", 1, 2, 320, 6),       # vocab-wide logits: online two-pass, CTA pairs
+    ((1, 16, 32000, 4096), "tc_tiled", 1, 2, 320, 4),         # skinny decode
+    ((1, 8192, 128, 64), "tc_cluster", 1, 1, 320, 3),         # the reference's own shape: 64 row blocks on 148 one-CTA clusters
 ])
-def test_plans_for_benchmark_configs(wtc_lib, shape, kernel, cluster, launches):
+def test_plans_for_benchmark_configs(wtc_lib, shape, kernel, cluster, launches, threads, stages):
     p = wtc_lib.plan_query(wtc_lib.make_desc(*shape))
     assert wtc_lib.launch.KERNEL_NAMES[p.kernel] == kernel
     assert (p.cluster_n, p.launches) == (cluster, launches)
     assert (p.tile_m, p.tile_n, p.tile_k) == (128, 256, 64)
-    assert p.tmem_columns == 512 and p.threads == 320
+    assert p.tmem_columns == 512 and (p.threads, p.stages) == (threads, stages)
     if kernel == "tc_tiled":
         b, M, N, K = shape
         assert p.workspace_bytes == b * M * ((N + 255) // 256) * 8

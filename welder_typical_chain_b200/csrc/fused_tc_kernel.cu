@@ -42,9 +42,6 @@ constexpr int BK = kTcBlockK;
 // four warps per scheduler hide the TMEM-load and barrier latencies the eight-warp form exposes).
 constexpr int kThreadsFor(int ew, bool relay = false) { return relay ? 640 : 64 + ew * 32; }
 constexpr int kMaxCluster = 8;
-// tiles per CTA from which the relay epilogue is chosen unless a form is asked for: with one tile
-// per CTA its two groups cannot overlap (measured equal to the split form on config 2)
-constexpr int kRelayMinTiles = 2;
 
 // OUT_TILES: 32-row x 64-column f16 staging tiles per epilogue warp (2 = the warp's two
 // column groups never wait for each other's TMA read; 1 = smaller, leaves room for a stage).

@@ -88,6 +88,9 @@ cudaError_t launch_simt_unfused(const void *A, const void *B, void *Out, void *w
 size_t simt_unfused_workspace_bytes(const SimtParams &p);
 
 constexpr int kTcBlockM = 128;
+// Tiles per CTA from which the relay epilogue is chosen unless a form is asked for: with one tile
+// per CTA its two groups cannot overlap (measured equal to the split form on config 2).
+constexpr int kRelayMinTiles = 2;
 constexpr int kTcBlockK = 64;
 constexpr int kTcBlockN = 256;
 

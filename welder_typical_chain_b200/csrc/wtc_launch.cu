@@ -139,15 +139,20 @@ int resolve(const wtc_chain_desc *in, Resolved &r) {
     p.tile_m = wtc::kTcBlockM; p.tile_n = r.bn; p.tile_k = wtc::kTcBlockK;
     p.threads = 320;
     p.tmem_columns = 2 * r.bn;
+    // threads / stages as the launchers choose them on a 148-SM part (the plan is made without a device)
+    const bool plain = r.bn == wtc::kTcBlockN && d.out_dtype == WTC_F16;
     if (r.num_nb <= 8 && !(d.flags & WTC_FLAG_FORCE_TILED)) {
       p.kernel = WTC_KERNEL_TC_CLUSTER;
       p.launches = 1;
       p.cluster_n = r.num_nb;
-      p.stages = 3;
+      p.stages = r.bn == 128 ? 4 : 3;
+      const int64_t resident = 148 / r.num_nb;
+      const int64_t tiles_per_cta = (static_cast<int64_t>(d.batch) * r.num_rb + resident - 1) / resident;
+      if (plain && tiles_per_cta >= wtc::kRelayMinTiles) p.threads = 640;   // relay epilogue: twenty warps
     } else {
       p.kernel = WTC_KERNEL_TC_TILED;
       p.launches = 2;
-      p.stages = 4;
+      p.stages = (r.bn == 128 || (plain && r.num_rb >= 2 && r.num_kb >= 8)) ? 6 : 4;   // 6: 128-column tiles, or CTA pairs (long K)
       p.workspace_bytes = static_cast<size_t>(d.batch) * d.M * r.num_nb * sizeof(float2);
     }
   } else {

@@ -13,6 +13,7 @@
 #include <fstream>
 #include <iostream>
 #include <mutex>
+#include <regex>
 #include <sstream>
 
 namespace wtc::pipeline {
@@ -163,6 +164,20 @@ bool validatePostbufferizeArtifacts(const std::string &artifactDir, std::string 
     << "ptx_st_local_count=" << countContains(runnable, "st.local") << "\n"
     << "launch_func_count=" << countContains(runnable, "gpu.launch_func") << "\n"
     << "tcgen05_kernel=" << (runnable.find("kernel = \"tc_") != std::string::npos ? 1 : 0) << "\n";
+  // kernel facts from the plan attributes: what the counters above meant for the reference's
+  // generated code (tensor-core use, on-chip footprint) read off a precompiled tcgen05 kernel
+  auto planInt = [&](const char *key) -> long long {
+    std::smatch m;
+    const std::regex re(std::string("\\b") + key + "\\s*=\\s*(-?[0-9]+)");
+    return std::regex_search(runnable, m, re) ? std::stoll(m[1].str()) : 0;
+  };
+  const bool tc = runnable.find("kernel = \"tc_") != std::string::npos;
+  r << "cluster_ctas=" << planInt("cluster_n") << "\n"
+    << "threads_per_cta=" << planInt("threads") << "\n"
+    << "pipeline_stages=" << planInt("stages") << "\n"
+    << "tmem_columns=" << planInt("tmem_columns") << "\n"
+    << "workspace_bytes=" << planInt("workspace_bytes") << "\n"
+    << "tcgen05_mma_per_tile=" << (tc ? (planInt("K") + 63) / 64 * 4 : 0) << "\n";
   if (!writeAll((out / "postbufferize_report.txt").string(), r.str())) { diagnostic = "failed to write postbufferize report"; return false; }
   diagnostic.clear();
   return true;
