@@ -139,6 +139,9 @@ int wtc_matmul_softmax_finish_launch(const wtc_chain_desc *desc, void *Out, cons
 /*
  * Whole call with HOST buffers: copies A and B to the device, launches, copies
  * Out back and synchronises.  Device buffers are cached per thread between calls.
+ * Large calls are cut into row (or batch) ranges that move through three streams, so
+ * both PCIe directions and the kernels overlap; pinned host memory makes the copies
+ * asynchronous, pageable memory works but serialises them.
  * This is what a host-side caller of the reference would otherwise do around the
  * profiler's cuMemcpyHtoD / launch / dump sequence (WelderProfiler.cpp:601-677,
  * :808-864).
@@ -198,6 +201,7 @@ int wtc_matmul_softmax_time(const wtc_chain_desc *desc, const void *A, const voi
  *   WTC_EW=16                 sixteen epilogue warps (cluster flavour, staged stores)
  *   WTC_STORE=direct          256-bit register stores instead of staged TMA stores
  *   WTC_PAIR=0|1              never | always pair CTAs for tcgen05 cta_group::2
+ *   WTC_HOST_SLABS=n          pieces the host-buffer entry point cuts a call into (default: ~6 MB each, at most 8)
  *   WTC_NO_PDL=1              (read once at load) no programmatic dependent launch
  *   WTC_TL_MODE=0|1|2         layout of the profiling stamps (wtc_debug_set_timeline)
  */

@@ -242,6 +242,32 @@ def test_host_buffer_entry_point(w, cuda_dev):
     _check(w.matmul_softmax_host(A32, B32, 1.0), oracle.chain(A32, B32, 1.0))
 
 
+@pytest.mark.parametrize("slabs", ["1", "3", "8"])
+def test_host_entry_point_slabs(w, cuda_dev, monkeypatch, slabs):
+    """The host-buffer call moves row ranges (or batch ranges) through copy-in, compute and
+    copy-out streams; any cut gives the same bytes as the single-slab call."""
+    monkeypatch.setenv("WTC_HOST_SLABS", slabs)
+    cases = [((1000, 136), (136, 1024), 0.07),             # ragged M: the last slab is short
+             ((5, 300, 72), (5, 72, 520), 0.2),            # batched, B per batch: slabs are batch ranges
+             ((4, 130, 64), (64, 256), 0.5),               # batched, B shared
+             ((700, 64), (64, 2304), 0.1)]                 # two-pass tiled schedule per slab
+    for sa, sb, scale in cases:
+        A = oracle.normal(sa, sa[-2]); B = oracle.normal(sb, sb[-1])
+        out = w.matmul_softmax_host(A, B, scale)
+        if A.ndim == 3:
+            ref = np.stack([oracle.chain(A[i], B[i] if B.ndim == 3 else B, scale) for i in range(A.shape[0])])
+        else:
+            ref = oracle.chain(A, B, scale)
+        _check(out, ref)
+        monkeypatch.setenv("WTC_HOST_SLABS", "1")
+        assert np.array_equal(out, w.matmul_softmax_host(A, B, scale)), (sa, slabs)
+        monkeypatch.setenv("WTC_HOST_SLABS", slabs)
+    A = np.random.default_rng(3).standard_normal((520, 64)).astype(np.float32)      # f32 buffers rounded on the device, per slab
+    B = np.random.default_rng(4).standard_normal((64, 256)).astype(np.float32)
+    out = w.matmul_softmax_host(A, B, 1.0, flags=w.FLAG_MATMUL_F16)
+    _check(out, oracle.chain(A.astype(np.float16), B.astype(np.float16), 1.0))
+
+
 def test_n_sharded_partial_and_finish(w, cuda_dev):
     """Two column shards on one GPU, combined the way two GPUs would combine them:
     per-row (max, sum) of each shard gathered, then each shard normalised."""

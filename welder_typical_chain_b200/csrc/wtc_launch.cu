@@ -478,6 +478,10 @@ int wtc_matmul_softmax_time(const wtc_chain_desc *desc, const void *A, const voi
   return wtc_check_device_status(nullptr, stream);
 }
 
+// Host buffers in, host buffer out.  The call is cut into slabs (row ranges, or batch ranges
+// of a batched call) that move through three streams -- copy in, compute, copy out -- so the
+// transfer of slab i+1 and the read-back of slab i-1 run under the kernel of slab i and the
+// two PCIe directions are busy at the same time.  B goes first, whole.
 int wtc_matmul_softmax_host(const wtc_chain_desc *desc, const void *hostA, const void *hostB, void *hostOut) {
   Resolved r;
   int rc = resolve(desc, r);
@@ -508,22 +512,77 @@ int wtc_matmul_softmax_host(const wtc_chain_desc *desc, const void *hostA, const
       }
     }
   }
-  thread_local cudaStream_t hs = nullptr;
-  thread_local int hs_dev = -1;
-  if (!hs || hs_dev != dev) {
-    e = cudaStreamCreateWithFlags(&hs, cudaStreamNonBlocking);
-    if (e != cudaSuccess) return cuda_fail(e, "cudaStreamCreate");
-    hs_dev = dev;
+  constexpr int kMaxSlabs = 8;
+  struct Lanes { cudaStream_t in = nullptr, run = nullptr, out = nullptr; cudaEvent_t b_in = nullptr, a_in[kMaxSlabs] = {}, done[kMaxSlabs] = {}; int dev = -1; };
+  thread_local Lanes ln;
+  if (ln.dev != dev) {
+    ln = Lanes();
+    for (cudaStream_t *st : {&ln.in, &ln.run, &ln.out}) {
+      e = cudaStreamCreateWithFlags(st, cudaStreamNonBlocking);
+      if (e != cudaSuccess) return cuda_fail(e, "cudaStreamCreate");
+    }
+    e = cudaEventCreateWithFlags(&ln.b_in, cudaEventDisableTiming);
+    for (int i = 0; i < kMaxSlabs && e == cudaSuccess; ++i) {
+      e = cudaEventCreateWithFlags(&ln.a_in[i], cudaEventDisableTiming);
+      if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ln.done[i], cudaEventDisableTiming);
+    }
+    if (e != cudaSuccess) return cuda_fail(e, "cudaEventCreate");
+    ln.dev = dev;
   }
-  e = cudaMemcpyAsync(bufs[0].p, hostA, a_bytes, cudaMemcpyHostToDevice, hs);
-  if (e != cudaSuccess) return cuda_fail(e, "copy of A to the device");
-  e = cudaMemcpyAsync(bufs[1].p, hostB, b_bytes, cudaMemcpyHostToDevice, hs);
+
+  // ---- slabs: about 6 MB of A + Out traffic each (measured on PCIe 5 x16: two or three slabs are best for
+  //      17 MB, each slab costs ~10 us of host enqueue time), at most kMaxSlabs; rows in multiples of the 128-row tile
+  const bool by_batch = d.batch > 1;
+  const int64_t units = by_batch ? d.batch : (d.M + wtc::kTcBlockM - 1) / wtc::kTcBlockM;
+  int64_t slabs = static_cast<int64_t>((a_bytes + o_bytes) / (6u << 20));
+  if (slabs < 1) slabs = 1;
+  if (slabs > kMaxSlabs) slabs = kMaxSlabs;
+  if (const char *ev = getenv("WTC_HOST_SLABS")) slabs = atoi(ev) > 0 ? atoi(ev) : 1;
+  if (slabs > kMaxSlabs) slabs = kMaxSlabs;
+  if (slabs > units) slabs = units;
+  const int64_t per = (units + slabs - 1) / slabs;
+
+  e = cudaMemcpyAsync(bufs[1].p, hostB, b_bytes, cudaMemcpyHostToDevice, ln.in);
+  if (e == cudaSuccess) e = cudaEventRecord(ln.b_in, ln.in);
+  if (e == cudaSuccess) e = cudaStreamWaitEvent(ln.run, ln.b_in, 0);
   if (e != cudaSuccess) return cuda_fail(e, "copy of B to the device");
-  rc = launch_resolved(r, bufs[0].p, bufs[1].p, bufs[2].p, bufs[3].p, bufs[3].cap, nullptr, 0, hs, nullptr);
-  if (rc) return rc;
-  e = cudaMemcpyAsync(hostOut, bufs[2].p, o_bytes, cudaMemcpyDeviceToHost, hs);
-  if (e != cudaSuccess) return cuda_fail(e, "copy of the result to the host");
-  return wtc_check_device_status(nullptr, hs);
+  int n = 0;
+  for (int64_t u0 = 0; u0 < units; u0 += per, ++n) {
+    const int64_t u1 = u0 + per < units ? u0 + per : units;
+    wtc_chain_desc sd = d;
+    size_t a_off, o_off, a_len, o_len, b_off = 0;
+    if (by_batch) {
+      sd.batch = static_cast<int32_t>(u1 - u0);
+      a_off = static_cast<size_t>(u0) * d.a_batch_stride * in_sz;  a_len = static_cast<size_t>(u1 - u0) * d.a_batch_stride * in_sz;
+      o_off = static_cast<size_t>(u0) * d.o_batch_stride * out_sz; o_len = static_cast<size_t>(u1 - u0) * d.o_batch_stride * out_sz;
+      if (r.b_batched) b_off = static_cast<size_t>(u0) * d.b_batch_stride * in_sz;
+      else sd.b_batch_stride = -1;
+    } else {
+      const int64_t r0 = u0 * wtc::kTcBlockM, r1 = u1 * wtc::kTcBlockM < d.M ? u1 * wtc::kTcBlockM : d.M;
+      sd.M = r1 - r0;
+      sd.a_batch_stride = 0; sd.o_batch_stride = 0;
+      a_off = static_cast<size_t>(r0) * d.lda * in_sz;  a_len = static_cast<size_t>(r1 - r0) * d.lda * in_sz;
+      o_off = static_cast<size_t>(r0) * d.ldo * out_sz; o_len = static_cast<size_t>(r1 - r0) * d.ldo * out_sz;
+    }
+    Resolved sr;
+    rc = resolve(&sd, sr);
+    if (rc) return rc;
+    e = cudaMemcpyAsync(static_cast<char *>(bufs[0].p) + a_off, static_cast<const char *>(hostA) + a_off, a_len, cudaMemcpyHostToDevice, ln.in);
+    if (e == cudaSuccess) e = cudaEventRecord(ln.a_in[n], ln.in);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(ln.run, ln.a_in[n], 0);
+    if (e != cudaSuccess) return cuda_fail(e, "copy of A to the device");
+    rc = launch_resolved(sr, static_cast<char *>(bufs[0].p) + a_off, static_cast<char *>(bufs[1].p) + b_off,
+                         static_cast<char *>(bufs[2].p) + o_off, bufs[3].p, bufs[3].cap, nullptr, 0, ln.run, nullptr);
+    if (rc) return rc;
+    e = cudaEventRecord(ln.done[n], ln.run);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(ln.out, ln.done[n], 0);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(static_cast<char *>(hostOut) + o_off, static_cast<char *>(bufs[2].p) + o_off, o_len, cudaMemcpyDeviceToHost, ln.out);
+    if (e != cudaSuccess) return cuda_fail(e, "copy of the result to the host");
+  }
+  // the next call's first copy must not overtake this call's last kernel or read-back
+  e = cudaStreamWaitEvent(ln.in, ln.done[n - 1], 0);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaStreamWaitEvent");
+  return wtc_check_device_status(nullptr, ln.out);
 }
 
 int wtc_debug_set_umma_geometry(uint32_t a_lbo, uint32_t a_sbo, uint32_t a_kstep, uint32_t b_lbo, uint32_t b_sbo,
