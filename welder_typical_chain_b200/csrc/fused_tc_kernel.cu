@@ -25,6 +25,12 @@
 // st.async -- then p = e * factor, packed to f16, staged 64 columns at a time in
 // 128-byte-swizzled shared memory and written with TMA stores.
 //
+// Other forms of the same kernel (template parameters): RELAY -- twenty warps, an "exp"
+// group and a "store" group that work on consecutive tiles at the same time, the exp values
+// parked in TMEM between them (chosen when a CTA sees several tiles); PAIR -- two CTAs issue
+// one 256-row tcgen05 cta_group::2 MMA; OUT32 -- f32 probabilities; EW = 16 -- a row's
+// columns split four ways; OUT_TILES = 0 -- register-to-global stores without staging.
+//
 // Operand layouts: A [M,K] is K-major, staged as 128 rows x 128 B with the 128-byte
 // swizzle.  B [K,N] has N contiguous, i.e. it is MN-major for the MMA: it is staged
 // as BN/64 blocks of (64 k-rows x 128 B), and the instruction descriptor's B-major
