@@ -157,8 +157,6 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
-    ap.add_argument("--graph", choices=["auto", "on", "off"], default="auto",
-                    help="replay each step from a CUDA graph (auto: off)")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
     if args.warmup < 3:
@@ -231,16 +229,16 @@ def main():
     if col_sharded:
         shard_calls = [wtc.PreparedShardCall(A, B, O, scale, ws, row_stats, all_stats, world) for (A, B, O) in sets]
 
-        def step(i, sp=None):
+        def step(i):
             c = shard_calls[i % nsets]
-            c.partial(sp or sptr)
+            c.partial(sptr)
             dist.all_gather_into_tensor(all_stats, row_stats)      # [M,2] f32 per rank over NVLink
-            c.finish(sp or sptr)
+            c.finish(sptr)
     else:
         prepared = [wtc.PreparedCall(A, B, O, scale, workspace=ws) for (A, B, O) in sets]
 
-        def step(i, sp=None):
-            prepared[i % nsets].launch(sp or sptr)
+        def step(i):
+            prepared[i % nsets].launch(sptr)
 
     # ---- parity spot check on this rank's first buffer set (sampled rows, CPU checker) ----
     parity = None
@@ -283,24 +281,6 @@ def main():
     for i in range(args.warmup):
         step(i)
     wtc.check_device_status()
-    # One CUDA graph per buffer set: the step's launches (and its collective) are recorded once
-    # and replayed, so the host pays one graph launch per step instead of several enqueues.
-    use_graph = args.graph == "on"
-    if use_graph:
-        torch.cuda.synchronize()
-        graphs = []
-        for k in range(nsets):
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                step(k, wtc.current_stream_ptr())
-            graphs.append(g)
-        eager_step = step
-
-        def step(i):
-            graphs[i % nsets].replay()
-        for i in range(min(3, args.warmup)):
-            step(i)
-        wtc.check_device_status()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
@@ -407,8 +387,7 @@ def main():
                             l2=f"{nsets} rotating buffer sets of {set_bytes / 1e6:.1f} MB "
                                f"({nsets * set_bytes / 1e6:.0f} MB vs 126 MB L2); timed region = {args.steps} back-to-back calls",
                             kernel=wtc.launch.KERNEL_NAMES[plan.kernel], cluster_n=plan.cluster_n,
-                            tile=[plan.tile_m, plan.tile_n, plan.tile_k], stages=plan.stages,
-                            submission="one CUDA graph replay per step" if use_graph else "direct launches"),
+                            tile=[plan.tile_m, plan.tile_n, plan.tile_k], stages=plan.stages),
                 roofline=roof, cpu_baseline=cpu, e2e=e2e, clocks=clocks,
                 gpu_launches=args.steps * plan.launches, parity=parity)
     print(json.dumps(line), flush=True)
