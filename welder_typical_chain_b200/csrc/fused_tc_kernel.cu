@@ -132,6 +132,8 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   // static shared memory in this kernel, so the dynamic window starts aligned; if it ever
   // does not, every thread leaves before any barrier or TMEM state exists.
   extern __shared__ __align__(1024) uint8_t smem[];
+  // the first TMA instruction waits for its descriptor: ask for all three before anything else
+  if (threadIdx.x == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); tma_prefetch_desc(&tmO); }
   if ((smem_u32(smem) & 1023u) != 0) { record_failure(p.status, WTC_DEV_BAD_SMEM_ALIGN); return; }
 
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + L::kOffBars);
@@ -168,7 +170,6 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
     for (int i = 0; i < 4; ++i) mbar_init(&stats_bar[i], 1);
     mbar_fence_init();
-    tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); tma_prefetch_desc(&tmO);
   }
   if (warp == 1) {
     if (PAIR) { tmem_alloc_pair(tmem_slot, 2 * BN); tmem_relinquish_pair(); }
