@@ -93,18 +93,31 @@ class ClockSampler(threading.Thread):
             getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
             getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4): "sw_power_cap",
         }
+        self._names = names
         while not self._stop_evt.is_set():
-            try:
-                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
-                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
-                for bit, name in names.items():
-                    if r & bit:
-                        self.reasons.add(name)
-            except Exception:
-                pass
+            self._sample()
             time.sleep(0.02)
 
+    def _sample(self):
+        try:
+            nv = self.nv
+            self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+            r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+            for bit, name in self._names.items():
+                if r & bit:
+                    self.reasons.add(name)
+        except Exception:
+            pass
+
+    def mark(self):
+        """Start of the timed region: forget what was sampled during warm-up."""
+        self.samples, self.reasons = [], set()
+
     def finish(self):
+        """Call with the timed work still in flight: takes one more sample (short regions fall
+        between two polls of the thread), then stops the thread."""
+        if self.ok and hasattr(self, "_names"):
+            self._sample()
         self._stop_evt.set()
         if self.is_alive():
             self.join(timeout=1)
@@ -278,6 +291,10 @@ def main():
         if not parity["ok"]:
             raise SystemExit(f"rank {rank}: column-sharded parity check failed: {parity}")
 
+    # the sampler thread starts before the warm-up so that its start-up (NVML first calls) is
+    # not inside the timed region; its samples are cleared when the timed region begins
+    sampler = ClockSampler(local)
+    sampler.start()
     for i in range(args.warmup):
         step(i)
     wtc.check_device_status()
@@ -285,8 +302,7 @@ def main():
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
-    sampler = ClockSampler(local)
-    sampler.start()
+    sampler.mark()
     stream = torch.cuda.current_stream()
     e0 = torch.cuda.Event(enable_timing=True)
     e1 = torch.cuda.Event(enable_timing=True)
@@ -294,11 +310,11 @@ def main():
     for i in range(args.steps):
         step(i)
     e1.record(stream)
+    clocks = sampler.finish()          # the queue is still draining: this sample is under load
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
-    clocks = sampler.finish()
     ms = e0.elapsed_time(e1)
     wtc.check_device_status()
     t = torch.tensor([ms], device=dev, dtype=torch.float64)
