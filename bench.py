@@ -327,6 +327,19 @@ def main():
     ms_per_step = ms_max / args.steps
     value = total_flops_step / (ms_per_step * 1e-3) / 1e12
 
+    # ---- isolated calls (the stream is idle before each), each between its own pair of events, this rank:
+    #      minimum and median; these include the launch latency the back-to-back loop hides
+    #      beside the mean of the back-to-back loop above (the reference harness reports a mean only)
+    single = []
+    for i in range(min(args.steps, 30)):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        step(i)
+        b.record(stream)
+        b.synchronize()
+        single.append(a.elapsed_time(b) * 1e3)
+    single.sort()
+
     # ---- end to end: host buffers in, host buffer out, through the C-ABI host entry point ----
     e2e = None
     if not args.no_e2e and not col_sharded:
@@ -393,6 +406,7 @@ def main():
 
     line = dict(metric="fused_matmul_softmax_tflops", value=value, unit="TFLOP/s", n_gpus=world, steps=args.steps,
                 warmup=args.warmup, ms_per_step=ms_per_step, us_per_call=ms_per_step * 1e3,
+                us_isolated_call_min=single[0] if single else None, us_isolated_call_median=single[len(single) // 2] if single else None,
                 higher_is_better=True, scaling=scaling, vs_baseline=None, dtype=wl["dtype"], data="synthetic",
                 config=dict(workload=f"{args.workload}: {wl['desc']}",
                             per_gpu=dict(batch=batch, M=M, N=n_local, K=K),
