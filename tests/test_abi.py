@@ -40,14 +40,15 @@ def test_struct_layout_matches_header(wtc_lib):
     ((64, 2048, 2048, 128), "tc_cluster", 8, 1, 640, 3),      # batched attention scores: many tiles per CTA, relay epilogue
     ((1, 8192, 32000, 4096), "tc_tiled", 1, 2, 320, 6),       # vocab-wide logits: online two-pass, CTA pairs
     ((1, 16, 32000, 4096), "tc_tiled", 1, 2, 320, 4),         # skinny decode
-    ((1, 8192, 128, 64), "tc_cluster", 1, 1, 320, 3),         # the reference's own shape: 64 row blocks on 148 one-CTA clusters
+    ((1, 8192, 128, 64), "tc_cluster", 1, 1, 320, 4),         # the reference's own shape: rows of 128 columns take the 128-column tile
 ])
 def test_plans_for_benchmark_configs(wtc_lib, shape, kernel, cluster, launches, threads, stages):
     p = wtc_lib.plan_query(wtc_lib.make_desc(*shape))
     assert wtc_lib.launch.KERNEL_NAMES[p.kernel] == kernel
     assert (p.cluster_n, p.launches) == (cluster, launches)
-    assert (p.tile_m, p.tile_n, p.tile_k) == (128, 256, 64)
-    assert p.tmem_columns == 512 and (p.threads, p.stages) == (threads, stages)
+    tn = 128 if shape[2] <= 128 else 256
+    assert (p.tile_m, p.tile_n, p.tile_k) == (128, tn, 64)
+    assert p.tmem_columns == 2 * tn and (p.threads, p.stages) == (threads, stages)
     if kernel == "tc_tiled":
         b, M, N, K = shape
         assert p.workspace_bytes == b * M * ((N + 255) // 256) * 8
@@ -60,7 +61,9 @@ def test_plan_fallbacks_and_variants(wtc_lib):
     assert w.plan_query(w.make_desc(1, 100, 70, 64)).kernel == w.KERNEL_SIMT_FUSED        # N % 8 != 0
     assert w.plan_query(w.make_desc(1, 100, 72, 60)).kernel == w.KERNEL_SIMT_FUSED        # K % 8 != 0
     assert w.plan_query(w.make_desc(1, 100, 72, 64, out_dtype=w.F32)).kernel == w.KERNEL_TC_CLUSTER   # f16 in, f32 out
-    assert w.plan_query(w.make_desc(1, 100, 72, 64, out_dtype=w.F32, tile_n=128)).tile_n == 256       # f32 output: 256-column tiles only
+    assert w.plan_query(w.make_desc(1, 100, 72, 64, out_dtype=w.F32, tile_n=128)).tile_n == 128       # f32 output has both column tiles too
+    assert w.plan_query(w.make_desc(1, 100, 72, 64, tile_n=256)).tile_n == 256                        # a hint wins over the narrow-row default
+    assert w.plan_query(w.make_desc(1, 100, 136, 64)).tile_n == 256
     assert w.plan_query(w.make_desc(1, 100, 72, 64, flags=w.FLAG_FORCE_SIMT)).kernel == w.KERNEL_SIMT_FUSED
     assert w.plan_query(w.make_desc(1, 100, 512, 64, flags=w.FLAG_FORCE_TILED)).kernel == w.KERNEL_TC_TILED
     p = w.plan_query(w.make_desc(2, 100, 72, 64, variant=w.VARIANT_BASELINE))

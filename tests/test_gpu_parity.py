@@ -336,6 +336,22 @@ def test_tile_choice_from_best_json_is_honoured(w, cuda_dev):
         _check(_run(w, cuda_dev, A, B, 1 / 32, tiles=(64, 128, 32)), ref)     # tileM / tileK replaced, tileN honoured
 
 
+def test_narrow_rows_take_the_128_column_tile(w, cuda_dev):
+    """Rows of at most 128 columns run the 128-column kernels by default (f16 and f32
+    probabilities, one-CTA cluster and two-pass schedule); a 256 hint still gets the wide tile."""
+    for M, N, K, scale in ((8192, 128, 64, 1.0), (300, 72, 136, 0.3), (1000, 120, 64, 0.2), (64, 8, 8, 1.0)):
+        A = oracle.normal((M, K), M + 1)
+        B = oracle.normal((K, N), N + 1)
+        ref = oracle.chain(A, B, scale)
+        for kw in (dict(), dict(out_dtype=w.F32), dict(flags=w.FLAG_FORCE_TILED), dict(flags=w.FLAG_FORCE_TILED, out_dtype=w.F32),
+                   dict(tiles=(128, 256, 64))):
+            _check(_run(w, cuda_dev, A, B, scale, **kw), ref)
+    A = oracle.normal((512, 64), 3); B = oracle.normal((64, 2304), 4)          # f32 probabilities on 128-column tiles, tiled and cluster
+    ref = oracle.chain(A, B, 0.125)
+    _check(_run(w, cuda_dev, A, B, 0.125, out_dtype=w.F32, tiles=(128, 128, 64)), ref)
+    _check(_run(w, cuda_dev, A[:, :64], B[:, :1024], 0.125, out_dtype=w.F32, tiles=(128, 128, 64)), oracle.chain(A[:, :64], B[:, :1024], 0.125))
+
+
 # ---------------------------------------------------------------- kernel variants
 
 @pytest.mark.parametrize("env", [

@@ -968,7 +968,9 @@ cudaError_t launch_fused_cluster(const CUtensorMap &tmA, const CUtensorMap &tmB,
                                  const TcParams &p, int bn, int cluster_n, int num_sms, cudaStream_t s,
                                  TcLaunchInfo *info) {
   if (cluster_n < 1 || cluster_n > kMaxCluster) return cudaErrorInvalidValue;
-  if (p.out_f32) return launch_impl<kTcBlockN, 3, true, 2, false, false, 8, true>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+  if (p.out_f32)
+    return bn == 128 ? launch_impl<128, 4, true, 2, false, false, 8, true>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info)
+                     : launch_impl<kTcBlockN, 3, true, 2, false, false, 8, true>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
   // 128-column tiles (a tile choice of best.json): the default schedule only
   if (bn == 128) return launch_impl<128, 4, true, 2, false, false, 8>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
   const bool pair = p.pair_mode == 2 && 2 * cluster_n <= kMaxCluster;
@@ -994,7 +996,9 @@ cudaError_t launch_fused_cluster(const CUtensorMap &tmA, const CUtensorMap &tmB,
 
 cudaError_t launch_tiled_partial(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO,
                                  const TcParams &p, int bn, int num_sms, cudaStream_t s, TcLaunchInfo *info) {
-  if (p.out_f32) return launch_impl<kTcBlockN, 4, false, 1, false, false, 8, true>(tmA, tmB, tmO, p, 1, num_sms, s, info);
+  if (p.out_f32)
+    return bn == 128 ? launch_impl<128, 6, false, 1, false, false, 8, true>(tmA, tmB, tmO, p, 1, num_sms, s, info)
+                     : launch_impl<kTcBlockN, 4, false, 1, false, false, 8, true>(tmA, tmB, tmO, p, 1, num_sms, s, info);
   if (bn == 128) return launch_impl<128, 6, false, 1, false, false, 8>(tmA, tmB, tmO, p, 1, num_sms, s, info);
   const bool pair = p.pair_mode == 2 || (p.pair_mode == 0 && p.num_rb >= 2 && p.num_kb >= 8);
   const bool tma = p.store_mode == 1;

@@ -117,8 +117,10 @@ int resolve(const wtc_chain_desc *in, Resolved &r) {
   memset(&p, 0, sizeof(p));
   p.cluster_n = 1;
   r.num_rb = static_cast<int>((d.M + wtc::kTcBlockM - 1) / wtc::kTcBlockM);
-  // tileN = 128 is the second legal column tile; everything else resolves to 256
-  r.bn = (d.tile_n == 128 && d.out_dtype == WTC_F16) ? 128 : wtc::kTcBlockN;
+  // tileN = 128 is the second legal column tile; everything else resolves to 256.  Without a
+  // tile hint, rows of at most 128 columns take the 128-column kernels (half of a 256-column
+  // tile would be padding: 6.4 vs 8.3 us on 8192x128x64).
+  r.bn = (d.tile_n == 128 || (d.tile_n == 0 && d.N <= 128)) ? 128 : wtc::kTcBlockN;
   r.num_nb = static_cast<int>((d.N + r.bn - 1) / r.bn);
   r.num_kb = static_cast<int>((d.K + wtc::kTcBlockK - 1) / wtc::kTcBlockK);
 
@@ -324,7 +326,6 @@ int launch_resolved(Resolved &r, const void *A, const void *B, void *Out, void *
     p.timeline = g_timeline;
     p.use_pdl = g_use_pdl;
     p.out_f32 = out32;
-    if (out32) r.bn = wtc::kTcBlockN;   // (resolve() already forces 256 for f32 output)
     p.out = Out; p.ldo = d.ldo; p.o_batch_stride = d.o_batch_stride;
     p.out_align32 = ((reinterpret_cast<uintptr_t>(Out) & 31) == 0) && ((d.ldo & 15) == 0) && ((d.o_batch_stride & 15) == 0);
     if (const char *e = getenv("WTC_TL_MODE")) p.timeline_mode = atoi(e);
