@@ -63,7 +63,12 @@ def test_plan_fallbacks_and_variants(wtc_lib):
     assert w.plan_query(w.make_desc(1, 100, 72, 64, out_dtype=w.F32)).kernel == w.KERNEL_TC_CLUSTER   # f16 in, f32 out
     assert w.plan_query(w.make_desc(1, 100, 72, 64, out_dtype=w.F32, tile_n=128)).tile_n == 128       # f32 output has both column tiles too
     assert w.plan_query(w.make_desc(1, 100, 72, 64, tile_n=256)).tile_n == 256                        # a hint wins over the narrow-row default
-    assert w.plan_query(w.make_desc(1, 100, 136, 64)).tile_n == 256
+    # without a hint: 128-column tiles when 256-column ones would leave most SMs idle and the narrower clusters all fit at once
+    assert w.plan_query(w.make_desc(1, 100, 136, 64)).tile_n == 128
+    assert w.plan_query(w.make_desc(1, 4096, 512, 1024)).tile_n == 128 and w.plan_query(w.make_desc(1, 4096, 512, 1024)).cluster_n == 4
+    assert w.plan_query(w.make_desc(1, 2048, 1024, 1024)).tile_n == 256        # sixteen 8-CTA clusters would need two rounds
+    assert w.plan_query(w.make_desc(1, 8192, 512, 128)).tile_n == 256          # 256-column tiles already fill the chip
+    assert w.plan_query(w.make_desc(1, 256, 1024, 1024, flags=w.FLAG_FORCE_TILED)).tile_n == 256
     assert w.plan_query(w.make_desc(1, 100, 72, 64, flags=w.FLAG_FORCE_SIMT)).kernel == w.KERNEL_SIMT_FUSED
     assert w.plan_query(w.make_desc(1, 100, 512, 64, flags=w.FLAG_FORCE_TILED)).kernel == w.KERNEL_TC_TILED
     p = w.plan_query(w.make_desc(2, 100, 72, 64, variant=w.VARIANT_BASELINE))

@@ -118,9 +118,21 @@ int resolve(const wtc_chain_desc *in, Resolved &r) {
   p.cluster_n = 1;
   r.num_rb = static_cast<int>((d.M + wtc::kTcBlockM - 1) / wtc::kTcBlockM);
   // tileN = 128 is the second legal column tile; everything else resolves to 256.  Without a
-  // tile hint, rows of at most 128 columns take the 128-column kernels (half of a 256-column
-  // tile would be padding: 6.4 vs 8.3 us on 8192x128x64).
-  r.bn = (d.tile_n == 128 || (d.tile_n == 0 && d.N <= 128)) ? 128 : wtc::kTcBlockN;
+  // tile hint the 128-column kernels are taken (a) for rows of at most 128 columns (half of a
+  // 256-column tile would be padding: 6.4 vs 8.3 us on 8192x128x64) and (b) when 256-column
+  // tiles would leave more than half of the SMs without a CTA while the 128-column clusters
+  // still all fit the chip at once (measured: 4096x512x1024 12.6 vs 14.5 us, 1024x1024x512
+  // 9.2 vs 11.1 us; but 2048x1024x1024 18.6 vs 14.5 us, where sixteen 8-CTA clusters need two rounds).
+  r.bn = wtc::kTcBlockN;
+  if (d.tile_n == 128) r.bn = 128;
+  else if (d.tile_n == 0) {
+    // clusters of n CTAs that are resident at once on a 148-SM part (8: measured 15; others: one short of 148 / n)
+    static const int kResident[9] = {0, 148, 72, 47, 35, 27, 22, 18, 15};
+    const int64_t units = static_cast<int64_t>(d.batch) * r.num_rb;
+    const int64_t nb128 = (d.N + 127) / 128, nb256 = (d.N + 255) / 256;
+    if (d.N <= 128) r.bn = 128;
+    else if (!(d.flags & WTC_FLAG_FORCE_TILED) && nb128 <= 8 && units * nb256 <= 74 && units <= kResident[nb128]) r.bn = 128;
+  }
   r.num_nb = static_cast<int>((d.N + r.bn - 1) / r.bn);
   r.num_kb = static_cast<int>((d.K + wtc::kTcBlockK - 1) / wtc::kTcBlockK);
 

@@ -71,7 +71,6 @@ std::vector<Candidate> enumerateCandidates(const ir::ChainSpec &spec, const Arch
   const bool f16 = spec.inType == "f16";
   const double eb = f16 ? 2.0 : 4.0;
   const double ob = spec.outType == "f16" ? 2.0 : 4.0;
-  const double flops = 2.0 * spec.batch * spec.M * spec.N * spec.K;
   const bool fused = maxConnectLevel > 0;
   for (int64_t tm : {64, 128}) {
     for (int64_t tn : {64, 128, 256}) {
@@ -104,21 +103,30 @@ std::vector<Candidate> enumerateCandidates(const ir::ChainSpec &spec, const Arch
         c.bytesA = bytesA; c.bytesB = bytesB; c.bytesC = bytesC; c.bytesCut = bytesCut;
         c.score = (bytesA + bytesB + bytesC + bytesCut) * waves;
         // latency model: the slowest of tensor time (M=64 MMAs run at half rate), L2 operand feed,
-        // HBM compulsory traffic and the MUFU-bound softmax epilogue (16 ex2/clk/SM), plus a fill term
-        const double tensorUs = flops / (arch.tensorTflops * 1e6) * (tm == 64 ? 2.0 : 1.0) * (tn < 256 ? 1.15 : 1.0);
+        // HBM compulsory traffic and the MUFU-bound softmax epilogue (16 ex2/clk/SM), plus a fill term.
+        // Tensor time counts rounds: a cluster of n CTAs is resident only kResident[n] times on the part.
+        static const int kResident[9] = {0, 148, 72, 47, 35, 27, 22, 18, 15};
+        const double parallel = twoPass ? std::min<double>(ctas, static_cast<double>(arch.numSM))
+                                        : std::min<double>(ctas, static_cast<double>(kResident[clusterN]) * static_cast<double>(clusterN));
+        const double rounds = std::ceil(ctas / std::max(1.0, parallel));
+        const double perTileUs = 2.0 * tm * tn * static_cast<double>(spec.K) / (arch.tensorTflops / static_cast<double>(arch.numSM) * 1e6) *
+                                 (tm == 64 ? 2.0 : 1.0) * (tn < 256 ? 1.15 : 1.0);
+        const double tensorUs = perTileUs * rounds;
         const double l2Us = (bytesA + bytesB) / (arch.l2TBps * 1e6);
         const double compulsory = eb * (spec.batch * static_cast<double>(spec.M) * spec.K +
                                         (spec.bBatched ? spec.batch : 1) * static_cast<double>(spec.K) * spec.N);
         const double hbmUs = (compulsory + bytesC + bytesCut) / (arch.hbmTBps * 1e6);
-        const double mufuUs = spec.batch * static_cast<double>(spec.M) * spec.N / (16.0 * arch.numSM * 1.9e3);
-        const double occupancy = std::min(1.0, ctas / static_cast<double>(arch.numSM));
-        c.estimatedLatencyUs = std::max({tensorUs / occupancy, l2Us, hbmUs, mufuUs / occupancy}) + 2.0;
+        const double mufuUs = static_cast<double>(tm) * tn / (16.0 * 1.9e3) * rounds;
+        c.estimatedLatencyUs = std::max({tensorUs, l2Us, hbmUs, mufuUs}) + 2.0;
         out.push_back(c);
       }
     }
   }
   std::stable_sort(out.begin(), out.end(), [](const Candidate &x, const Candidate &y) {
     if (x.implemented != y.implemented) return x.implemented;
+    // among tiles that have kernels the latency model decides (it knows about idle SMs and
+    // cluster residency); the rest keep the reference's traffic x waves order
+    if (x.implemented && x.estimatedLatencyUs != y.estimatedLatencyUs) return x.estimatedLatencyUs < y.estimatedLatencyUs;
     if (x.score != y.score) return x.score < y.score;
     return x.estimatedLatencyUs < y.estimatedLatencyUs;
   });
