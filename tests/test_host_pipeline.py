@@ -110,6 +110,38 @@ def test_f32_arguments_rounded_to_f16_are_recognised(tmp_path):
     assert r.returncode == 1 and "rounded to f16 by arith.truncf" in open(tmp_path / "b" / "ir" / "01.canonicalize.log").read()
 
 
+def test_type_and_map_aliases_are_expanded(tmp_path):
+    """MLIR printers name types and affine maps at the top of a module; the recogniser expands the
+    names, and the canonical form it writes spells everything out."""
+    out = tmp_path / "o"
+    r = run(["--input", os.path.join(MLIR, "matmul_softmax_chain_named_softmax.mlir"), "--out-dir", str(out), "--search-only", "--backend-mode", "api"])
+    assert r.returncode == 0, r.stderr
+    canon = open(out / "ir" / "01.canonicalized.mlir").read()
+    assert "!t0" not in canon and "#m0" not in canon and "tensor<8192x128xf32>" in canon and "affine_map<(d0, d1) -> (d0)>" in canon
+    spelled = tmp_path / "spelled.mlir"
+    spelled.write_text(canon)                                               # alias-free text parses to the same chain
+    r = run(["--input", str(spelled), "--out-dir", str(tmp_path / "o2"), "--search-only", "--backend-mode", "api"])
+    a, b = json.load(open(tmp_path / "o2" / "ir" / "chain.json")), json.load(open(out / "ir" / "chain.json"))
+    assert r.returncode == 0 and a.pop("softmax_form") == "decomposed" and b.pop("softmax_form") == "named" and a == b
+    nested = tmp_path / "nested.mlir"                                       # an alias may use an earlier alias; !t1 must not eat !t10
+    nested.write_text("!e = f32\n!t1 = tensor<8x16x!e>\n!t10 = tensor<16x24x!e>\n!t2 = tensor<8x24x!e>\n" + """module {
+  func.func @main(%A: !t1, %B: !t10) -> !t2 {
+    %z = arith.constant 0.0 : f32
+    %e = tensor.empty() : !t2
+    %f = linalg.fill ins(%z : f32) outs(%e : !t2) -> !t2
+    %C = linalg.matmul ins(%A, %B : !t1, !t10) outs(%f : !t2) -> !t2
+    %s = tensor.empty() : !t2
+    %P = linalg.softmax dimension(1) ins(%C : !t2) outs(%s : !t2) -> !t2
+    return %P : !t2
+  }
+}
+""")
+    r = run(["--input", str(nested), "--out-dir", str(tmp_path / "o3"), "--search-only", "--backend-mode", "api"])
+    assert r.returncode == 0, r.stderr
+    c = json.load(open(tmp_path / "o3" / "ir" / "chain.json"))
+    assert (c["M"], c["N"], c["K"], c["softmax_form"]) == (8, 24, 16, "named")
+
+
 def test_tile_source_priority_and_overrides(tmp_path):
     inp = os.path.join(MLIR, "cfg2_f16_native_4096x1024x1024.mlir")
     bj = tmp_path / "best.json"
@@ -152,7 +184,9 @@ def test_usage_and_stage_errors(tmp_path):
     bad.write_text("module { func.func @main(%A: tensor<4x4xf32>, %B: tensor<4x4xf32>) -> tensor<4x4xf32> { return %A : tensor<4x4xf32> } }")
     r = run(["--input", str(bad), "--out-dir", str(tmp_path / "o")])
     assert r.returncode == 1 and "matmul" in r.stderr
-    mism = open(os.path.join(MLIR, "cfg1_decomposed_f32_128.mlir")).read().replace("%B: tensor<128x128xf32>", "%B: tensor<64x128xf32>")
+    src = open(os.path.join(MLIR, "cfg1_decomposed_f32_128.mlir")).read()
+    assert "%B: !t0" in src and "!t0 = tensor<128x128xf32>" in src          # the shipped inputs name their types once (aliases)
+    mism = src.replace("%B: !t0", "%B: tensor<64x128xf32>")
     (tmp_path / "mism.mlir").write_text(mism)
     r = run(["--input", str(tmp_path / "mism.mlir"), "--out-dir", str(tmp_path / "o")])
     assert r.returncode == 1

@@ -12,6 +12,7 @@
 // the four generics itself.
 #include "wtc_host.h"
 
+#include <cctype>
 #include <cstdio>
 #include <cstdlib>
 #include <filesystem>
@@ -64,6 +65,48 @@ std::string stripComments(const std::string &text) {
     out << (p == std::string::npos ? line : line.substr(0, p)) << '\n';
   }
   return out.str();
+}
+
+// Attribute and type aliases (`#map = affine_map<...>`, `!row_t = tensor<...>`), which MLIR
+// printers emit at the top of a module, are expanded in place so that the rest of the
+// recogniser only ever sees spelled-out types.  Definitions may use earlier aliases.
+std::string expandAliases(const std::string &text) {
+  static const std::regex defRe(R"(^[ \t]*([#!][A-Za-z_][\w.$-]*)[ \t]*=[ \t]*(.*\S)[ \t]*$)");
+  std::vector<std::pair<std::string, std::string>> defs;
+  std::ostringstream body;
+  std::istringstream in(text);
+  std::string line;
+  bool top = true;
+  while (std::getline(in, line)) {
+    if (top) {
+      const size_t c = line.find("//");
+      const std::string code = c == std::string::npos ? line : line.substr(0, c);
+      std::smatch m;
+      if (std::regex_match(code, m, defRe)) { defs.emplace_back(m[1].str(), m[2].str()); continue; }
+      if (code.find("module") != std::string::npos || code.find("func.func") != std::string::npos) top = false;
+    }
+    body << line << '\n';
+  }
+  if (defs.empty()) return text;
+  auto substitute = [&](std::string s) {
+    for (int pass = 0; pass < 4; ++pass) {
+      bool changed = false;
+      for (const auto &d : defs) {
+        size_t pos = 0;
+        while ((pos = s.find(d.first, pos)) != std::string::npos) {
+          const size_t end = pos + d.first.size();
+          const bool boundary = end >= s.size() || !(std::isalnum(static_cast<unsigned char>(s[end])) || s[end] == '_' || s[end] == '.' || s[end] == '$' || s[end] == '-');
+          if (!boundary) { pos = end; continue; }
+          s.replace(pos, d.first.size(), d.second);
+          pos += d.second.size();
+          changed = true;
+        }
+      }
+      if (!changed) break;
+    }
+    return s;
+  };
+  return substitute(body.str());
 }
 
 bool parseTensorType(const std::string &s, TensorType &t) {
@@ -177,7 +220,7 @@ std::string decomposedSoftmax(const std::string &input, const std::string &resul
 } // namespace
 
 bool parseChain(const std::string &rawText, ChainSpec &spec, std::string &diag) {
-  const std::string text = stripComments(rawText);
+  const std::string text = expandAliases(stripComments(rawText));
   spec = ChainSpec();
 
   // ---- function signature
@@ -310,7 +353,7 @@ bool canonicalizeMatmulSoftmaxChain(const std::string &inputPath, const std::str
     return failWith("chain recogniser rejected the input: " + perr + ", see " + logPath);
   }
 
-  std::string text = input;
+  std::string text = expandAliases(input);   // the canonical form spells every type and map out
   if (spec.namedSoftmax) {
     // locate the statement  <result> = linalg.softmax dimension(d) ins(<x> : T) outs(... ) -> T
     static const std::regex stRe(R"((%[\w.]+)\s*=\s*linalg\.softmax\s+dimension\(\s*[0-9]+\s*\)\s*ins\(\s*(%[\w.]+)\s*:\s*(tensor<[^>]+>)\s*\))");

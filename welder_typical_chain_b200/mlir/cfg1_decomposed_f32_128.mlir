@@ -1,47 +1,51 @@
 // configuration 1: decomposed f32 chain, 128 cubed
+#m0 = affine_map<(d0, d1) -> (d0, d1)>
+#m1 = affine_map<(d0, d1) -> (d0)>
+!t0 = tensor<128x128xf32>
+!t1 = tensor<128xf32>
 module {
-  func.func @main(%A: tensor<128x128xf32>, %B: tensor<128x128xf32>) -> tensor<128x128xf32> {
+  func.func @main(%A: !t0, %B: !t0) -> !t0 {
     %zero_acc = arith.constant 0.0 : f32
-    %c_empty = tensor.empty() : tensor<128x128xf32>
-    %c_init = linalg.fill ins(%zero_acc : f32) outs(%c_empty : tensor<128x128xf32>) -> tensor<128x128xf32>
-    %C = linalg.matmul ins(%A, %B : tensor<128x128xf32>, tensor<128x128xf32>) outs(%c_init : tensor<128x128xf32>) -> tensor<128x128xf32>
+    %c_empty = tensor.empty() : !t0
+    %c_init = linalg.fill ins(%zero_acc : f32) outs(%c_empty : !t0) -> !t0
+    %C = linalg.matmul ins(%A, %B : !t0, !t0) outs(%c_init : !t0) -> !t0
     %neg_inf = arith.constant -3.4028235e+38 : f32
     %zero = arith.constant 0.0 : f32
     // row maximum
-    %max_empty = tensor.empty() : tensor<128xf32>
-    %max_init = linalg.fill ins(%neg_inf : f32) outs(%max_empty : tensor<128xf32>) -> tensor<128xf32>
-    %max = linalg.generic {indexing_maps = [affine_map<(d0, d1) -> (d0, d1)>, affine_map<(d0, d1) -> (d0)>], iterator_types = ["parallel", "reduction"]}
-        ins(%C : tensor<128x128xf32>) outs(%max_init : tensor<128xf32>) {
+    %max_empty = tensor.empty() : !t1
+    %max_init = linalg.fill ins(%neg_inf : f32) outs(%max_empty : !t1) -> !t1
+    %max = linalg.generic {indexing_maps = [#m0, #m1], iterator_types = ["parallel", "reduction"]}
+        ins(%C : !t0) outs(%max_init : !t1) {
       ^bb0(%in: f32, %acc: f32):
         %m = arith.maximumf %in, %acc : f32
         linalg.yield %m : f32
-      } -> tensor<128xf32>
+      } -> !t1
     // exp(x - max)
-    %exp_empty = tensor.empty() : tensor<128x128xf32>
-    %exp = linalg.generic {indexing_maps = [affine_map<(d0, d1) -> (d0, d1)>, affine_map<(d0, d1) -> (d0)>, affine_map<(d0, d1) -> (d0, d1)>], iterator_types = ["parallel", "parallel"]}
-        ins(%C, %max : tensor<128x128xf32>, tensor<128xf32>) outs(%exp_empty : tensor<128x128xf32>) {
+    %exp_empty = tensor.empty() : !t0
+    %exp = linalg.generic {indexing_maps = [#m0, #m1, #m0], iterator_types = ["parallel", "parallel"]}
+        ins(%C, %max : !t0, !t1) outs(%exp_empty : !t0) {
       ^bb0(%x: f32, %m: f32, %o: f32):
         %d = arith.subf %x, %m : f32
         %e = math.exp %d : f32
         linalg.yield %e : f32
-      } -> tensor<128x128xf32>
+      } -> !t0
     // row sum
-    %sum_empty = tensor.empty() : tensor<128xf32>
-    %sum_init = linalg.fill ins(%zero : f32) outs(%sum_empty : tensor<128xf32>) -> tensor<128xf32>
-    %sum = linalg.generic {indexing_maps = [affine_map<(d0, d1) -> (d0, d1)>, affine_map<(d0, d1) -> (d0)>], iterator_types = ["parallel", "reduction"]}
-        ins(%exp : tensor<128x128xf32>) outs(%sum_init : tensor<128xf32>) {
+    %sum_empty = tensor.empty() : !t1
+    %sum_init = linalg.fill ins(%zero : f32) outs(%sum_empty : !t1) -> !t1
+    %sum = linalg.generic {indexing_maps = [#m0, #m1], iterator_types = ["parallel", "reduction"]}
+        ins(%exp : !t0) outs(%sum_init : !t1) {
       ^bb0(%in: f32, %acc: f32):
         %s = arith.addf %in, %acc : f32
         linalg.yield %s : f32
-      } -> tensor<128xf32>
+      } -> !t1
     // normalise
-    %div_empty = tensor.empty() : tensor<128x128xf32>
-    %P = linalg.generic {indexing_maps = [affine_map<(d0, d1) -> (d0, d1)>, affine_map<(d0, d1) -> (d0)>, affine_map<(d0, d1) -> (d0, d1)>], iterator_types = ["parallel", "parallel"]}
-        ins(%exp, %sum : tensor<128x128xf32>, tensor<128xf32>) outs(%div_empty : tensor<128x128xf32>) {
+    %div_empty = tensor.empty() : !t0
+    %P = linalg.generic {indexing_maps = [#m0, #m1, #m0], iterator_types = ["parallel", "parallel"]}
+        ins(%exp, %sum : !t0, !t1) outs(%div_empty : !t0) {
       ^bb0(%e: f32, %s: f32, %o: f32):
         %q = arith.divf %e, %s : f32
         linalg.yield %q : f32
-      } -> tensor<128x128xf32>
-    return %P : tensor<128x128xf32>
+      } -> !t0
+    return %P : !t0
   }
 }

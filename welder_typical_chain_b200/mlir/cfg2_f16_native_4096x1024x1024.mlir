@@ -1,64 +1,70 @@
 // configuration 2: f16 operands, f32 accumulate, scale 1/32, f16 probabilities
+#m0 = affine_map<(d0, d1) -> (d0, d1)>
+#m1 = affine_map<(d0, d1) -> (d0)>
+!t0 = tensor<4096x1024xf16>
+!t1 = tensor<1024x1024xf16>
+!t2 = tensor<4096x1024xf32>
+!t3 = tensor<4096xf32>
 module {
-  func.func @main(%A: tensor<4096x1024xf16>, %B: tensor<1024x1024xf16>) -> tensor<4096x1024xf16> {
+  func.func @main(%A: !t0, %B: !t1) -> !t0 {
     %zero_acc = arith.constant 0.0 : f32
-    %c_empty = tensor.empty() : tensor<4096x1024xf32>
-    %c_init = linalg.fill ins(%zero_acc : f32) outs(%c_empty : tensor<4096x1024xf32>) -> tensor<4096x1024xf32>
-    %C = linalg.matmul ins(%A, %B : tensor<4096x1024xf16>, tensor<1024x1024xf16>) outs(%c_init : tensor<4096x1024xf32>) -> tensor<4096x1024xf32>
+    %c_empty = tensor.empty() : !t2
+    %c_init = linalg.fill ins(%zero_acc : f32) outs(%c_empty : !t2) -> !t2
+    %C = linalg.matmul ins(%A, %B : !t0, !t1) outs(%c_init : !t2) -> !t2
     %scale = arith.constant 0.03125 : f32
     // scaled logits
-    %V_empty = tensor.empty() : tensor<4096x1024xf32>
-    %V = linalg.generic {indexing_maps = [affine_map<(d0, d1) -> (d0, d1)>, affine_map<(d0, d1) -> (d0, d1)>], iterator_types = ["parallel", "parallel"]}
-        ins(%C : tensor<4096x1024xf32>) outs(%V_empty : tensor<4096x1024xf32>) {
+    %V_empty = tensor.empty() : !t2
+    %V = linalg.generic {indexing_maps = [#m0, #m0], iterator_types = ["parallel", "parallel"]}
+        ins(%C : !t2) outs(%V_empty : !t2) {
       ^bb0(%x: f32, %o: f32):
         %y = arith.mulf %x, %scale : f32
         linalg.yield %y : f32
-      } -> tensor<4096x1024xf32>
+      } -> !t2
     %neg_inf = arith.constant -3.4028235e+38 : f32
     %zero = arith.constant 0.0 : f32
     // row maximum
-    %max_empty = tensor.empty() : tensor<4096xf32>
-    %max_init = linalg.fill ins(%neg_inf : f32) outs(%max_empty : tensor<4096xf32>) -> tensor<4096xf32>
-    %max = linalg.generic {indexing_maps = [affine_map<(d0, d1) -> (d0, d1)>, affine_map<(d0, d1) -> (d0)>], iterator_types = ["parallel", "reduction"]}
-        ins(%V : tensor<4096x1024xf32>) outs(%max_init : tensor<4096xf32>) {
+    %max_empty = tensor.empty() : !t3
+    %max_init = linalg.fill ins(%neg_inf : f32) outs(%max_empty : !t3) -> !t3
+    %max = linalg.generic {indexing_maps = [#m0, #m1], iterator_types = ["parallel", "reduction"]}
+        ins(%V : !t2) outs(%max_init : !t3) {
       ^bb0(%in: f32, %acc: f32):
         %m = arith.maximumf %in, %acc : f32
         linalg.yield %m : f32
-      } -> tensor<4096xf32>
+      } -> !t3
     // exp(x - max)
-    %exp_empty = tensor.empty() : tensor<4096x1024xf32>
-    %exp = linalg.generic {indexing_maps = [affine_map<(d0, d1) -> (d0, d1)>, affine_map<(d0, d1) -> (d0)>, affine_map<(d0, d1) -> (d0, d1)>], iterator_types = ["parallel", "parallel"]}
-        ins(%V, %max : tensor<4096x1024xf32>, tensor<4096xf32>) outs(%exp_empty : tensor<4096x1024xf32>) {
+    %exp_empty = tensor.empty() : !t2
+    %exp = linalg.generic {indexing_maps = [#m0, #m1, #m0], iterator_types = ["parallel", "parallel"]}
+        ins(%V, %max : !t2, !t3) outs(%exp_empty : !t2) {
       ^bb0(%x: f32, %m: f32, %o: f32):
         %d = arith.subf %x, %m : f32
         %e = math.exp %d : f32
         linalg.yield %e : f32
-      } -> tensor<4096x1024xf32>
+      } -> !t2
     // row sum
-    %sum_empty = tensor.empty() : tensor<4096xf32>
-    %sum_init = linalg.fill ins(%zero : f32) outs(%sum_empty : tensor<4096xf32>) -> tensor<4096xf32>
-    %sum = linalg.generic {indexing_maps = [affine_map<(d0, d1) -> (d0, d1)>, affine_map<(d0, d1) -> (d0)>], iterator_types = ["parallel", "reduction"]}
-        ins(%exp : tensor<4096x1024xf32>) outs(%sum_init : tensor<4096xf32>) {
+    %sum_empty = tensor.empty() : !t3
+    %sum_init = linalg.fill ins(%zero : f32) outs(%sum_empty : !t3) -> !t3
+    %sum = linalg.generic {indexing_maps = [#m0, #m1], iterator_types = ["parallel", "reduction"]}
+        ins(%exp : !t2) outs(%sum_init : !t3) {
       ^bb0(%in: f32, %acc: f32):
         %s = arith.addf %in, %acc : f32
         linalg.yield %s : f32
-      } -> tensor<4096xf32>
+      } -> !t3
     // normalise
-    %div_empty = tensor.empty() : tensor<4096x1024xf32>
-    %P = linalg.generic {indexing_maps = [affine_map<(d0, d1) -> (d0, d1)>, affine_map<(d0, d1) -> (d0)>, affine_map<(d0, d1) -> (d0, d1)>], iterator_types = ["parallel", "parallel"]}
-        ins(%exp, %sum : tensor<4096x1024xf32>, tensor<4096xf32>) outs(%div_empty : tensor<4096x1024xf32>) {
+    %div_empty = tensor.empty() : !t2
+    %P = linalg.generic {indexing_maps = [#m0, #m1, #m0], iterator_types = ["parallel", "parallel"]}
+        ins(%exp, %sum : !t2, !t3) outs(%div_empty : !t2) {
       ^bb0(%e: f32, %s: f32, %o: f32):
         %q = arith.divf %e, %s : f32
         linalg.yield %q : f32
-      } -> tensor<4096x1024xf32>
+      } -> !t2
     // probabilities in the output type
-    %P16_empty = tensor.empty() : tensor<4096x1024xf16>
-    %P16 = linalg.generic {indexing_maps = [affine_map<(d0, d1) -> (d0, d1)>, affine_map<(d0, d1) -> (d0, d1)>], iterator_types = ["parallel", "parallel"]}
-        ins(%P : tensor<4096x1024xf32>) outs(%P16_empty : tensor<4096x1024xf16>) {
+    %P16_empty = tensor.empty() : !t0
+    %P16 = linalg.generic {indexing_maps = [#m0, #m0], iterator_types = ["parallel", "parallel"]}
+        ins(%P : !t2) outs(%P16_empty : !t0) {
       ^bb0(%x: f32, %o: f16):
         %y = arith.truncf %x : f32 to f16
         linalg.yield %y : f16
-      } -> tensor<4096x1024xf16>
-    return %P16 : tensor<4096x1024xf16>
+      } -> !t0
+    return %P16 : !t0
   }
 }

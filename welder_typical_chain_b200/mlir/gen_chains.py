@@ -100,7 +100,24 @@ def chain(batch, M, N, K, in_t="f32", acc_t="f32", out_t="f32", scale=1.0, named
                     [c32], res_t, [cur], "probabilities in the output type")
         cur = "%P16"
     L += [f"    return {cur} : {res_t}", "  }", "}", ""]
-    return "\n".join(L)
+    return with_aliases("\n".join(L))
+
+
+def with_aliases(text):
+    """Names every distinct tensor type and affine map once at the top of the module (`!t0 = ...`,
+    `#m0 = ...`), the way MLIR printers do, and uses the names in the body."""
+    import re
+    title, body = text.split("\n", 1)
+    defs = []
+    for pattern, sigil in ((r"affine_map<\([^)]*\) -> \([^)]*\)>", "#m"), (r"tensor<[0-9x]+f(?:16|32)>", "!t")):
+        seen = []
+        for m in re.finditer(pattern, body):
+            if m.group(0) not in seen:
+                seen.append(m.group(0))
+        for i, full in enumerate(seen):
+            defs.append(f"{sigil}{i} = {full}")
+            body = body.replace(full, f"{sigil}{i}")
+    return "\n".join([title] + defs + [body])
 
 
 FILES = {
