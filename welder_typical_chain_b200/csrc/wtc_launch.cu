@@ -264,6 +264,16 @@ int *default_status() {
   return words[dev];
 }
 
+// what a non-zero device status word means
+int status_result(int v) {
+  if (v == 0) return WTC_OK;
+  static const char *names[] = {"ok", "a TMA stage never landed", "a pipeline stage was never released",
+                                "an accumulator never completed", "an accumulator buffer was never drained",
+                                "cluster peers never sent their row statistics",
+                                "dynamic shared memory was not 1024-byte aligned"};
+  return fail(WTC_E_DEVICE, "device status %d: %s", v, (v > 0 && v < 7) ? names[v] : "unknown");
+}
+
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 wtc::SimtParams simt_params(const Resolved &r) {
@@ -450,14 +460,7 @@ int wtc_check_device_status(const int *device_status, void *stream) {
   int v = 0;
   e = cudaMemcpy(&v, src, sizeof(int), cudaMemcpyDeviceToHost);
   if (e != cudaSuccess) return cuda_fail(e, "reading the device status word");
-  if (v != 0) {
-    static const char *names[] = {"ok", "a TMA stage never landed", "a pipeline stage was never released",
-                                  "an accumulator never completed", "an accumulator buffer was never drained",
-                                  "cluster peers never sent their row statistics",
-                                  "dynamic shared memory was not 1024-byte aligned"};
-    return fail(WTC_E_DEVICE, "device status %d: %s", v, (v > 0 && v < 7) ? names[v] : "unknown");
-  }
-  return WTC_OK;
+  return status_result(v);
 }
 
 int wtc_matmul_softmax_time(const wtc_chain_desc *desc, const void *A, const void *B, void *Out, void *workspace,
@@ -595,7 +598,20 @@ int wtc_matmul_softmax_host(const wtc_chain_desc *desc, const void *hostA, const
   // the next call's first copy must not overtake this call's last kernel or read-back
   e = cudaStreamWaitEvent(ln.in, ln.done[n - 1], 0);
   if (e != cudaSuccess) return cuda_fail(e, "cudaStreamWaitEvent");
-  return wtc_check_device_status(nullptr, ln.out);
+  // the device status word rides back on the copy-out stream into pinned memory: one wait
+  // covers the results and the status (no separate blocking read)
+  thread_local int *host_status = nullptr;
+  if (!host_status) {
+    e = cudaHostAlloc(reinterpret_cast<void **>(&host_status), sizeof(int), cudaHostAllocDefault);
+    if (e != cudaSuccess) { host_status = nullptr; return cuda_fail(e, "cudaHostAlloc (status word)"); }
+  }
+  const int *dev_status = default_status();
+  if (!dev_status) return fail(WTC_E_CUDA, "no status word");
+  *host_status = 0;
+  e = cudaMemcpyAsync(host_status, dev_status, sizeof(int), cudaMemcpyDeviceToHost, ln.out);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(ln.out);
+  if (e != cudaSuccess) return cuda_fail(e, "waiting for the results");
+  return status_result(*host_status);
 }
 
 int wtc_debug_set_umma_geometry(uint32_t a_lbo, uint32_t a_sbo, uint32_t a_kstep, uint32_t b_lbo, uint32_t b_sbo,
