@@ -376,3 +376,11 @@ def test_every_kernel_variant_matches_the_checker(w, cuda_dev, monkeypatch, env)
         A = oracle.normal((M, K), M)
         B = oracle.normal((K, N), N)
         _check(_run(w, cuda_dev, A, B, scale, flags=flags), oracle.chain(A, B, scale))
+    # a negative scale turns the row maximum into a minimum of the raw accumulators; logits
+    # rounded to f16 (the f16 matmul result) take the epilogue's general path; batched with B per batch
+    A = oracle.normal((1500, 64), 7); B = oracle.normal((64, 1024), 8)
+    _check(_run(w, cuda_dev, A, B, -0.11), oracle.chain(A, B, -0.11))
+    A = oracle.normal((3, 520, 72), 9) * np.float16(0.25); B = oracle.normal((3, 72, 768), 10) * np.float16(0.25)
+    got = _run(w, cuda_dev, A, B, 1.0, acc_dtype=w.F16)
+    ref = np.stack([oracle.chain(A[i], B[i], 1.0, acc=oracle.ACC_F16_SEQ) for i in range(3)])
+    assert np.abs(got.astype(np.float64) - ref).max() < 5e-3
