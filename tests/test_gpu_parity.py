@@ -352,6 +352,15 @@ def test_narrow_rows_take_the_128_column_tile(w, cuda_dev):
     _check(_run(w, cuda_dev, A[:, :64], B[:, :1024], 0.125, out_dtype=w.F32, tiles=(128, 128, 64)), oracle.chain(A[:, :64], B[:, :1024], 0.125))
 
 
+def test_few_rows_wide_row_rescale_is_split_over_ctas(w, cuda_dev):
+    """With few rows and a wide row the rescale pass runs several CTAs per row, each on a column
+    range; same numbers as the one-CTA-per-row form (checked against the checker)."""
+    for M, N, K, kw in ((16, 32000, 64, {}), (5, 10008, 72, {}), (40, 4104, 64, dict(out_dtype=w.F32)), (1, 8200, 128, {})):
+        A = oracle.normal((M, K), M + 3)
+        B = oracle.normal((K, N), N + 3) * np.float16(0.5)
+        _check(_run(w, cuda_dev, A, B, 0.25, **kw), oracle.chain(A, B, 0.25))
+
+
 # ---------------------------------------------------------------- kernel variants
 
 @pytest.mark.parametrize("env", [

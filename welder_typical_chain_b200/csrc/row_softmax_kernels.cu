@@ -36,11 +36,12 @@ __global__ void row_stats_kernel(const float2 *__restrict__ tile_stats, float2 *
   if (lane == 0) row_stats[row] = v;
 }
 
-// one CTA per row
+// One CTA per row, or -- when there are few rows -- gridDim.y CTAs per row, each taking `chunk`
+// columns (a multiple of 256) after working out the row's total for itself.
 __global__ void __launch_bounds__(256)
 rescale_rows_kernel(void *__restrict__ out_v, int out_f32, int N, int64_t ld_out, int BN, int num_nb,
                     const float2 *__restrict__ tile_stats, const float2 *__restrict__ global_stats,
-                    int num_parts, int64_t rows) {
+                    int num_parts, int64_t rows, int chunk) {
   extern __shared__ float factor[];          // [num_nb]
   __shared__ float2 warp_part[8];
   __shared__ float2 row_total;
@@ -68,19 +69,21 @@ rescale_rows_kernel(void *__restrict__ out_v, int out_f32, int N, int64_t ld_out
   for (int t = threadIdx.x; t < num_nb; t += blockDim.x)
     factor[t] = ex2_approx(tile_stats[row * num_nb + t].x - gm) * inv;
   __syncthreads();
+  const int c0 = blockIdx.y * chunk;                       // my columns: [c0, c1)
+  const int c1 = min(N, c0 + chunk);
 
   if (out_f32) {
     float *frow = static_cast<float *>(out_v) + row * ld_out;
     if ((N % 4 == 0) && (ld_out % 4 == 0) && ((reinterpret_cast<uintptr_t>(out_v) & 15) == 0) && (BN % 4 == 0)) {
       float4 *o4 = reinterpret_cast<float4 *>(frow);
-      for (int j = threadIdx.x; j < N / 4; j += blockDim.x) {
+      for (int j = c0 / 4 + threadIdx.x; j < c1 / 4; j += blockDim.x) {
         const float fct = factor[(j * 4) / BN];
         float4 x = o4[j];
         x.x *= fct; x.y *= fct; x.z *= fct; x.w *= fct;
         o4[j] = x;
       }
     } else {
-      for (int j = threadIdx.x; j < N; j += blockDim.x) frow[j] *= factor[j / BN];
+      for (int j = c0 + threadIdx.x; j < c1; j += blockDim.x) frow[j] *= factor[j / BN];
     }
     return;
   }
@@ -89,7 +92,7 @@ rescale_rows_kernel(void *__restrict__ out_v, int out_f32, int N, int64_t ld_out
   const bool vec_ok = (N % 8 == 0) && (ld_out % 8 == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0) && (BN % 8 == 0);
   if (vec_ok) {
     uint4 *o4 = reinterpret_cast<uint4 *>(orow);
-    for (int j = threadIdx.x; j < N / 8; j += blockDim.x) {
+    for (int j = c0 / 8 + threadIdx.x; j < c1 / 8; j += blockDim.x) {
       const float f = factor[(j * 8) / BN];
       uint4 x = o4[j];
       __half2 *h = reinterpret_cast<__half2 *>(&x);
@@ -101,7 +104,7 @@ rescale_rows_kernel(void *__restrict__ out_v, int out_f32, int N, int64_t ld_out
       o4[j] = x;
     }
   } else {
-    for (int j = threadIdx.x; j < N; j += blockDim.x)
+    for (int j = c0 + threadIdx.x; j < c1; j += blockDim.x)
       orow[j] = __float2half_rn(__half2float(orow[j]) * factor[j / BN]);
   }
 }
@@ -129,8 +132,18 @@ cudaError_t launch_rescale_rows(void *out, int out_f32, int64_t rows, int N, int
                                 const float2 *tile_stats, const float2 *global_stats, int num_parts,
                                 cudaStream_t s) {
   if (rows <= 0) return cudaSuccess;
+  // few rows (skinny problems): several CTAs per row so that the pass still fills the chip
+  // (16 rows x 32000 columns: one CTA per row takes 12 us, sixteen per row 3 us)
+  int splits = 1, chunk = N;
+  if (rows < 2 * 148 && N > 4096) {
+    const int want = static_cast<int>((2 * 148 + rows - 1) / rows);
+    const int by_size = (N + 2047) / 2048;
+    splits = want < by_size ? want : by_size;
+    chunk = ((N + splits - 1) / splits + 255) / 256 * 256;
+    splits = (N + chunk - 1) / chunk;
+  }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(static_cast<unsigned>(rows), 1, 1);
+  cfg.gridDim = dim3(static_cast<unsigned>(rows), static_cast<unsigned>(splits), 1);
   cfg.blockDim = dim3(256, 1, 1);
   cfg.dynamicSmemBytes = num_nb * sizeof(float);
   cfg.stream = s;
@@ -140,7 +153,7 @@ cudaError_t launch_rescale_rows(void *out, int out_f32, int64_t rows, int N, int
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, rescale_rows_kernel, out, out_f32, N, ld_out, BN, num_nb, tile_stats,
-                            global_stats, num_parts, rows);
+                            global_stats, num_parts, rows, chunk);
 }
 
 // ---- f32 -> f16 rounding of an operand (the chain that truncates its f32 arguments) --------
