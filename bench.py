@@ -403,6 +403,13 @@ def main():
         cpu = dict(value=2.0 * rows * N * K / dt_s / 1e12, unit="TFLOP/s", cores=threads, kind="port",
                    sample=f"{rows} of {wl['batch'] * M} rows, {reps} repetitions of the scalar loop-nest restatement "
                           f"(f32 accumulate, separate max/exp/sum/div passes), rows spread over {threads} threads")
+        # the same loop nest on ONE thread (what a plain linalg-to-loops lowering runs as), on a smaller slice
+        rows1 = max(1, min(rows, int(2.0e9 / (2.0 * N * K))))
+        t1 = time.perf_counter()
+        oracle.chain_loops_f32(A[:rows1], B, scale, 1)
+        dt1 = time.perf_counter() - t1
+        cpu["single_thread"] = dict(value=2.0 * rows1 * N * K / dt1 / 1e12, unit="TFLOP/s", cores=1,
+                                    sample=f"{rows1} rows, one pass")
 
     line = dict(metric="fused_matmul_softmax_tflops", value=value, unit="TFLOP/s", n_gpus=world, steps=args.steps,
                 warmup=args.warmup, ms_per_step=ms_per_step, us_per_call=ms_per_step * 1e3,
