@@ -295,3 +295,35 @@ def test_solver_profiles_top_candidates_through_the_profiler_binary(tmp_path):
     # a profiler that fails leaves the candidates unmeasured and the model's order in place
     r = subprocess.run(args[:-4] + ["--profile-profiler-bin", str(fake)], capture_output=True, text=True)
     assert r.returncode == 0 and "tileN=256" in r.stdout
+
+
+def test_generated_chains_round_trip_through_the_recogniser(tmp_path):
+    """Every spelling the generator can write (decomposed / named softmax, batched, scaled, f16
+    operands and results, f32 arguments rounded to f16) parses back to the shapes, types and
+    scale it was written with, through the search-only front-end."""
+    import importlib.util
+    import random
+    spec = importlib.util.spec_from_file_location("gen_chains", os.path.join(MLIR, "gen_chains.py"))
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    rng = random.Random(7)
+    for case in range(24):
+        batch = rng.choice([1, 1, 3, 8])
+        M, N, K = rng.randrange(1, 5000), rng.randrange(1, 40000), rng.randrange(1, 3000)
+        in_t = rng.choice(["f32", "f16"])
+        arg_t = "f32" if (in_t == "f16" and rng.random() < 0.3) else None
+        acc_t = rng.choice(["f32", "f16"]) if in_t == "f16" else "f32"
+        out_t = rng.choice(["f32", "f16"]) if in_t == "f16" else "f32"
+        scale = rng.choice([1.0, 0.125, 1.0 / 3.0, 17.5])
+        named = rng.random() < 0.4
+        path = tmp_path / f"c{case}.mlir"
+        path.write_text(gen.chain(batch, M, N, K, in_t=in_t, acc_t=acc_t, out_t=out_t, scale=scale, named=named, title=f"case {case}", arg_t=arg_t))
+        out = tmp_path / f"o{case}"
+        r = run(["--input", str(path), "--out-dir", str(out), "--search-only", "--backend-mode", "api"])
+        assert r.returncode == 0, (case, r.stderr)
+        c = json.load(open(out / "ir" / "chain.json"))
+        assert (c["batch"], c["M"], c["N"], c["K"]) == (batch, M, N, K), case
+        assert (c["arg_dtype"], c["in_dtype"], c["acc_dtype"], c["out_dtype"]) == (arg_t or in_t, in_t, acc_t, out_t), case
+        assert abs(c["scale"] - scale) <= 1e-6 * scale and c["softmax_form"] == ("named" if named else "decomposed"), case
+        best = json.load(open(out / "search" / "best.json"))
+        assert best["tileM"] > 0 and best["tileN"] > 0 and best["tileK"] > 0
