@@ -51,7 +51,7 @@ constexpr int kMaxCluster = 8;
 
 // OUT_TILES: 32-row x 64-column f16 staging tiles per epilogue warp (2 = the warp's two
 // column groups never wait for each other's TMA read; 1 = smaller, leaves room for a stage).
-template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool RELAY, bool PAIR, int EW, bool OUT32 = false>
+template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool RELAY, bool PAIR, int EW, bool OUT32 = false, bool SINGLE = false>
 struct SmemLayout {
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BK * BN * 2 / (PAIR ? 2 : 1);     // a CTA pair splits B's columns between its two CTAs
@@ -116,16 +116,21 @@ __device__ __forceinline__ void stamp_fine(const TcParams &p, int seq, int k) {
   if (p.timeline && p.timeline_mode == 2 && (seq == 1 || seq == 2)) stamp(p.timeline, (seq - 1) * 8 + k);
 }
 
-template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool RELAY, bool PAIR, int EW, bool OUT32 = false>
+template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool RELAY, bool PAIR, int EW, bool OUT32 = false, bool SINGLE = false>
 __global__ void __launch_bounds__(kThreadsFor(EW, RELAY), 1)
 fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmO, const TcParams p) {
-  using L = SmemLayout<BN, STAGES, CLUSTER, OUT_TILES, RELAY, PAIR, EW, OUT32>;
+  using L = SmemLayout<BN, STAGES, CLUSTER, OUT_TILES, RELAY, PAIR, EW, OUT32, SINGLE>;
   constexpr int HC = L::kHalfCols;      // columns per epilogue thread
   constexpr int NCH = HC / 32;          // 32-column chunks per epilogue thread
   constexpr int kEpiThreads = EW * 32;
   constexpr int PARTS = BN / HC;        // threads that share a row (split epilogue)
   static_assert(!RELAY || (EW == 16 && CLUSTER && !PAIR && OUT_TILES == 1 && !OUT32), "relay epilogue: cluster flavour, f16 staged stores, sixteen warps");
+  // SINGLE: every CTA owns exactly one tile (the launcher checks it).  Nothing can overlap with a
+  // next tile then, so the exp group keeps the first 64 columns of its share in registers and
+  // writes them out itself, through staging tiles laid over the operand stages (idle once the
+  // tile's accumulator is complete); the store group takes only the last 64 columns.
+  static_assert(!SINGLE || (RELAY && STAGES * L::kStageBytes >= 8 * 4096), "single-tile form: relay only");
   static_assert(!OUT32 || (!RELAY && !PAIR && EW == 8 && OUT_TILES >= 1), "f32 output: the eight-warp split epilogue with staged stores");
   static_assert(EW == 8 || (CLUSTER && OUT_TILES == 1 && !PAIR), "sixteen epilogue warps: cluster flavour with staged stores only");
   // The 128-byte swizzle needs the stage buffers on 1024-byte boundaries.  There is no
@@ -240,7 +245,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   // role's code sits under its own reallocation so the allocator sees one budget per region.
   const int relay_role = !RELAY ? 0 : (warp < 4 ? 0 : (warp < 12 ? 1 : 2));
   if (RELAY && relay_role == 1) {
-    setmaxnreg_inc<152>();
+    setmaxnreg_inc<SINGLE ? 160 : 152>();
     // ======================= softmax epilogue, two-stage relay ==============
     // Two groups of eight epilogue warps work on consecutive tiles at the same time.  The
     // first group (warps 4-11, 152 registers a thread after the reallocation above) turns
@@ -369,8 +374,11 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       // ---- e = 2^(v - m_half) in place, row sum; each chunk goes back over its logits ----
       float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
       if (valid == HC) {
+        // (single-tile form: the chunks that go to tensor memory first, so their registers are
+        // free while the two chunks this thread keeps are processed and held)
 #pragma unroll
-        for (int c = 0; c < NCH; ++c) {
+        for (int k = 0; k < NCH; ++k) {
+          const int c = SINGLE ? (k + 2) % NCH : k;
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
             const float e0 = ex2_approx(fmaf(__uint_as_float(r[c][i]), c2, -m_half));
@@ -381,11 +389,12 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             r[c][i] = __float_as_uint(e0); r[c][i + 1] = __float_as_uint(e1);
             r[c][i + 2] = __float_as_uint(e2); r[c][i + 3] = __float_as_uint(e3);
           }
-          tmem_st_32x32b_x32(tbase + c * 32, r[c]);
+          if (!(SINGLE && c < 2)) tmem_st_32x32b_x32(tbase + c * 32, r[c]);
         }
       } else {
 #pragma unroll
-        for (int c = 0; c < NCH; ++c) {
+        for (int k = 0; k < NCH; ++k) {
+          const int c = SINGLE ? (k + 2) % NCH : k;
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             float e = 0.f;
@@ -393,7 +402,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             s0 += e;
             r[c][i] = __float_as_uint(e);
           }
-          if (c * 32 < valid) tmem_st_32x32b_x32(tbase + c * 32, r[c]);
+          if (c * 32 < valid && !(SINGLE && c < 2)) tmem_st_32x32b_x32(tbase + c * 32, r[c]);
         }
       }
       const float sum = (s0 + s1) + (s2 + s3);
@@ -418,9 +427,46 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       tc_fence_before_sync();
       mbar_arrive(&xdone[ab]);                    // exp values parked, maxima published
       if (stamper) stamp_tile(p, it, 2);
+      if (SINGLE && valid > 0) {
+        // ---- single-tile form: this thread scales, packs and stores its first 64 columns itself ----
+        if (!mbar_wait_cluster(&stats_bar[sset], 0)) { record_failure(p.status, WTC_DEV_TIMEOUT_STATS); break; }
+        float gm, inv_gl;
+        {
+          float xs[kMaxCluster];
+#pragma unroll
+          for (int j = 0; j < kMaxCluster; ++j)
+            xs[j] = static_cast<uint32_t>(j) < cluster_n ? stats[(sset * kMaxCluster + j) * BM + row_in_tile].x : -INFINITY;
+          gm = fmaxf(fmaxf(max3(xs[0], xs[1], xs[2]), max3(xs[3], xs[4], xs[5])), fmaxf(xs[6], xs[7]));
+          float l = 0.f;
+#pragma unroll
+          for (int j = 0; j < kMaxCluster; ++j)
+            if (static_cast<uint32_t>(j) < cluster_n) l += stats[(sset * kMaxCluster + j) * BM + row_in_tile].y * ex2_approx(xs[j] - gm);
+          inv_gl = rcp_approx(l);
+        }
+        const float f = ex2_approx(m_half - gm) * inv_gl;
+        uint8_t *xstg = smem + (warp - 4) * 4096;   // over operand stage 0: every stage has been consumed
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t hc[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const __half2 hh = __floats2half2_rn(__uint_as_float(r[c][i]) * f, __uint_as_float(r[c][i + 1]) * f);
+            hc[i >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
+          }
+          stage_row_chunk(xstg, lane, c, hc);       // (columns past `valid` hold zeros: e was 0 there)
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          const int row0 = rb * BM + q * 32;
+          if (row0 < p.M) tma_store_3d(&tmO, xstg, col0, row0, b);
+          tma_store_commit();
+          tma_store_wait_all();
+        }
+      }
     }
   } else if (RELAY && relay_role == 2) {
-    setmaxnreg_dec<64>();
+    setmaxnreg_dec<SINGLE ? 56 : 64>();
     const int q = warp & 3;                       // TMEM lane quarter this warp may touch
     const int row_in_tile = q * 32 + lane;
     float *mh = reinterpret_cast<float *>(smem + L::kOffMh);   // [2][2][BM]: each half's own maximum, per tile parity
@@ -454,13 +500,14 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       // wait packed in registers, so the accumulator buffer goes back to the MMA warp after
       // the fourth load and before anything waits for a store.
       static_assert(!RELAY || NCH == 4, "relay epilogue: a thread owns 128 columns");
-      if (valid == 0) { tc_fence_before_sync(); release_accumulator(ab); }
+      if (valid == 0 || (SINGLE && valid <= 64)) { tc_fence_before_sync(); release_accumulator(ab); }
       if (lane == 0) tma_store_wait_read();         // the previous tile's store has read the staging tile
       __syncwarp();
       uint32_t h[2][16];
 #pragma unroll
       for (int c = 0; c < NCH; ++c) {
         uint32_t hc[16];
+        if (SINGLE && c < 2) continue;                // the exp group writes these columns itself
         if (c * 32 < valid) {
           uint32_t r[32];
           tmem_ld_32x32b_x32(tbase + c * 32, r);
@@ -478,13 +525,13 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
           for (int i = 0; i < 16; ++i) hc[i] = 0u;
         }
-        if (c < 2) stage_row_chunk(stg, lane, c, hc);
+        if (c < 2 || SINGLE) stage_row_chunk(stg, lane, c & 1, hc);   // single-tile form: nothing in flight, stage straight away
         else {
 #pragma unroll
           for (int i = 0; i < 16; ++i) h[c - 2][i] = hc[i];
         }
       }
-      if (valid > 0) {
+      if (valid > 0 && !SINGLE) {
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
@@ -493,10 +540,12 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
       }
       if (valid > 64) {
-        if (lane == 0) tma_store_wait_read();
-        __syncwarp();
-        stage_row_chunk(stg, lane, 0, h[0]);
-        stage_row_chunk(stg, lane, 1, h[1]);
+        if (!SINGLE) {
+          if (lane == 0) tma_store_wait_read();
+          __syncwarp();
+          stage_row_chunk(stg, lane, 0, h[0]);
+          stage_row_chunk(stg, lane, 1, h[1]);
+        }
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
@@ -511,7 +560,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     if (lead && p.timeline_mode == 0) stamp(p.timeline, 5);
     
   } else {
-  if (RELAY) setmaxnreg_dec<48>();
+  if (RELAY) setmaxnreg_dec<SINGLE ? 40 : 48>();
   if (warp == 0) {
     // ======================= TMA producer ==================================
     uint32_t n = 0;
@@ -898,11 +947,11 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   if (warp == 1) { if (PAIR) tmem_dealloc_pair(tmem_base, 2 * BN); else tmem_dealloc(tmem_base, 2 * BN); }
 }
 
-template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool RELAY, bool PAIR, int EW, bool OUT32 = false>
+template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool RELAY, bool PAIR, int EW, bool OUT32 = false, bool SINGLE = false>
 cudaError_t launch_impl(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO, TcParams p,
                         int cluster_n, int num_sms, cudaStream_t s, TcLaunchInfo *info) {
-  using L = SmemLayout<BN, STAGES, CLUSTER, OUT_TILES, RELAY, PAIR, EW, OUT32>;
-  auto kern = fused_tc_kernel<BN, STAGES, CLUSTER, OUT_TILES, RELAY, PAIR, EW, OUT32>;
+  using L = SmemLayout<BN, STAGES, CLUSTER, OUT_TILES, RELAY, PAIR, EW, OUT32, SINGLE>;
+  auto kern = fused_tc_kernel<BN, STAGES, CLUSTER, OUT_TILES, RELAY, PAIR, EW, OUT32, SINGLE>;
   static bool attr_set = false;   // per template instance
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
@@ -944,6 +993,7 @@ cudaError_t launch_impl(const CUtensorMap &tmA, const CUtensorMap &tmB, const CU
       max_clusters_cache[cluster_size] = mc;
     }
     const int max_clusters = max_clusters_cache[cluster_size];
+    if (SINGLE && p.num_items > max_clusters) return cudaErrorNotSupported;   // some CTA would own two tiles: the caller takes another form
     const int clusters = p.num_items < max_clusters ? p.num_items : max_clusters;
     grid = clusters * cluster_size;
   } else {
@@ -985,6 +1035,12 @@ cudaError_t launch_fused_cluster(const CUtensorMap &tmA, const CUtensorMap &tmB,
     const int tiles_per_cta = (p.batch * p.num_rb + resident - 1) / (resident > 0 ? resident : 1);
     const bool relay = p.epilogue_mode == 2 || (p.epilogue_mode == 0 && tiles_per_cta >= kRelayMinTiles);
     if (relay) return launch_impl<kTcBlockN, 3, true, 1, true, false, 16>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+    // one tile per CTA: the single-tile relay form (both groups share the tile's store phase), unless
+    // a form was asked for; it declines (before launching) when the clusters do not all fit at once
+    if (p.epilogue_mode == 0 && p.epilogue_warps != 16) {
+      const cudaError_t e = launch_impl<kTcBlockN, 3, true, 1, true, false, 16, false, true>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+      if (e != cudaErrorNotSupported) return e;
+    }
     // sixteen epilogue warps (a row's columns split four ways) on request: measured on B200 it
     // does not beat eight (the exp and pack phases are bound by the special-function unit)
     if (p.epilogue_warps == 16)

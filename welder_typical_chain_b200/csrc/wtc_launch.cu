@@ -161,8 +161,12 @@ int resolve(const wtc_chain_desc *in, Resolved &r) {
       p.cluster_n = r.num_nb;
       p.stages = r.bn == 128 ? 4 : 3;
       const int64_t resident = 148 / r.num_nb;
-      const int64_t tiles_per_cta = (static_cast<int64_t>(d.batch) * r.num_rb + resident - 1) / resident;
-      if (plain && tiles_per_cta >= wtc::kRelayMinTiles) p.threads = 640;   // relay epilogue: twenty warps
+      const int64_t units = static_cast<int64_t>(d.batch) * r.num_rb;
+      const int64_t tiles_per_cta = (units + resident - 1) / resident;
+      // relay epilogue (twenty warps) when a CTA sees several tiles, its single-tile form when every
+      // cluster fits the chip at once; otherwise the eight-warp split form
+      static const int kResidentClusters[9] = {0, 148, 72, 47, 35, 27, 22, 18, 15};
+      if (plain && (tiles_per_cta >= wtc::kRelayMinTiles || units <= kResidentClusters[r.num_nb])) p.threads = 640;
     } else {
       p.kernel = WTC_KERNEL_TC_TILED;
       p.launches = 2;
