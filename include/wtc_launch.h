@@ -47,6 +47,12 @@ extern "C" {
  * reference.  Needs in_dtype = WTC_F32.  The rounded copies live in the workspace
  * (wtc_matmul_softmax_workspace_bytes counts them); the single-GPU entry points only. */
 #define WTC_FLAG_MATMUL_F16 0x4
+/* Schedule overrides, for experiments and for the tests that run every kernel form:
+ * the launch layer normally picks the epilogue form and the CTA pairing by shape. */
+#define WTC_FLAG_EPILOGUE_SPLIT 0x8  /* cluster flavour: eight epilogue warps share a tile            */
+#define WTC_FLAG_EPILOGUE_RELAY 0x10 /* cluster flavour: two warp groups relay consecutive tiles      */
+#define WTC_FLAG_NO_PAIR 0x20        /* tiled flavour: never pair CTAs for tcgen05 cta_group::2       */
+#define WTC_FLAG_PAIR 0x40           /* tiled flavour: pair CTAs whenever there are two row blocks    */
 
 /* error codes */
 #define WTC_OK 0
@@ -157,32 +163,39 @@ int wtc_matmul_softmax_host(const wtc_chain_desc *desc, const void *hostA, const
  * up, a step loop that must not hit the device-wide synchronisation an
  * allocation implies, a plugin running under a memory budget it may not exceed.
  * This entry point runs the two-pass tiled schedule with its scratch -- the
- * per-tile (max, sum) pairs and the device status word -- in an array that is
- * part of the library image: WTC_STATIC_SCRATCH_BYTES (16 MiB) on every GPU
- * that loads the library, held until the process exits.  It calls no cudaMalloc,
- * cudaFree or allocating library routine; the caller still provides A, B and Out
- * (device pointers).
+ * per-tile (max, sum) pairs -- in an array that is part of the library image:
+ * WTC_STATIC_SCRATCH_BYTES (16 MiB) on every GPU that loads the library, held
+ * until the process exits.  It calls no cudaMalloc, cudaFree or allocating
+ * library routine; the caller still provides A, B and Out (device pointers).
  *
  * Limits and rules:
  *  - f16 operands and output on the tensor-core path only (K, N and the row
- *    strides multiples of 8), and batch * M * ceil(N/256) * 8 bytes of scratch
- *    must fit: WTC_E_UNSUPPORTED / WTC_E_WORKSPACE otherwise, with the sizes in
- *    wtc_last_error().
+ *    strides multiples of 8; A, B and Out on 16-byte boundaries), and
+ *    batch * M * ceil(N/tile) * 8 bytes of scratch must fit (tile = 256 columns,
+ *    128 for rows of at most 128 columns): WTC_E_UNSUPPORTED / WTC_E_WORKSPACE
+ *    otherwise, with the sizes in wtc_last_error().  Empty shapes return WTC_OK.
  *  - The first call on each device looks the array's device address up (with
- *    that device current).  Make that first call outside any stream capture.
+ *    that device current), and, like the first launch of any kernel of the
+ *    library, makes the CUDA runtime load the library's device image -- the
+ *    16 MiB array included.  A host whose pool already owns HBM should make that
+ *    first call at start-up, before it hands the memory out, and outside any
+ *    stream capture.
  *  - Every call on a device shares the one array.  Calls whose kernels may
  *    overlap on the GPU (two streams, two threads) race on it: serialise them.
  *    Nothing is assumed about what the previous call left there.
- *  - device_status: as for wtc_matmul_softmax_launch (a zeroed int32 in the
- *    caller's own device memory, checked with wtc_check_device_status).  With
- *    NULL the kernels report into a word inside the static array, which this
- *    call clears first and no entry point reads back.
+ *  - device_status: as for wtc_matmul_softmax_launch.  With NULL the kernels
+ *    report into the library's own status word -- also a word of the library
+ *    image, never allocated -- which wtc_check_device_status(NULL, stream) reads
+ *    and then clears.
  */
 #define WTC_STATIC_SCRATCH_BYTES (16u << 20)
 int wtc_matmul_softmax_launch_static(const wtc_chain_desc *desc, const void *A, const void *B, void *Out,
                                      void *stream, int *device_status);
 
-/* Synchronise `stream`, read a device status word, 0 if clean else WTC_E_DEVICE. */
+/* Synchronise `stream`, read a device status word, 0 if clean else WTC_E_DEVICE.
+ * device_status NULL reads the library's own per-device word (the one kernels use when a
+ * launch was given no status pointer) and clears it after a non-zero report; a caller's
+ * word is the caller's to clear.  Allocates nothing. */
 int wtc_check_device_status(const int *device_status, void *stream);
 
 /*
@@ -195,34 +208,10 @@ int wtc_matmul_softmax_time(const wtc_chain_desc *desc, const void *A, const voi
                             float *avg_ms);
 
 /*
- * Kernel variants.  The launch layer picks the schedule; these environment variables,
- * read at every launch, override the choice for experiments and for the variant tests:
- *   WTC_EPILOGUE=split|relay  eight epilogue warps share a tile | two groups of eight overlap consecutive tiles
- *   WTC_EW=16                 sixteen epilogue warps (cluster flavour, staged stores)
- *   WTC_STORE=direct          256-bit register stores instead of staged TMA stores
- *   WTC_PAIR=0|1              never | always pair CTAs for tcgen05 cta_group::2
- *   WTC_HOST_SLABS=n          pieces the host-buffer entry point cuts a call into (default: ~6 MB each, at most 8)
- *   WTC_NO_PDL=1              (read once at load) no programmatic dependent launch
- *   WTC_TL_MODE=0|1|2         layout of the profiling stamps (wtc_debug_set_timeline)
+ * Environment, read once when the library first needs it:
+ *   WTC_HOST_SLABS=n   pieces the host-buffer entry point cuts a call into (default: by size, at most 8)
+ *   WTC_NO_PDL=1       no programmatic dependent launch
  */
-
-/*
- * Bring-up aid: override the UMMA shared-memory descriptor geometry (byte
- * offsets: leading / stride / per-MMA K step, for A then B) used by the
- * tensor-core kernels.  Pass all zeros to restore the built-in values.
- */
-int wtc_debug_set_umma_geometry(uint32_t a_lbo, uint32_t a_sbo, uint32_t a_kstep, uint32_t b_lbo,
-                                uint32_t b_sbo, uint32_t b_kstep);
-
-/*
- * Profiling aid: when set to a device buffer of grid*16 int64, the tensor-core
- * kernels stamp %globaltimer (ns) for their first tile: [0] set-up done,
- * [1] accumulator complete, [2] first softmax pass done, [3] row statistics
- * received, [4] staged for the store, [5] epilogue finished, [6] first TMA load
- * issued, [7] first stage landed, [8] last MMA of the first tile committed.
- * NULL (the default) switches the stamps off.
- */
-int wtc_debug_set_timeline(void *device_buffer);
 
 #ifdef __cplusplus
 }

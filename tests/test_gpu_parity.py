@@ -363,17 +363,15 @@ def test_few_rows_wide_row_rescale_is_split_over_ctas(w, cuda_dev):
 
 # ---------------------------------------------------------------- kernel variants
 
-@pytest.mark.parametrize("env", [
-    {"WTC_EPILOGUE": "relay"},                      # two warp groups overlap consecutive tiles, exp values parked in TMEM
-    {"WTC_EW": "16"},                               # sixteen epilogue warps, a row split four ways
-    {"WTC_STORE": "direct"},                        # 256-bit register->global stores instead of staged TMA stores
-    {"WTC_PAIR": "1"},                              # tcgen05 cta_group::2 in the cluster flavour too
-    {"WTC_PAIR": "0"},                              # never pair
-    {"WTC_EPILOGUE": "split"},
+@pytest.mark.parametrize("extra", [
+    "FLAG_EPILOGUE_RELAY",      # two warp groups overlap consecutive tiles, exp values parked in TMEM
+    "FLAG_EPILOGUE_SPLIT",      # eight epilogue warps share a tile
+    "FLAG_PAIR",                # tcgen05 cta_group::2 whenever the tiled flavour has two row blocks
+    "FLAG_NO_PAIR",             # never pair
+    None,                       # the launch layer's own choice
 ])
-def test_every_kernel_variant_matches_the_checker(w, cuda_dev, monkeypatch, env):
-    for k, v in env.items():
-        monkeypatch.setenv(k, v)
+def test_every_kernel_variant_matches_the_checker(w, cuda_dev, extra):
+    xf = getattr(w, extra) if extra else 0
     cases = [
         (777, 1024, 136, 0.07, 0),                  # cluster of 4, ragged M and K, several tiles per cluster
         (9000, 2048, 64, 0.125, 0),                 # cluster of 8, many tiles per CTA
@@ -384,12 +382,12 @@ def test_every_kernel_variant_matches_the_checker(w, cuda_dev, monkeypatch, env)
     for M, N, K, scale, flags in cases:
         A = oracle.normal((M, K), M)
         B = oracle.normal((K, N), N)
-        _check(_run(w, cuda_dev, A, B, scale, flags=flags), oracle.chain(A, B, scale))
+        _check(_run(w, cuda_dev, A, B, scale, flags=flags | xf), oracle.chain(A, B, scale))
     # a negative scale turns the row maximum into a minimum of the raw accumulators; logits
     # rounded to f16 (the f16 matmul result) take the epilogue's general path; batched with B per batch
     A = oracle.normal((1500, 64), 7); B = oracle.normal((64, 1024), 8)
-    _check(_run(w, cuda_dev, A, B, -0.11), oracle.chain(A, B, -0.11))
+    _check(_run(w, cuda_dev, A, B, -0.11, flags=xf), oracle.chain(A, B, -0.11))
     A = oracle.normal((3, 520, 72), 9) * np.float16(0.25); B = oracle.normal((3, 72, 768), 10) * np.float16(0.25)
-    got = _run(w, cuda_dev, A, B, 1.0, acc_dtype=w.F16)
+    got = _run(w, cuda_dev, A, B, 1.0, acc_dtype=w.F16, flags=xf)
     ref = np.stack([oracle.chain(A[i], B[i], 1.0, acc=oracle.ACC_F16_SEQ) for i in range(3)])
     assert np.abs(got.astype(np.float64) - ref).max() < 5e-3

@@ -297,15 +297,77 @@ def test_solver_profiles_top_candidates_through_the_profiler_binary(tmp_path):
     assert r.returncode == 0 and "tileN=256" in r.stdout
 
 
+def _chain_gen():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("chain_gen", os.path.join(os.path.dirname(os.path.abspath(__file__)), "chain_gen.py"))
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    return gen
+
+
+def test_chains_that_are_not_the_operator_are_rejected(tmp_path):
+    """The recogniser follows the dataflow: anything that is not scale * A . B followed by a row
+    softmax is refused at the canonicalize stage instead of being compiled as the fixed kernel."""
+    gen = _chain_gen()
+    ok = dict(batch=1, M=256, N=512, K=64, in_t="f16", out_t="f16", scale=0.125)
+    cases = {
+        "factor after the division": (gen.chain(**ok, post_scale=2.0), "division"),
+        "non-zero matmul init": (gen.chain(**ok, fill="1.0"), "zero fill"),
+        "constant added to the logits": (gen.chain(**ok, extra_add=0.5), "between the matmul and the softmax"),
+        "factor after a named softmax": (gen.chain(**ok, named=True, post_scale=0.5), "division"),
+    }
+    # a sum that does not start from zero, a maximum that starts from zero, an exp of the wrong difference,
+    # swapped matmul operands, a second (dead) generic
+    good = gen.chain(**ok, aliases=False)
+    cases["row sum from 1"] = (good.replace("%zero = arith.constant 0.0 : f32", "%zero = arith.constant 1.0 : f32"), "start from 0")
+    cases["row max from 0"] = (good.replace("%neg_inf = arith.constant -3.4028235e+38 : f32", "%neg_inf = arith.constant 0.0 : f32"), "most negative")
+    cases["exp(max - x)"] = (good.replace("%d = arith.subf %x, %m : f32", "%d = arith.subf %m, %x : f32"), "math.exp(x - row_max)")
+    cases["min instead of max"] = (good.replace("arith.maximumf", "arith.minimumf"), "row maximum")
+    sq = gen.chain(batch=1, M=64, N=64, K=64, aliases=False)
+    cases["B . A"] = (sq.replace("ins(%A, %B :", "ins(%B, %A :"), "first and second argument")
+    cases["an operation outside the chain"] = (good.replace("    return %P16", "    %dead_empty = tensor.empty() : tensor<256x512xf32>\n"
+                                               "    %dead = linalg.fill ins(%zero : f32) outs(%dead_empty : tensor<256x512xf32>) -> tensor<256x512xf32>\n    return %P16"), "outside the chain")
+    for name, (text, needle) in cases.items():
+        path = tmp_path / "bad.mlir"
+        path.write_text(text)
+        r = run(["--input", str(path), "--out-dir", str(tmp_path / "o"), "--search-only", "--backend-mode", "api"])
+        assert r.returncode == 1, name
+        assert "canonicalize failed" in r.stderr and needle in r.stderr, (name, r.stderr)
+    # and the unbroken chain, in both spellings, is accepted
+    for text in (gen.chain(**ok), good):
+        path = tmp_path / "good.mlir"
+        path.write_text(text)
+        assert run(["--input", str(path), "--out-dir", str(tmp_path / "g"), "--search-only", "--backend-mode", "api"]).returncode == 0
+
+
+REFERENCE_ROOT = os.environ.get("WTC_REFERENCE_ROOT", "/root/reference")
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REFERENCE_ROOT, "mlir")), reason="the reference tree is not mounted here")
+def test_the_reference_inputs_compile_unmodified(tmp_path):
+    """The reference's own operator inputs, read where they lie (they are not copied into this
+    repository), go through the whole front-end: canonicalize, tag, search, compile."""
+    files = [os.path.join(REFERENCE_ROOT, "mlir", f) for f in ("matmul_softmax_chain.mlir", "matmul_softmax_chain_f16_native.mlir",
+                                                               "matmul_softmax_chain_named_softmax.mlir")]
+    files.append(os.path.join(REFERENCE_ROOT, "backend/welder/mlir_pipeline/matmul_softmax_chain_f16_matmul.mlir"))
+    want = {"matmul_softmax_chain.mlir": ("f32", "f32", "f32", "decomposed"), "matmul_softmax_chain_f16_native.mlir": ("f16", "f16", "f32", "decomposed"),
+            "matmul_softmax_chain_named_softmax.mlir": ("f32", "f32", "f32", "named"), "matmul_softmax_chain_f16_matmul.mlir": ("f16", "f16", "f32", "decomposed")}
+    for f in files:
+        out = tmp_path / os.path.basename(f)
+        r = run(["--input", f, "--out-dir", str(out), "--backend-mode", "api"])
+        assert r.returncode == 0, (f, r.stderr)
+        c = json.load(open(out / "ir" / "chain.json"))
+        assert (c["batch"], c["M"], c["N"], c["K"], c["scale"]) == (1, 8192, 128, 64, 1), f
+        assert (c["in_dtype"], c["acc_dtype"], c["out_dtype"], c["softmax_form"]) == want[os.path.basename(f)], f
+        assert (out / "fused/05.out.nvvm.runnable.mlir").exists()
+
+
 def test_generated_chains_round_trip_through_the_recogniser(tmp_path):
     """Every spelling the generator can write (decomposed / named softmax, batched, scaled, f16
     operands and results, f32 arguments rounded to f16) parses back to the shapes, types and
     scale it was written with, through the search-only front-end."""
-    import importlib.util
     import random
-    spec = importlib.util.spec_from_file_location("gen_chains", os.path.join(MLIR, "gen_chains.py"))
-    gen = importlib.util.module_from_spec(spec)
-    spec.loader.exec_module(gen)
+    gen = _chain_gen()
     rng = random.Random(7)
     for case in range(24):
         batch = rng.choice([1, 1, 3, 8])
@@ -317,7 +379,8 @@ def test_generated_chains_round_trip_through_the_recogniser(tmp_path):
         scale = rng.choice([1.0, 0.125, 1.0 / 3.0, 17.5])
         named = rng.random() < 0.4
         path = tmp_path / f"c{case}.mlir"
-        path.write_text(gen.chain(batch, M, N, K, in_t=in_t, acc_t=acc_t, out_t=out_t, scale=scale, named=named, title=f"case {case}", arg_t=arg_t))
+        path.write_text(gen.chain(batch, M, N, K, in_t=in_t, acc_t=acc_t, out_t=out_t, scale=scale, named=named, title=f"case {case}", arg_t=arg_t,
+                                  aliases=rng.random() < 0.5))
         out = tmp_path / f"o{case}"
         r = run(["--input", str(path), "--out-dir", str(out), "--search-only", "--backend-mode", "api"])
         assert r.returncode == 0, (case, r.stderr)

@@ -1,35 +1,44 @@
 // Fused Matmul -> row-Softmax for sm_100a: f16 operands, f32 accumulate in TMEM,
-// f16 probabilities.  One persistent, warp-specialised kernel in two flavours:
+// f16 (or f32) probabilities.  One persistent, warp-specialised kernel in two flavours:
 //
 //   CLUSTER = true   a thread-block cluster of ceil(N/BN) CTAs owns 128 complete
 //                    rows.  Each CTA contracts its 128 x BN slice, reduces its
 //                    local row (max, sum), sends the pair to its peers' shared
 //                    memory (st.async + mbarrier transaction bytes: no fences, no
-//                    cluster-wide barrier) and writes normalised f16.
+//                    cluster-wide barrier in the loop) and writes normalised values.
 //   CLUSTER = false  independent 128 x BN tiles.  Each writes exp(v - tile max)
 //                    as f16 and the per-tile (max, sum); a second, bandwidth-bound
 //                    kernel (row_softmax_kernels.cu) rescales the rows.  Used when
 //                    a row does not fit one cluster, and for skinny M.
 //
-// Warp roles (320 threads): warp 0 feeds shared memory with TMA, warp 1 owns TMEM
-// and issues tcgen05.mma, warps 2..9 are the softmax epilogue: thread = one row x
-// half of the tile's columns (TMEM lane quarter = warp_id % 4, column half =
-// (warp_id - 2) / 4).  Two accumulator buffers in TMEM let the epilogue of tile i
-// run under the contraction of tile i+1.  The logits never leave the SM:
-// TMEM -> registers -> swizzled shared -> TMA store.
+// Warp roles: ONE thread of warp 0 feeds shared memory with TMA, ONE thread of warp 1
+// issues tcgen05.mma (warp 1 also owns the TMEM allocation), the remaining warps are the
+// softmax epilogue.  The two single-thread loops are kept as short as possible: the tensor
+// pipe holds only a few instructions ahead, so every cycle the issuing thread spends on
+// anything else is a cycle the pipe idles (measured on B200: 4 MMAs of 128x256x16 take
+// 512 cycles; a loop that waits, builds descriptors from scratch and re-converges its warp
+// per K block ran at 740).  Hence: descriptors advanced by additions, the next stage's
+// barrier probed while the current MMAs drain, no warp-wide instruction inside the loop.
 //
-// Epilogue, per thread: its 128 accumulator values go TMEM -> registers in one go
-// and the accumulator buffer is released at once; row extreme, e = 2^(v - max) in
-// place (one MUFU per element), the row's (max, sum) exchange -- between the two
-// column halves through shared memory, between the CTAs of the cluster through
-// st.async -- then p = e * factor, packed to f16, staged 64 columns at a time in
-// 128-byte-swizzled shared memory and written with TMA stores.
-//
-// Other forms of the same kernel (template parameters): RELAY -- twenty warps, an "exp"
-// group and a "store" group that work on consecutive tiles at the same time, the exp values
-// parked in TMEM between them (chosen when a CTA sees several tiles); PAIR -- two CTAs issue
-// one 256-row tcgen05 cta_group::2 MMA; OUT32 -- f32 probabilities; EW = 16 -- a row's
-// columns split four ways; OUT_TILES = 0 -- register-to-global stores without staging.
+// Epilogue forms (template parameter EPI):
+//   EPI_SPLIT   eight warps; thread = one row x half of the tile's columns (TMEM lane
+//               quarter = warp_id % 4).  The thread's 128 accumulators go TMEM -> registers
+//               in one go and the accumulator buffer is released at once; row extreme,
+//               e = 2^(v - max) in place (one MUFU per element), the (max, sum) exchange --
+//               between the two halves through shared memory, between the CTAs of the
+//               cluster through st.async -- then p = e * factor, packed, staged in
+//               128-byte-swizzled shared memory and written with TMA stores.
+//   EPI_RELAY   sixteen warps in two groups that work on consecutive tiles at the same
+//               time: an "exp" group turns the accumulator into exp values in place in
+//               tensor memory and sends the row statistics, a "store" group scales, packs
+//               and stores them.  Chosen when a CTA sees several tiles.
+//   EPI_SINGLE  for launches in which every CTA owns exactly one tile (nothing can overlap
+//               with a next tile): sixteen warps, thread = one row x a quarter of the tile's
+//               columns, values in registers from the TMEM load to the staging tile; the
+//               staging tiles lie over the (by then idle) operand stages, which buys a
+//               fourth operand stage.
+// PAIR: two CTAs issue one 256-row tcgen05 cta_group::2 MMA (tiled flavour, long K).
+// OUT32: f32 probabilities.
 //
 // Operand layouts: A [M,K] is K-major, staged as 128 rows x 128 B with the 128-byte
 // swizzle.  B [K,N] has N contiguous, i.e. it is MN-major for the MMA: it is staged
@@ -44,23 +53,34 @@ namespace {
 
 constexpr int BM = kTcBlockM;
 constexpr int BK = kTcBlockK;
-// Epilogue warps per CTA: 8 (a thread owns one row x BN/2 columns) or 16 (one row x BN/4:
-// four warps per scheduler hide the TMEM-load and barrier latencies the eight-warp form exposes).
-constexpr int kThreadsFor(int ew, bool relay = false) { return relay ? 640 : 64 + ew * 32; }
 constexpr int kMaxCluster = 8;
+enum : int { EPI_SPLIT = 0, EPI_RELAY = 1, EPI_SINGLE = 2 };
+constexpr int kThreadsFor(int epi) { return epi == EPI_SPLIT ? 320 : (epi == EPI_RELAY ? 640 : 576); }
 
-// OUT_TILES: 32-row x 64-column f16 staging tiles per epilogue warp (2 = the warp's two
-// column groups never wait for each other's TMA read; 1 = smaller, leaves room for a stage).
-template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool RELAY, bool PAIR, int EW, bool OUT32 = false, bool SINGLE = false>
+// UMMA shared-memory descriptor geometry (bytes).
+//   A (K-major, 128-byte swizzle): 8-row groups are 1024 B apart; one 16-wide K step is 32 B.
+//   B (MN-major, 128-byte swizzle): 64-column blocks are 64 k-rows * 128 B = 8192 B apart
+//   (leading), 8-k-row groups are 1024 B apart (stride); one 16-deep K step is 16 * 128 B.
+constexpr uint32_t kALbo = 16, kASbo = 1024, kAKstep = 32;
+constexpr uint32_t kBLbo = 8192, kBSbo = 1024, kBKstep = 2048;
+
+template <int BN, int STAGES, bool CLUSTER, int EPI, bool PAIR, bool OUT32>
 struct SmemLayout {
+  static constexpr bool RELAY = EPI == EPI_RELAY;
+  static constexpr bool SINGLE = EPI == EPI_SINGLE;
   static constexpr int kABytes = BM * BK * 2;
   static constexpr int kBBytes = BK * BN * 2 / (PAIR ? 2 : 1);     // a CTA pair splits B's columns between its two CTAs
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kHalfCols = RELAY ? BN / 2 : BN * 4 / EW;       // columns per epilogue thread (per step)
-  static constexpr int kOutWarpBytes = OUT_TILES * 32 * 64 * 2;      // 0: the epilogue stores straight from registers
-  static constexpr int kOutBytes = (RELAY ? 8 : EW) * kOutWarpBytes;   // relay: only the storing group stages
-  static constexpr int kPairBytes = 2 * BM * 8;                       // [half][row] float2
-  static constexpr int kStatsSets = RELAY ? 4 : 2;                     // relay: a peer may run up to three tiles ahead of this CTA's storing group
+  static constexpr int kHalfCols = SINGLE ? BN / 4 : BN / 2;         // columns per epilogue thread
+  // 32-row x 64-column f16 (32 x 32 f32) staging tiles per storing warp: two let a warp's
+  // column groups go out without waiting for each other's TMA read; the tiled flavour and
+  // the relay take one and spend the room on operand stages
+  static constexpr int kOutTiles = (RELAY || SINGLE || !CLUSTER) ? 1 : 2;
+  static constexpr int kOutWarpBytes = kOutTiles * 4096;
+  static constexpr int kOutBytes = SINGLE ? 0 : 8 * kOutWarpBytes;   // single-tile form: staging lies over the operand stages
+  static constexpr int kPairBytes = (SINGLE ? 4 : 2) * BM * 8;        // [part][row] float2
+  // statistics sets: a peer's exp group may run up to three tiles ahead of this CTA's store group
+  static constexpr int kStatsSets = SINGLE ? 1 : (RELAY ? 4 : 2);
   static constexpr int kStatsBytes = CLUSTER ? kStatsSets * kMaxCluster * BM * 8 : 0;
   static constexpr int kOffOut = STAGES * kStageBytes;
   static constexpr int kOffPair = kOffOut + kOutBytes;
@@ -73,6 +93,7 @@ struct SmemLayout {
   static constexpr int kTotal = kOffTmemSlot + 16;
   static constexpr int kDynamic = kTotal;
   static_assert(kDynamic <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
+  static_assert(!SINGLE || STAGES * kStageBytes >= 16 * 4096, "single-tile form: sixteen staging tiles over the operand stages");
 };
 
 __device__ __forceinline__ void record_failure(int *status, int code) {
@@ -102,43 +123,96 @@ __device__ __forceinline__ void stage_row_f32(uint8_t *tile, int lane, const flo
   }
 }
 
+// Bring-up builds (-DWTC_BRINGUP) stamp the phases of each CTA's first tile; the default
+// build carries no stamps.
+#ifdef WTC_BRINGUP
 __device__ __forceinline__ void stamp(long long *timeline, int slot) {
-  if (timeline) timeline[static_cast<size_t>(blockIdx.x) * 16 + slot] = static_cast<long long>(globaltimer_ns());
+  if (timeline) {
+    long long *t = timeline + static_cast<size_t>(blockIdx.x) * 48;
+    t[slot] = static_cast<long long>(globaltimer_ns());
+    t[24 + slot] = clock64();
+  }
+}
+#define WTC_STAMP(p, slot) stamp((p).timeline, slot)
+#else
+#define WTC_STAMP(p, slot) ((void)0)
+#endif
+// stamp slots
+enum : int { TS_ENTRY = 0, TS_SETUP = 1, TS_DEPS = 2, TS_TMA0 = 3, TS_FULL0 = 4, TS_MMA_DONE = 5, TS_ACCUM = 6, TS_EXP = 7,
+             TS_STATS = 8, TS_STAGED = 9, TS_STORED = 10, TS_EXIT = 11, TS_LOADED = 12, TS_MAX = 13, TS_TEARDOWN = 14, TS_CLSYNC = 15, TS_MMA_READY = 16, TS_PACKED = 17, TS_PRODUCER_END = 18 };
+
+// ---- extreme of 32 raw accumulators folded into four running chains ----
+template <bool POS>
+__device__ __forceinline__ void fold_extreme(const uint32_t (&v)[32], float &m0, float &m1, float &m2, float &m3) {
+#pragma unroll
+  for (int i = 0; i < 32; i += 8) {
+    if (POS) {
+      m0 = max3(m0, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+      m1 = max3(m1, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+      m2 = max3(m2, __uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+      m3 = max3(m3, __uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+    } else {
+      m0 = min3(m0, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+      m1 = min3(m1, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+      m2 = min3(m2, __uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+      m3 = min3(m3, __uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+    }
+  }
 }
 
-// Second stamp layout (timeline_mode 1): four points of the first four tiles one thread sees.
-__device__ __forceinline__ void stamp_tile(const TcParams &p, int seq, int k) {
-  if (p.timeline && p.timeline_mode == 1 && seq < 4) stamp(p.timeline, seq * 4 + k);
-  if (p.timeline && p.timeline_mode == 3 && seq >= 20 && seq < 24) stamp(p.timeline, (seq - 20) * 4 + k);   // same, steady state
-}
-// Third layout (timeline_mode 2): eight points of the second and third tile one thread sees.
-__device__ __forceinline__ void stamp_fine(const TcParams &p, int seq, int k) {
-  if (p.timeline && p.timeline_mode == 2 && (seq == 1 || seq == 2)) stamp(p.timeline, (seq - 1) * 8 + k);
+// max (scale >= 0) or min (scale < 0) of a thread's NCH x 32 raw accumulators of which the
+// first `valid` exist, times c2: the row share's largest logit in the log2 domain
+template <int NCH>
+__device__ __forceinline__ float share_extreme(const uint32_t (&r)[NCH][32], int valid, float c2) {
+  const bool pos = c2 >= 0.f;
+  if (valid == NCH * 32) {
+    float m0 = __uint_as_float(r[0][0]), m1 = __uint_as_float(r[0][1]);
+    float m2 = __uint_as_float(r[0][2]), m3 = __uint_as_float(r[0][3]);
+    if (pos) {
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) fold_extreme<true>(r[c], m0, m1, m2, m3);
+      return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * c2;
+    }
+#pragma unroll
+    for (int c = 0; c < NCH; ++c) fold_extreme<false>(r[c], m0, m1, m2, m3);
+    return fminf(fminf(m0, m1), fminf(m2, m3)) * c2;
+  }
+  if (valid <= 0) return -INFINITY;
+  float m = __uint_as_float(r[0][0]);
+#pragma unroll
+  for (int c = 0; c < NCH; ++c)
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (c * 32 + i < valid) m = pos ? fmaxf(m, __uint_as_float(r[c][i])) : fminf(m, __uint_as_float(r[c][i]));
+  return m * c2;
 }
 
-template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool RELAY, bool PAIR, int EW, bool OUT32 = false, bool SINGLE = false>
-__global__ void __launch_bounds__(kThreadsFor(EW, RELAY), 1)
+// 32 values times f, rounded to f16 pairs
+__device__ __forceinline__ void scale_pack(const uint32_t (&r)[32], float f, uint32_t (&h)[16]) {
+#pragma unroll
+  for (int i = 0; i < 32; i += 2) h[i >> 1] = pack_f16x2(__uint_as_float(r[i]) * f, __uint_as_float(r[i + 1]) * f);
+}
+
+template <int BN, int STAGES, bool CLUSTER, int EPI, bool PAIR, bool OUT32>
+__global__ void __launch_bounds__(kThreadsFor(EPI), 1)
 fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmO, const TcParams p) {
-  using L = SmemLayout<BN, STAGES, CLUSTER, OUT_TILES, RELAY, PAIR, EW, OUT32, SINGLE>;
+  using L = SmemLayout<BN, STAGES, CLUSTER, EPI, PAIR, OUT32>;
+  constexpr bool RELAY = L::RELAY;
+  constexpr bool SINGLE = L::SINGLE;
+  constexpr int OUT_TILES = L::kOutTiles;
   constexpr int HC = L::kHalfCols;      // columns per epilogue thread
   constexpr int NCH = HC / 32;          // 32-column chunks per epilogue thread
-  constexpr int kEpiThreads = EW * 32;
-  constexpr int PARTS = BN / HC;        // threads that share a row (split epilogue)
-  static_assert(!RELAY || (EW == 16 && CLUSTER && !PAIR && OUT_TILES == 1 && !OUT32), "relay epilogue: cluster flavour, f16 staged stores, sixteen warps");
-  // SINGLE: every CTA owns exactly one tile (the launcher checks it).  Nothing can overlap with a
-  // next tile then, so the exp group keeps the first 64 columns of its share in registers and
-  // writes them out itself, through staging tiles laid over the operand stages (idle once the
-  // tile's accumulator is complete); the store group takes only the last 64 columns.
-  static_assert(!SINGLE || (RELAY && STAGES * L::kStageBytes >= 8 * 4096), "single-tile form: relay only");
-  static_assert(!OUT32 || (!RELAY && !PAIR && EW == 8 && OUT_TILES >= 1), "f32 output: the eight-warp split epilogue with staged stores");
-  static_assert(EW == 8 || (CLUSTER && OUT_TILES == 1 && !PAIR), "sixteen epilogue warps: cluster flavour with staged stores only");
+  constexpr int kEpiThreads = (RELAY || SINGLE) ? 512 : 256;
+  static_assert(!(RELAY || SINGLE) || (CLUSTER && !PAIR && !OUT32 && BN == 256), "sixteen-warp epilogues: cluster flavour, 256-column tiles, f16 staged stores");
+  static_assert(!OUT32 || !PAIR, "f32 output: unpaired CTAs");
+  static_assert(!PAIR || !CLUSTER, "CTA pairs: tiled flavour only");
   // The 128-byte swizzle needs the stage buffers on 1024-byte boundaries.  There is no
   // static shared memory in this kernel, so the dynamic window starts aligned; if it ever
   // does not, every thread leaves before any barrier or TMEM state exists.
   extern __shared__ __align__(1024) uint8_t smem[];
   // the first TMA instruction waits for its descriptor: ask for all three before anything else
-  if (threadIdx.x == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); tma_prefetch_desc(&tmO); }
+  if (threadIdx.x == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); tma_prefetch_desc(&tmO); WTC_STAMP(p, TS_ENTRY); }
   if ((smem_u32(smem) & 1023u) != 0) { record_failure(p.status, WTC_DEV_BAD_SMEM_ALIGN); return; }
 
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + L::kOffBars);
@@ -147,52 +221,25 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   uint64_t *accum_full = bars + 2 * STAGES;
   uint64_t *accum_empty = bars + 2 * STAGES + 2;
   uint64_t *stats_bar = bars + 2 * STAGES + 4;
-  uint64_t *xdone = bars + 2 * STAGES + 8;                         // relay: first group -> second group, per accumulator buffer
+  uint64_t *xdone = bars + 2 * STAGES + 8;                         // relay: exp group -> store group, per accumulator buffer
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + L::kOffTmemSlot);
   float2 *pair = reinterpret_cast<float2 *>(smem + L::kOffPair);    // [2][BM]
-  float2 *stats = reinterpret_cast<float2 *>(smem + L::kOffStats);  // [2][kMaxCluster][BM]
+  float2 *stats = reinterpret_cast<float2 *>(smem + L::kOffStats);  // [sets][kMaxCluster][BM]
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  // Cluster geometry.  PAIR: ranks 2j and 2j+1 form one tcgen05 CTA pair (256 rows x BN
-  // columns; the even CTA issues the MMAs); j is the column block.  The CTAs that swap row
-  // statistics are the ones with the same rows: same parity when paired.
+  // Cluster geometry.  PAIR: ranks 0 and 1 form one tcgen05 CTA pair (256 rows x BN
+  // columns; the even CTA issues the MMAs).
   constexpr bool CLUSTERED = CLUSTER || PAIR;
   const uint32_t cta_rank = CLUSTERED ? cluster_ctarank() : 0u;
   const uint32_t cluster_size = CLUSTERED ? cluster_nctarank() : 1u;
   const uint32_t pair_rank = PAIR ? (cta_rank & 1u) : 0u;
   const uint32_t leader_rank = PAIR ? (cta_rank & ~1u) : cta_rank;
   const bool is_leader = pair_rank == 0;
-  const uint32_t col_rank = PAIR ? (cta_rank >> 1) : cta_rank;               // my column block inside the cluster
-  const uint32_t cluster_n = CLUSTER ? (PAIR ? cluster_size / 2 : cluster_size) : 1u;   // CTAs that share my rows
+  const uint32_t col_rank = cta_rank;                                // my column block inside the cluster (cluster flavour)
+  const uint32_t cluster_n = CLUSTER ? cluster_size : 1u;           // CTAs that share my rows
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&accum_full[i], 1);
-      mbar_init(&accum_empty[i], (RELAY ? kEpiThreads / 2 : kEpiThreads) * (PAIR ? 2 : 1));
-      mbar_init(&xdone[i], kEpiThreads / 2);
-    }
-    for (int i = 0; i < 4; ++i) mbar_init(&stats_bar[i], 1);
-    mbar_fence_init();
-  }
-  if (warp == 1) {
-    if (PAIR) { tmem_alloc_pair(tmem_slot, 2 * BN); tmem_relinquish_pair(); }
-    else { tmem_alloc(tmem_slot, 2 * BN); tmem_relinquish(); }
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_slot;
-  if (CLUSTERED) cluster_sync_all();   // every peer's barriers exist before anyone signals them
-  // Programmatic dependent launch: everything above overlapped the tail of the previous
-  // kernel on the stream; from here on global memory is touched, so wait for that kernel
-  // to finish, and let the next one start its own set-up as our CTAs retire.
-  grid_dependency_wait();
-  grid_launch_dependents();
-  if (threadIdx.x == 64 && p.timeline_mode == 0) stamp(p.timeline, 0);
-
-  // ---- work distribution --------------------------------------------------
+  // ---- work distribution (needs nothing but special registers and parameters) ----
   int first, stride;
   if (CLUSTERED) { first = blockIdx.x / cluster_size; stride = gridDim.x / cluster_size; }
   else { first = blockIdx.x; stride = gridDim.x; }
@@ -218,13 +265,98 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     rb = PAIR ? ru * 2 + static_cast<int>(pair_rank) : ru;
   };
 
-  // hands accumulator buffer `ab` back to the MMA warp (of the pair's even CTA)
+  // one K block of operands into stage s (unpaired CTAs)
+  auto load_stage = [&](uint32_t s, int kb, int rb, int nb, int b, int bb) {
+    uint8_t *sa = smem + s * L::kStageBytes;
+    uint8_t *sb = sa + L::kABytes;
+    mbar_expect_tx(&full[s], L::kStageBytes);
+    tma_load_3d(sa, &tmA, &full[s], kb * BK, rb * BM, b);
+#pragma unroll
+    for (int j = 0; j < BN / 64; ++j)
+      tma_load_3d(sb + j * (BK * 128), &tmB, &full[s], nb * BN + j * 64, kb * BK, bb);
+  };
+
+  // ---- set-up.  Warp 0 creates the barriers and requests the first stages of the first tile on
+  // its own, while warp 1 allocates tensor memory: the loads' latency then runs under the rest of
+  // the set-up instead of after it.  (A CTA pair counts both CTAs' bytes on the even CTA's
+  // barrier, which must exist first: pairs start loading after the cluster barrier.)
+  const int early = PAIR ? 0 : (p.num_kb < STAGES ? p.num_kb : STAGES);
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+      for (int i = 0; i < 2; ++i) {
+        mbar_init(&accum_full[i], 1);
+        mbar_init(&accum_empty[i], (RELAY ? kEpiThreads / 2 : kEpiThreads) * (PAIR ? 2 : 1));   // relay: the store group hands it back
+        mbar_init(&xdone[i], kEpiThreads / 2);
+      }
+      for (int i = 0; i < 4; ++i) mbar_init(&stats_bar[i], 1);
+      mbar_fence_init();
+    }
+    __syncwarp();
+    if (!PAIR && first < p.num_items) {
+      int b, rb, nb; decode(first, b, rb, nb);
+      const int bb = p.b_batched ? b : 0;
+#ifndef WTC_EXP_NO_PREFETCH
+      if (CLUSTER) {
+        // Under programmatic dependent launch this CTA is resident a microsecond or two before
+        // the previous kernel on the stream is complete.  Shared memory may not be filled yet
+        // (the operands may be that kernel's output), but asking for them to be brought into L2
+        // is harmless, and turns the cold start of the pipeline into L2 hits.  The CTAs that
+        // share a panel split its K blocks: A[rb] among the cluster, B[nb] among the clusters;
+        // a lane per K block.
+        const int cl = static_cast<int>(cluster_n);
+        const int groups = stride < p.num_kb ? stride : p.num_kb;
+        for (int kb = lane; kb < p.num_kb; kb += 32) {
+          if (kb % cl == nb || kb < early) tma_prefetch_l2_3d(&tmA, kb * BK, rb * BM, b);
+          if (kb % groups == first % groups || kb < early) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_prefetch_l2_3d(&tmB, nb * BN + j * 64, kb * BK, bb);
+          }
+        }
+      }
+#endif
+      // programmatic dependent launch: the operands may be the previous kernel's output
+      grid_dependency_wait();
+      if (lane == 0)
+        for (int s = 0; s < early; ++s) mbar_expect_tx(&full[s], L::kStageBytes);
+      __syncwarp();
+      // one box per lane: box 0 of a stage is A's, the others are B's 64-column blocks
+      constexpr int kBoxes = 1 + BN / 64;
+      for (int t = lane; t < early * kBoxes; t += 32) {
+        const int st = t / kBoxes, j = t - st * kBoxes;
+        uint8_t *sa = smem + st * L::kStageBytes;
+        if (j == 0) tma_load_3d(sa, &tmA, &full[st], st * BK, rb * BM, b);
+        else tma_load_3d(sa + L::kABytes + (j - 1) * (BK * 128), &tmB, &full[st], nb * BN + (j - 1) * 64, st * BK, bb);
+      }
+      if (lane == 0) WTC_STAMP(p, TS_TMA0);
+    }
+  }
+  if (warp == 1) {
+    if (PAIR) { tmem_alloc_pair(tmem_slot, 2 * BN); tmem_relinquish_pair(); }
+    else { tmem_alloc(tmem_slot, 2 * BN); tmem_relinquish(); }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  // Every peer's barriers must exist before anyone signals them.  A CTA pair signals from its
+  // main loop, so it completes the cluster barrier here; the cluster flavour signals only from
+  // the epilogue (row statistics), so its threads arrive now and wait where they first need it.
+  if (CLUSTERED) cluster_arrive_release();
+  if (PAIR) cluster_wait_acquire();
+  if (threadIdx.x == 0) WTC_STAMP(p, TS_SETUP);
+  // Programmatic dependent launch: everything above overlapped the tail of the previous
+  // kernel on the stream; from here on global memory is touched, so wait for that kernel
+  // to finish, and let the next one start its own set-up as our CTAs retire.
+  grid_dependency_wait();
+  grid_launch_dependents();
+  if (threadIdx.x == 0) WTC_STAMP(p, TS_DEPS);
+
+  // hands accumulator buffer `ab` back to the MMA thread (of the pair's even CTA)
   auto release_accumulator = [&](int ab) {
     if (PAIR) mbar_arrive_remote_release(map_to_cta(smem_u32(&accum_empty[ab]), leader_rank));
     else mbar_arrive(&accum_empty[ab]);
   };
-  // cluster rank of the j-th CTA that holds the same rows as this one
-  auto row_peer = [&](uint32_t j) -> uint32_t { return PAIR ? 2 * j + pair_rank : j; };
 
   // (row max, 1 / row sum) from the pairs the CTAs of the cluster sent for statistics set
   // `set`: all loads first, then a max tree, independent exps, a sum tree.
@@ -244,8 +376,11 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   // group needs a whole row share (128 values) in registers, the others need little; each
   // role's code sits under its own reallocation so the allocator sees one budget per region.
   const int relay_role = !RELAY ? 0 : (warp < 4 ? 0 : (warp < 12 ? 1 : 2));
+  bool cluster_waited = PAIR;     // this thread has completed the set-up's cluster barrier
   if (RELAY && relay_role == 1) {
-    setmaxnreg_inc<SINGLE ? 160 : 152>();
+    setmaxnreg_inc<152>();
+    cluster_wait_acquire();
+    cluster_waited = true;
     // ======================= softmax epilogue, two-stage relay ==============
     // Two groups of eight epilogue warps work on consecutive tiles at the same time.  The
     // first group (warps 4-11, 152 registers a thread after the reallocation above) turns
@@ -258,7 +393,6 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const int q = warp & 3;                       // TMEM lane quarter this warp may touch
     const int row_in_tile = q * 32 + lane;
     const float c2 = p.c2;
-    const bool pos = c2 >= 0.f;
     float *mh = reinterpret_cast<float *>(smem + L::kOffMh);   // [2][2][BM]: each half's own maximum, per tile parity
     // ---------------- first group: max, exp in place, statistics out ----------------
     const int half = (warp - 4) >> 2;
@@ -273,8 +407,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       const int sset = it & 3;
       if (!mbar_wait(&accum_full[ab], tile_phase)) { record_failure(p.status, WTC_DEV_TIMEOUT_ACCUM); break; }
       tc_fence_after_sync();
-      if (stamper && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 1);
-      if (stamper) { stamp_tile(p, it, 0); stamp_fine(p, it, 0); }
+      if (stamper && it == 0) WTC_STAMP(p, TS_ACCUM);
       const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ab * BN + half * HC;
       const int col0 = nb * BN + half * HC;
       const int valid = max(0, min(HC, p.N - col0));
@@ -283,35 +416,28 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       if (valid == HC && !p.round_logits_f16) {
         // whole share, no rounding: the second half of the loads is in flight while the
         // extreme of the first half is taken
-        float m0, m1, m2, m3;
-        auto fold = [&](const uint32_t (&v)[32]) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            if (pos) {
-              m0 = max3(m0, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
-              m1 = max3(m1, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
-              m2 = max3(m2, __uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
-              m3 = max3(m3, __uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
-            } else {
-              m0 = min3(m0, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
-              m1 = min3(m1, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
-              m2 = min3(m2, __uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
-              m3 = min3(m3, __uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
-            }
-          }
-        };
+        const bool pos = c2 >= 0.f;
 #pragma unroll
         for (int c = 0; c < NCH / 2; ++c) tmem_ld_32x32b_x32(tbase + c * 32, r[c]);
         tmem_ld_wait();
 #pragma unroll
         for (int c = NCH / 2; c < NCH; ++c) tmem_ld_32x32b_x32(tbase + c * 32, r[c]);
-        m0 = __uint_as_float(r[0][0]); m1 = __uint_as_float(r[0][1]); m2 = __uint_as_float(r[0][2]); m3 = __uint_as_float(r[0][3]);
+        float m0 = __uint_as_float(r[0][0]), m1 = __uint_as_float(r[0][1]), m2 = __uint_as_float(r[0][2]), m3 = __uint_as_float(r[0][3]);
+        if (pos) {
 #pragma unroll
-        for (int c = 0; c < NCH / 2; ++c) fold(r[c]);
+          for (int c = 0; c < NCH / 2; ++c) fold_extreme<true>(r[c], m0, m1, m2, m3);
+        } else {
+#pragma unroll
+          for (int c = 0; c < NCH / 2; ++c) fold_extreme<false>(r[c], m0, m1, m2, m3);
+        }
         tmem_ld_wait();
-        if (stamper) stamp_fine(p, it, 1);
+        if (pos) {
 #pragma unroll
-        for (int c = NCH / 2; c < NCH; ++c) fold(r[c]);
+          for (int c = NCH / 2; c < NCH; ++c) fold_extreme<true>(r[c], m0, m1, m2, m3);
+        } else {
+#pragma unroll
+          for (int c = NCH / 2; c < NCH; ++c) fold_extreme<false>(r[c], m0, m1, m2, m3);
+        }
         m_half = (pos ? fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) : fminf(fminf(m0, m1), fminf(m2, m3))) * c2;
       } else {
 #pragma unroll
@@ -323,62 +449,19 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           }
         }
         tmem_ld_wait();
-        if (stamper) stamp_fine(p, it, 1);
         if (p.round_logits_f16) {
 #pragma unroll
           for (int c = 0; c < NCH; ++c)
 #pragma unroll
             for (int i = 0; i < 32; ++i) r[c][i] = __float_as_uint(__half2float(__float2half_rn(__uint_as_float(r[c][i]))));
         }
-        // ---- extreme of the raw accumulators (max if scale >= 0, else min), four chains ----
-        if (valid == HC) {
-          float m0 = __uint_as_float(r[0][0]), m1 = __uint_as_float(r[0][1]);
-          float m2 = __uint_as_float(r[0][2]), m3 = __uint_as_float(r[0][3]);
-          if (pos) {
-#pragma unroll
-            for (int c = 0; c < NCH; ++c)
-#pragma unroll
-              for (int i = 0; i < 32; i += 8) {
-                m0 = max3(m0, __uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1]));
-                m1 = max3(m1, __uint_as_float(r[c][i + 2]), __uint_as_float(r[c][i + 3]));
-                m2 = max3(m2, __uint_as_float(r[c][i + 4]), __uint_as_float(r[c][i + 5]));
-                m3 = max3(m3, __uint_as_float(r[c][i + 6]), __uint_as_float(r[c][i + 7]));
-              }
-            m_half = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
-          } else {
-#pragma unroll
-            for (int c = 0; c < NCH; ++c)
-#pragma unroll
-              for (int i = 0; i < 32; i += 8) {
-                m0 = min3(m0, __uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1]));
-                m1 = min3(m1, __uint_as_float(r[c][i + 2]), __uint_as_float(r[c][i + 3]));
-                m2 = min3(m2, __uint_as_float(r[c][i + 4]), __uint_as_float(r[c][i + 5]));
-                m3 = min3(m3, __uint_as_float(r[c][i + 6]), __uint_as_float(r[c][i + 7]));
-              }
-            m_half = fminf(fminf(m0, m1), fminf(m2, m3));
-          }
-          m_half *= c2;
-        } else if (valid > 0) {
-          float m = __uint_as_float(r[0][0]);
-#pragma unroll
-          for (int c = 0; c < NCH; ++c)
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (c * 32 + i < valid) m = pos ? fmaxf(m, __uint_as_float(r[c][i])) : fminf(m, __uint_as_float(r[c][i]));
-          m_half = m * c2;
-        } else {
-          m_half = -INFINITY;
-        }
+        m_half = share_extreme<NCH>(r, valid, c2);
       }
-      if (stamper) stamp_fine(p, it, 2);
       // ---- e = 2^(v - m_half) in place, row sum; each chunk goes back over its logits ----
       float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
       if (valid == HC) {
-        // (single-tile form: the chunks that go to tensor memory first, so their registers are
-        // free while the two chunks this thread keeps are processed and held)
 #pragma unroll
-        for (int k = 0; k < NCH; ++k) {
-          const int c = SINGLE ? (k + 2) % NCH : k;
+        for (int c = 0; c < NCH; ++c) {
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
             const float e0 = ex2_approx(fmaf(__uint_as_float(r[c][i]), c2, -m_half));
@@ -389,12 +472,11 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             r[c][i] = __float_as_uint(e0); r[c][i + 1] = __float_as_uint(e1);
             r[c][i + 2] = __float_as_uint(e2); r[c][i + 3] = __float_as_uint(e3);
           }
-          if (!(SINGLE && c < 2)) tmem_st_32x32b_x32(tbase + c * 32, r[c]);
+          tmem_st_32x32b_x32(tbase + c * 32, r[c]);
         }
       } else {
 #pragma unroll
-        for (int k = 0; k < NCH; ++k) {
-          const int c = SINGLE ? (k + 2) % NCH : k;
+        for (int c = 0; c < NCH; ++c) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             float e = 0.f;
@@ -402,12 +484,11 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             s0 += e;
             r[c][i] = __float_as_uint(e);
           }
-          if (c * 32 < valid && !(SINGLE && c < 2)) tmem_st_32x32b_x32(tbase + c * 32, r[c]);
+          if (c * 32 < valid) tmem_st_32x32b_x32(tbase + c * 32, r[c]);
         }
       }
       const float sum = (s0 + s1) + (s2 + s3);
-      if (stamper && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 2);
-      if (stamper) { stamp_tile(p, it, 1); stamp_fine(p, it, 3); }
+      if (stamper && it == 0) WTC_STAMP(p, TS_EXP);
       // ---- the two halves of a row meet through shared memory, the CTAs through the cluster ----
       *mine = make_float2(m_half, sum);
       mh[((it & 1) * 2 + half) * BM + row_in_tile] = m_half;
@@ -421,52 +502,16 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const uint32_t slot = smem_u32(&stats[(sset * kMaxCluster + col_rank) * BM + row_in_tile]);
         const uint32_t bar = smem_u32(&stats_bar[sset]);
         for (uint32_t peer = 0; peer < cluster_n; ++peer)
-          st_async_f32x2(map_to_cta(slot, row_peer(peer)), lm, ll, map_to_cta(bar, row_peer(peer)));
+          st_async_f32x2(map_to_cta(slot, peer), lm, ll, map_to_cta(bar, peer));
       }
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(&xdone[ab]);                    // exp values parked, maxima published
-      if (stamper) stamp_tile(p, it, 2);
-      if (SINGLE && valid > 0) {
-        // ---- single-tile form: this thread scales, packs and stores its first 64 columns itself ----
-        if (!mbar_wait_cluster(&stats_bar[sset], 0)) { record_failure(p.status, WTC_DEV_TIMEOUT_STATS); break; }
-        float gm, inv_gl;
-        {
-          float xs[kMaxCluster];
-#pragma unroll
-          for (int j = 0; j < kMaxCluster; ++j)
-            xs[j] = static_cast<uint32_t>(j) < cluster_n ? stats[(sset * kMaxCluster + j) * BM + row_in_tile].x : -INFINITY;
-          gm = fmaxf(fmaxf(max3(xs[0], xs[1], xs[2]), max3(xs[3], xs[4], xs[5])), fmaxf(xs[6], xs[7]));
-          float l = 0.f;
-#pragma unroll
-          for (int j = 0; j < kMaxCluster; ++j)
-            if (static_cast<uint32_t>(j) < cluster_n) l += stats[(sset * kMaxCluster + j) * BM + row_in_tile].y * ex2_approx(xs[j] - gm);
-          inv_gl = rcp_approx(l);
-        }
-        const float f = ex2_approx(m_half - gm) * inv_gl;
-        uint8_t *xstg = smem + (warp - 4) * 4096;   // over operand stage 0: every stage has been consumed
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t hc[16];
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const __half2 hh = __floats2half2_rn(__uint_as_float(r[c][i]) * f, __uint_as_float(r[c][i + 1]) * f);
-            hc[i >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
-          }
-          stage_row_chunk(xstg, lane, c, hc);       // (columns past `valid` hold zeros: e was 0 there)
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          const int row0 = rb * BM + q * 32;
-          if (row0 < p.M) tma_store_3d(&tmO, xstg, col0, row0, b);
-          tma_store_commit();
-          tma_store_wait_all();
-        }
-      }
     }
   } else if (RELAY && relay_role == 2) {
-    setmaxnreg_dec<SINGLE ? 56 : 64>();
+    setmaxnreg_dec<64>();
+    cluster_wait_acquire();
+    cluster_waited = true;
     const int q = warp & 3;                       // TMEM lane quarter this warp may touch
     const int row_in_tile = q * 32 + lane;
     float *mh = reinterpret_cast<float *>(smem + L::kOffMh);   // [2][2][BM]: each half's own maximum, per tile parity
@@ -483,10 +528,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       if (lead) mbar_expect_tx(&stats_bar[sset], cluster_n * BM * 8);
       if (!mbar_wait(&xdone[ab], tile_phase)) { record_failure(p.status, WTC_DEV_TIMEOUT_ACCUM); break; }
       tc_fence_after_sync();
-      if (lead) stamp_fine(p, it, 4);
       if (!mbar_wait_cluster(&stats_bar[sset], (it >> 2) & 1)) { record_failure(p.status, WTC_DEV_TIMEOUT_STATS); break; }
-      if (lead && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 3);
-      if (lead) stamp_fine(p, it, 5);
       float gm, inv_gl;
       combine_cluster_stats(sset, row_in_tile, gm, inv_gl);
       const float f = ex2_approx(mh[((it & 1) * 2 + half) * BM + row_in_tile] - gm) * inv_gl;
@@ -497,17 +539,16 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       const bool rows_live = row0 < p.M;
       // 32 columns at a time through one register buffer (the scheduler's other warps cover
       // the load latency).  The first 64 columns are staged as they are packed, the last 64
-      // wait packed in registers, so the accumulator buffer goes back to the MMA warp after
+      // wait packed in registers, so the accumulator buffer goes back to the MMA thread after
       // the fourth load and before anything waits for a store.
       static_assert(!RELAY || NCH == 4, "relay epilogue: a thread owns 128 columns");
-      if (valid == 0 || (SINGLE && valid <= 64)) { tc_fence_before_sync(); release_accumulator(ab); }
+      if (valid == 0) { tc_fence_before_sync(); release_accumulator(ab); }
       if (lane == 0) tma_store_wait_read();         // the previous tile's store has read the staging tile
       __syncwarp();
       uint32_t h[2][16];
 #pragma unroll
       for (int c = 0; c < NCH; ++c) {
         uint32_t hc[16];
-        if (SINGLE && c < 2) continue;                // the exp group writes these columns itself
         if (c * 32 < valid) {
           uint32_t r[32];
           tmem_ld_32x32b_x32(tbase + c * 32, r);
@@ -516,22 +557,18 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             tc_fence_before_sync();
             release_accumulator(ab);
           }
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const __half2 hh = __floats2half2_rn(__uint_as_float(r[i]) * f, __uint_as_float(r[i + 1]) * f);
-            hc[i >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
-          }
+          scale_pack(r, f, hc);
         } else {
 #pragma unroll
           for (int i = 0; i < 16; ++i) hc[i] = 0u;
         }
-        if (c < 2 || SINGLE) stage_row_chunk(stg, lane, c & 1, hc);   // single-tile form: nothing in flight, stage straight away
+        if (c < 2) stage_row_chunk(stg, lane, c & 1, hc);
         else {
 #pragma unroll
           for (int i = 0; i < 16; ++i) h[c - 2][i] = hc[i];
         }
       }
-      if (valid > 0 && !SINGLE) {
+      if (valid > 0) {
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
@@ -540,12 +577,10 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
       }
       if (valid > 64) {
-        if (!SINGLE) {
-          if (lane == 0) tma_store_wait_read();
-          __syncwarp();
-          stage_row_chunk(stg, lane, 0, h[0]);
-          stage_row_chunk(stg, lane, 1, h[1]);
-        }
+        if (lane == 0) tma_store_wait_read();
+        __syncwarp();
+        stage_row_chunk(stg, lane, 0, h[0]);
+        stage_row_chunk(stg, lane, 1, h[1]);
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
@@ -553,99 +588,219 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           tma_store_commit();
         }
       }
-      if (lead && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 4);
-      if (lead) { stamp_tile(p, it, 3); stamp_fine(p, it, 7); }
+      if (lead && it == 0) WTC_STAMP(p, TS_STAGED);
     }
-    if (lane == 0) tma_store_wait_all();
-    if (lead && p.timeline_mode == 0) stamp(p.timeline, 5);
-    
+    if (lane == 0) tma_store_wait_read();
+  } else if (SINGLE && warp >= 2) {
+    // ======================= softmax epilogue, sixteen warps, one tile per CTA ==============
+    // Thread = one row x a quarter (64) of the tile's columns: TMEM lane quarter = warp_id % 4,
+    // column quarter = (warp_id - 2) / 4.  Everything stays in registers between the TMEM load
+    // and the staging tile; with four warps per scheduler the exponentials of the whole tile
+    // run at the special-function unit's rate, and all sixteen warps share the store phase.
+    cluster_wait_acquire();
+    cluster_waited = true;
+    const int q = warp & 3;
+    const int part = (warp - 2) >> 2;
+    const int row_in_tile = q * 32 + lane;
+    const bool lead = threadIdx.x == 64;
+    const float c2 = p.c2;
+    if (first < p.num_items) {
+      int b, rb, nb; decode(first, b, rb, nb);
+      if (lead) mbar_expect_tx(&stats_bar[0], cluster_n * BM * 8);
+      if (!mbar_wait(&accum_full[0], 0)) record_failure(p.status, WTC_DEV_TIMEOUT_ACCUM);
+      else {
+        tc_fence_after_sync();
+        if (lead) WTC_STAMP(p, TS_ACCUM);
+        const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + part * HC;
+        const int col0 = nb * BN + part * HC;
+        const int valid = max(0, min(HC, p.N - col0));
+        const int row0 = rb * BM + q * 32;
+        uint32_t r[NCH][32];
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+          if (c * 32 < valid) tmem_ld_32x32b_x32(tbase + c * 32, r[c]);
+          else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[c][i] = 0u;
+          }
+        }
+        tmem_ld_wait();
+        if (lead) WTC_STAMP(p, TS_LOADED);
+        if (p.round_logits_f16) {
+#pragma unroll
+          for (int c = 0; c < NCH; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[c][i] = __float_as_uint(__half2float(__float2half_rn(__uint_as_float(r[c][i]))));
+        }
+        const float m_part = share_extreme<NCH>(r, valid, c2);
+        if (lead) WTC_STAMP(p, TS_MAX);
+        // ---- e = 2^(v - m_part) in place, row sum ----
+        float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+        if (valid == HC) {
+#pragma unroll
+          for (int c = 0; c < NCH; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              const float e0 = ex2_approx(fmaf(__uint_as_float(r[c][i]), c2, -m_part));
+              const float e1 = ex2_approx(fmaf(__uint_as_float(r[c][i + 1]), c2, -m_part));
+              const float e2 = ex2_approx(fmaf(__uint_as_float(r[c][i + 2]), c2, -m_part));
+              const float e3 = ex2_approx(fmaf(__uint_as_float(r[c][i + 3]), c2, -m_part));
+              s0 += e0; s1 += e1; s2 += e2; s3 += e3;
+              r[c][i] = __float_as_uint(e0); r[c][i + 1] = __float_as_uint(e1);
+              r[c][i + 2] = __float_as_uint(e2); r[c][i + 3] = __float_as_uint(e3);
+            }
+        } else {
+#pragma unroll
+          for (int c = 0; c < NCH; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              float e = 0.f;
+              if (c * 32 + i < valid) e = ex2_approx(fmaf(__uint_as_float(r[c][i]), c2, -m_part));
+              s0 += e;
+              r[c][i] = __float_as_uint(e);
+            }
+        }
+        const float sum = (s0 + s1) + (s2 + s3);
+        if (lead) WTC_STAMP(p, TS_EXP);
+        // ---- the four quarters of a row meet through shared memory, the CTAs through the cluster ----
+        pair[part * BM + row_in_tile] = make_float2(m_part, sum);
+        named_bar_sync(1 + q, 128);
+        float2 pq[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) pq[j] = pair[j * BM + row_in_tile];
+        const float lm = fmaxf(fmaxf(pq[0].x, pq[1].x), fmaxf(pq[2].x, pq[3].x));
+        if (part == 0) {
+          float ll = 0.f;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) ll += pq[j].x == -INFINITY ? 0.f : pq[j].y * ex2_approx(pq[j].x - lm);
+          const uint32_t slot = smem_u32(&stats[col_rank * BM + row_in_tile]);
+          const uint32_t bar = smem_u32(&stats_bar[0]);
+          for (uint32_t peer = 0; peer < cluster_n; ++peer)
+            st_async_f32x2(map_to_cta(slot, peer), lm, ll, map_to_cta(bar, peer));
+        }
+        if (!mbar_wait_cluster(&stats_bar[0], 0)) record_failure(p.status, WTC_DEV_TIMEOUT_STATS);
+        else {
+          if (lead) WTC_STAMP(p, TS_STATS);
+          float gm, inv_gl;
+          combine_cluster_stats(0, row_in_tile, gm, inv_gl);
+          const float f = ex2_approx(m_part - gm) * inv_gl;
+          // ---- p = e * f -> f16 -> this warp's staging tile (over the idle operand stages) -> one TMA store ----
+          uint8_t *stg = smem + (warp - 2) * 4096;
+#pragma unroll
+          for (int c = 0; c < NCH; ++c) {
+            uint32_t h[16];
+            scale_pack(r[c], f, h);                  // (columns past `valid` hold zeros: e was 0 there)
+            stage_row_chunk(stg, lane, c, h);
+          }
+          if (lead) WTC_STAMP(p, TS_PACKED);
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+#ifdef WTC_EXP_EVICT_FIRST
+            if (valid > 0 && row0 < p.M) tma_store_3d_hint(&tmO, stg, col0, row0, b, l2_policy_evict_first());
+#else
+            if (valid > 0 && row0 < p.M) tma_store_3d(&tmO, stg, col0, row0, b);
+#endif
+            tma_store_commit();
+            if (lead) WTC_STAMP(p, TS_STAGED);
+            tma_store_wait_read();
+          }
+          if (lead) WTC_STAMP(p, TS_STORED);
+        }
+      }
+    }
   } else {
-  if (RELAY) setmaxnreg_dec<SINGLE ? 40 : 48>();
+  if (RELAY) setmaxnreg_dec<48>();
   if (warp == 0) {
-    // ======================= TMA producer ==================================
-    uint32_t n = 0;
-    bool ok = true;
-    for (int w = first; w < p.num_items && ok; w += stride) {
-      int b, rb, nb; decode(w, b, rb, nb);
-      for (int kb = 0; kb < p.num_kb; ++kb, ++n) {
-        const int s = n % STAGES;
-        const uint32_t ph = (n / STAGES) & 1;
-        if (!mbar_wait(&empty[s], ph ^ 1)) { record_failure(p.status, WTC_DEV_TIMEOUT_EMPTY); ok = false; break; }
-        if (lane == 0) {
-          uint8_t *sa = smem + s * L::kStageBytes;
-          uint8_t *sb = sa + L::kABytes;
+    // ======================= TMA producer: one thread =======================
+    if (lane == 0) {
+      // (the first `early` stages of the first tile are already on their way)
+      uint32_t s = early == STAGES ? 0 : early, ph = early == STAGES ? 1 : 0;
+      bool ok = true;
+      for (int w = first; w < p.num_items && ok; w += stride) {
+        int b, rb, nb; decode(w, b, rb, nb);
+        const int bb = p.b_batched ? b : 0;
+        for (int kb = (w == first ? early : 0); kb < p.num_kb; ++kb) {
+          if (!mbar_wait(&empty[s], ph ^ 1)) { record_failure(p.status, WTC_DEV_TIMEOUT_EMPTY); ok = false; break; }
           if (PAIR) {
             // both CTAs of the pair fill their own stage; all bytes are counted on the even CTA's barrier
+            uint8_t *sa = smem + s * L::kStageBytes;
+            uint8_t *sb = sa + L::kABytes;
             if (is_leader) mbar_expect_tx(&full[s], 2 * L::kStageBytes);
             tma_load_3d_pair(sa, &tmA, &full[s], kb * BK, rb * BM, b);
 #pragma unroll
             for (int j = 0; j < BN / 128; ++j)
-              tma_load_3d_pair(sb + j * (BK * 128), &tmB, &full[s], nb * BN + static_cast<int>(pair_rank) * (BN / 2) + j * 64, kb * BK,
-                               p.b_batched ? b : 0);
+              tma_load_3d_pair(sb + j * (BK * 128), &tmB, &full[s], nb * BN + static_cast<int>(pair_rank) * (BN / 2) + j * 64, kb * BK, bb);
+            if (w == first && kb == 0) WTC_STAMP(p, TS_TMA0);
           } else {
-            mbar_expect_tx(&full[s], L::kStageBytes);
-            tma_load_3d(sa, &tmA, &full[s], kb * BK, rb * BM, b);
-#pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
-              tma_load_3d(sb + j * (BK * 128), &tmB, &full[s], nb * BN + j * 64, kb * BK, p.b_batched ? b : 0);
+            load_stage(s, kb, rb, nb, b, bb);
           }
-          if (n == 0 && p.timeline_mode == 0) stamp(p.timeline, 6);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
         }
-        __syncwarp();
       }
+      WTC_STAMP(p, TS_PRODUCER_END);
     }
+    __syncwarp();
   } else if (warp == 1) {
-    // ======================= MMA issuer (the even CTA of a pair only) =======
-    constexpr uint32_t idesc = umma_idesc_f16_f32(PAIR ? 2 * BM : BM, BN, /*a_mn_major=*/0, /*b_mn_major=*/1);
-    const uint16_t pair_mask = static_cast<uint16_t>(3u << leader_rank);
-    uint32_t n = 0;
-    int it = 0;
-    bool ok = true;
-    for (int w = first; w < p.num_items && ok && is_leader; w += stride, ++it) {
-      const int ab = it & 1;
-      if (!mbar_wait(&accum_empty[ab], ((it >> 1) & 1) ^ 1)) { record_failure(p.status, WTC_DEV_TIMEOUT_TMEM); ok = false; break; }
-      tc_fence_after_sync();
-      const uint32_t d_tmem = tmem_base + ab * BN;
-      for (int kb = 0; kb < p.num_kb; ++kb, ++n) {
-        const int s = n % STAGES;
-        const uint32_t ph = (n / STAGES) & 1;
-        if (!mbar_wait(&full[s], ph)) { record_failure(p.status, WTC_DEV_TIMEOUT_FULL); ok = false; break; }
+    // ======================= MMA issuer: one thread (of the even CTA of a pair) =======
+    if (is_leader && elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_f16_f32(PAIR ? 2 * BM : BM, BN, /*a_mn_major=*/0, /*b_mn_major=*/1);
+      const uint16_t pair_mask = static_cast<uint16_t>(3u << leader_rank);
+      // everything of the two operand descriptors but the address, which is added per stage
+      const uint64_t a_desc0 = umma_smem_desc_sw128(smem_u32(smem), kALbo, kASbo);
+      const uint64_t b_desc0 = umma_smem_desc_sw128(smem_u32(smem) + L::kABytes, kBLbo, kBSbo);
+      uint32_t s = 0, ph = 0;
+      uint32_t landed = 0;            // the next stage's barrier was already seen complete
+      WTC_STAMP(p, TS_MMA_READY);
+      int it = 0;
+      bool ok = true;
+      for (int w = first; w < p.num_items && ok; w += stride, ++it) {
+        const int ab = it & 1;
+        if (!mbar_wait(&accum_empty[ab], ((it >> 1) & 1) ^ 1)) { record_failure(p.status, WTC_DEV_TIMEOUT_TMEM); ok = false; break; }
         tc_fence_after_sync();
-        if (lane == 0) {
-          if (n == 0 && p.timeline_mode == 0) stamp(p.timeline, 7);
-          const uint32_t sa = smem_u32(smem + s * L::kStageBytes);
-          const uint32_t sb = sa + L::kABytes;
+        const uint32_t d_tmem = tmem_base + ab * BN;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!landed && !mbar_wait(&full[s], ph)) { record_failure(p.status, WTC_DEV_TIMEOUT_FULL); ok = false; break; }
+          tc_fence_after_sync();
+          if (it == 0 && kb == 0) WTC_STAMP(p, TS_FULL0);
+          uint64_t da = a_desc0 + ((s * L::kStageBytes) >> 4);
+          uint64_t db = b_desc0 + ((s * L::kStageBytes) >> 4);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
-            const uint64_t da = umma_smem_desc_sw128(sa + k * p.geom.a_kstep, p.geom.a_lbo, p.geom.a_sbo);
-            const uint64_t db = umma_smem_desc_sw128(sb + k * p.geom.b_kstep, p.geom.b_lbo, p.geom.b_sbo);
             if (PAIR) umma_f16_ss_pair(d_tmem, da, db, idesc, (kb | k) != 0);
             else umma_f16_ss(d_tmem, da, db, idesc, (kb | k) != 0);
+            da += kAKstep >> 4;
+            db += kBKstep >> 4;
           }
+          // while those MMAs drain: has the next stage landed already?  (The ring runs on
+          // across tiles, so "next" is the same barrier whichever tile it belongs to.)
+          const uint32_t s1 = s + 1 == STAGES ? 0 : s + 1;
+          const uint32_t ph1 = s1 == 0 ? ph ^ 1 : ph;
+          landed = mbar_try_wait(&full[s1], ph1);
           // frees the stage (in both CTAs of a pair) once these MMAs have read it
           if (PAIR) umma_commit_pair(&empty[s], pair_mask);
           else umma_commit(&empty[s]);
+          s = s1; ph = ph1;
         }
-        __syncwarp();
+        if (ok) {
+          if (PAIR) umma_commit_pair(&accum_full[ab], pair_mask);
+          else umma_commit(&accum_full[ab]);
+          if (it == 0) WTC_STAMP(p, TS_MMA_DONE);
+        }
       }
-      if (ok && lane == 0) {
-        if (PAIR) umma_commit_pair(&accum_full[ab], pair_mask);
-        else umma_commit(&accum_full[ab]);
-        if (it == 0 && p.timeline_mode == 0) stamp(p.timeline, 8);
-      }
-      __syncwarp();
     }
-  } else if (!RELAY) {
-    // ======================= softmax epilogue ==============================
+    __syncwarp();
+  } else if (!RELAY && !SINGLE) {
+    // ======================= softmax epilogue, eight warps ==================
+    if (CLUSTER) { cluster_wait_acquire(); cluster_waited = true; }
     const int q = warp & 3;                      // TMEM lane quarter this warp may read
-    const int half = (warp - 2) >> 2;            // which part (of PARTS) of the tile's columns
+    const int half = (warp - 2) >> 2;            // which half of the tile's columns
     const int row_in_tile = q * 32 + lane;
     const bool lead = threadIdx.x == 64;         // first epilogue thread: posts expect_tx, stamps
-    uint8_t *stg = smem + L::kOffOut + (warp - 2) * L::kOutWarpBytes;   // one 32-row x 64-col f16 tile
+    uint8_t *stg = smem + L::kOffOut + (warp - 2) * L::kOutWarpBytes;
     float2 *mine = &pair[half * BM + row_in_tile];
     const float2 *other = &pair[(half ^ 1) * BM + row_in_tile];
     const float c2 = p.c2;
-    const bool pos = c2 >= 0.f;
     int it = 0;
     uint32_t gcount = 0;                         // staging groups committed so far by this warp
     for (int w = first; w < p.num_items; w += stride, ++it) {
@@ -656,8 +811,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       if (CLUSTER && lead) mbar_expect_tx(&stats_bar[par], cluster_n * BM * 8);
       if (!mbar_wait(&accum_full[ab], tile_phase)) { record_failure(p.status, WTC_DEV_TIMEOUT_ACCUM); break; }
       tc_fence_after_sync();
-      if (lead && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 1);
-      if (lead) { stamp_tile(p, it, 0); stamp_fine(p, it, 0); }
+      if (lead && it == 0) WTC_STAMP(p, TS_ACCUM);
       const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ab * BN + half * HC;
       const int col0 = nb * BN + half * HC;               // first matrix column of this thread
       const int valid = max(0, min(HC, p.N - col0));      // my columns that exist
@@ -665,7 +819,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       const bool rows_live = row0 < p.M;
 
       // ---- the thread's whole share of the accumulator row goes to registers at once,
-      //      and the accumulator buffer is handed back to the MMA warp straight away ----
+      //      and the accumulator buffer is handed back to the MMA thread straight away ----
       uint32_t r[NCH][32];
 #pragma unroll
       for (int c = 0; c < NCH; ++c) {
@@ -678,58 +832,16 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       tmem_ld_wait();
       tc_fence_before_sync();
       release_accumulator(ab);
-      if (lead && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 14);
-      if (lead) stamp_fine(p, it, 1);
+      if (lead && it == 0) WTC_STAMP(p, TS_LOADED);
       if (p.round_logits_f16) {
 #pragma unroll
         for (int c = 0; c < NCH; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i) r[c][i] = __float_as_uint(__half2float(__float2half_rn(__uint_as_float(r[c][i]))));
       }
+      const float m_half = share_extreme<NCH>(r, valid, c2);
+      if (lead && it == 0) WTC_STAMP(p, TS_MAX);
 
-      // ---- extreme of the raw accumulators (max if scale >= 0, else min), four chains ----
-      float m_half;
-      if (valid == HC) {
-        float m0 = __uint_as_float(r[0][0]), m1 = __uint_as_float(r[0][1]);
-        float m2 = __uint_as_float(r[0][2]), m3 = __uint_as_float(r[0][3]);
-        if (pos) {
-#pragma unroll
-          for (int c = 0; c < NCH; ++c)
-#pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              m0 = max3(m0, __uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1]));
-              m1 = max3(m1, __uint_as_float(r[c][i + 2]), __uint_as_float(r[c][i + 3]));
-              m2 = max3(m2, __uint_as_float(r[c][i + 4]), __uint_as_float(r[c][i + 5]));
-              m3 = max3(m3, __uint_as_float(r[c][i + 6]), __uint_as_float(r[c][i + 7]));
-            }
-          m_half = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
-        } else {
-#pragma unroll
-          for (int c = 0; c < NCH; ++c)
-#pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              m0 = min3(m0, __uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1]));
-              m1 = min3(m1, __uint_as_float(r[c][i + 2]), __uint_as_float(r[c][i + 3]));
-              m2 = min3(m2, __uint_as_float(r[c][i + 4]), __uint_as_float(r[c][i + 5]));
-              m3 = min3(m3, __uint_as_float(r[c][i + 6]), __uint_as_float(r[c][i + 7]));
-            }
-          m_half = fminf(fminf(m0, m1), fminf(m2, m3));
-        }
-        m_half *= c2;
-      } else if (valid > 0) {
-        float m = __uint_as_float(r[0][0]);
-#pragma unroll
-        for (int c = 0; c < NCH; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (c * 32 + i < valid) m = pos ? fmaxf(m, __uint_as_float(r[c][i])) : fminf(m, __uint_as_float(r[c][i]));
-        m_half = m * c2;
-      } else {
-        m_half = -INFINITY;
-      }
-
-      if (lead && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 15);
-      if (lead) stamp_fine(p, it, 2);
       // ---- e = 2^(v - m_half) in place, row sum ----
       float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
       if (valid == HC) {
@@ -756,59 +868,28 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             r[c][i] = __float_as_uint(e);
           }
       }
-      float sum = (s0 + s1) + (s2 + s3);
-      if (lead && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 2);
-      if (lead) { stamp_tile(p, it, 1); stamp_fine(p, it, 3); }
+      const float sum = (s0 + s1) + (s2 + s3);
+      if (lead && it == 0) WTC_STAMP(p, TS_EXP);
 
-      float lm;                                    // tile-row max (log2 domain)
-      float2 o = make_float2(-INFINITY, 0.f);      // PARTS == 2: the other half's (max, sum)
-      float ll4 = 0.f;                             // PARTS == 4: the row's sum over the four parts (part 0 only)
-      if (PARTS == 2) {
-        // ---- the two halves of a row meet through shared memory ----
-        *mine = make_float2(m_half, sum);
-        named_bar_sync(1 + q, 64);
-        o = *other;
-        named_bar_sync(1 + q, 64);                 // both have read: the slots may be reused
-        lm = fmaxf(m_half, o.x);
-      } else {
-        // ---- four parts of a row: parts 1..3 leave their (max, sum) in their own warp's
-        //      staging tile (idle now: its last store has been read), part 0 collects.  Only
-        //      part 0 needs the combination; the others just signal and move on. ----
-        if (lane == 0) tma_store_wait_read();
-        __syncwarp();
-        if (half != 0) {
-          *reinterpret_cast<float2 *>(stg + lane * 8) = make_float2(m_half, sum);
-          named_bar_arrive(1 + q, 128);
-          lm = m_half;                             // unused by parts 1..3
-        } else {
-          named_bar_sync(1 + q, 128);
-          lm = m_half;
-          float2 part[3];
-#pragma unroll
-          for (int j = 0; j < 3; ++j) {
-            part[j] = *reinterpret_cast<const float2 *>(smem + L::kOffOut + (4 * (j + 1) + ((q + 2) & 3)) * L::kOutWarpBytes + lane * 8);
-            lm = fmaxf(lm, part[j].x);
-          }
-          ll4 = sum * ex2_approx(m_half - lm);
-#pragma unroll
-          for (int j = 0; j < 3; ++j) ll4 += part[j].x == -INFINITY ? 0.f : part[j].y * ex2_approx(part[j].x - lm);
-        }
-      }
+      // ---- the two halves of a row meet through shared memory ----
+      *mine = make_float2(m_half, sum);
+      named_bar_sync(1 + q, 64);
+      const float2 o = *other;
+      named_bar_sync(1 + q, 64);                 // both have read: the slots may be reused
+      const float lm = fmaxf(m_half, o.x);       // tile-row max (log2 domain)
       float f;                                     // what my e values still have to be multiplied by
       if (CLUSTER) {
-        const float ll = PARTS == 4 ? ll4
-                                    : (m_half == -INFINITY ? 0.f : sum * ex2_approx(m_half - lm)) +
-                                          (o.x == -INFINITY ? 0.f : o.y * ex2_approx(o.x - lm));
+        const float ll = (m_half == -INFINITY ? 0.f : sum * ex2_approx(m_half - lm)) +
+                         (o.x == -INFINITY ? 0.f : o.y * ex2_approx(o.x - lm));
         // ... and the CTAs of the cluster through each other's shared memory
         if (half == 0) {
           const uint32_t slot = smem_u32(&stats[(par * kMaxCluster + col_rank) * BM + row_in_tile]);
           const uint32_t bar = smem_u32(&stats_bar[par]);
           for (uint32_t peer = 0; peer < cluster_n; ++peer)
-            st_async_f32x2(map_to_cta(slot, row_peer(peer)), lm, ll, map_to_cta(bar, row_peer(peer)));
+            st_async_f32x2(map_to_cta(slot, peer), lm, ll, map_to_cta(bar, peer));
         }
         if (!mbar_wait_cluster(&stats_bar[par], tile_phase)) { record_failure(p.status, WTC_DEV_TIMEOUT_STATS); break; }
-        if (lead && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 3);
-        if (lead) { stamp_tile(p, it, 2); stamp_fine(p, it, 4); }
+        if (lead && it == 0) WTC_STAMP(p, TS_STATS);
         float gm, inv_gl;
         combine_cluster_stats(par, row_in_tile, gm, inv_gl);
         f = ex2_approx(m_half - gm) * inv_gl;
@@ -816,8 +897,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         f = ex2_approx(m_half - lm);               // tiled: values relative to the tile max, not normalised
       }
 
-      if (lead) stamp_fine(p, it, 5);              // row statistics combined, factor known
-      // ---- p = e * f -> f16 -> global memory ----
+      // ---- p = e * f -> output type -> 128-byte-swizzled staging tiles -> TMA stores ----
       float sum_r = 0.f;                           // tiled: sum of what is actually stored
       if (OUT32) {
         // f32 probabilities: 32 columns (one 128-byte row) per staging tile and TMA store
@@ -840,80 +920,56 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             ++gcount;
           }
         }
-      } else if (OUT_TILES == 0) {
-        // straight from registers: each thread owns 256 contiguous bytes of its row
-        const int row = rb * BM + row_in_tile;
-        __half *orow = static_cast<__half *>(p.out) + static_cast<long long>(b) * p.o_batch_stride + static_cast<long long>(row) * p.ldo + col0;
+      } else if (OUT_TILES * 2 >= NCH) {
+        // the warp's whole share of the tile fits its staging tiles: pack and stage
+        // everything, then ONE proxy fence and warp barrier, then all stores back to back
+        if (lane == 0) tma_store_wait_read();    // the previous tile's stores have read the staging tiles
+        __syncwarp();
 #pragma unroll
         for (int c = 0; c < NCH; ++c) {
           if (c * 32 < valid) {
             uint32_t h[16];
+            scale_pack(r[c], f, h);
+            if (!CLUSTER) {
 #pragma unroll
-            for (int i = 0; i < 32; i += 2) {
-              const __half2 hh = __floats2half2_rn(__uint_as_float(r[c][i]) * f, __uint_as_float(r[c][i + 1]) * f);
-              if (!CLUSTER) { const float2 back = __half22float2(hh); sum_r += back.x + back.y; }
-              h[i >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
+              for (int i = 0; i < 16; ++i) { const float2 back = __half22float2(*reinterpret_cast<const __half2 *>(&h[i])); sum_r += back.x + back.y; }
             }
-            if (row < p.M) st_global_row32(orow + c * 32, h, p.out_align32, valid - c * 32);
+            stage_row_chunk(stg + (c >> 1) * 4096, lane, c & 1, h);
           }
         }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (rows_live) {
+#pragma unroll
+            for (int g = 0; g < NCH / 2; ++g)
+              if (g * 64 < valid) tma_store_3d(&tmO, stg + g * 4096, col0 + g * 64, row0, b);
+          }
+          tma_store_commit();
+        }
       } else {
-        // 128-byte-swizzled staging tiles in shared memory, written out by TMA.
-        if (OUT_TILES * 2 >= NCH) {
-          // the warp's whole share of the tile fits its staging tiles: pack and stage
-          // everything, then ONE proxy fence and warp barrier, then all stores back to back
-          if (lane == 0) tma_store_wait_read();    // the previous tile's stores have read the staging tiles
-          __syncwarp();
+        // fewer staging tiles than column groups: 64 columns at a time through one tile
 #pragma unroll
-          for (int c = 0; c < NCH; ++c) {
-            if (c * 32 < valid) {
+        for (int g = 0; g < NCH / 2; ++g) {
+          if (g * 64 < valid) {
+            if (lane == 0) tma_store_wait_read();
+            __syncwarp();
+#pragma unroll
+            for (int hc = 0; hc < 2; ++hc) {
+              const int c = g * 2 + hc;
               uint32_t h[16];
+              scale_pack(r[c], f, h);
+              if (!CLUSTER) {
 #pragma unroll
-              for (int i = 0; i < 32; i += 2) {
-                const __half2 hh = __floats2half2_rn(__uint_as_float(r[c][i]) * f, __uint_as_float(r[c][i + 1]) * f);
-                if (!CLUSTER) { const float2 back = __half22float2(hh); sum_r += back.x + back.y; }
-                h[i >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
+                for (int i = 0; i < 16; ++i) { const float2 back = __half22float2(*reinterpret_cast<const __half2 *>(&h[i])); sum_r += back.x + back.y; }
               }
-              stage_row_chunk(stg + (c >> 1) * 4096, lane, c & 1, h);
+              stage_row_chunk(stg, lane, hc, h);
             }
-          }
-          if (lead) stamp_fine(p, it, 6);          // packed and staged
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            if (rows_live) {
-#pragma unroll
-              for (int g = 0; g < NCH / 2; ++g)
-                if (g * 64 < valid) tma_store_3d(&tmO, stg + g * 4096, col0 + g * 64, row0, b);
-            }
-            tma_store_commit();
-          }
-        } else {
-          // fewer staging tiles than column groups: 64 columns at a time through one tile
-#pragma unroll
-          for (int g = 0; g < NCH / 2; ++g) {
-            if (g * 64 < valid) {
-              if (lane == 0) tma_store_wait_read();
-              __syncwarp();
-#pragma unroll
-              for (int hc = 0; hc < 2; ++hc) {
-                const int c = g * 2 + hc;
-                uint32_t h[16];
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                  const __half2 hh = __floats2half2_rn(__uint_as_float(r[c][i]) * f, __uint_as_float(r[c][i + 1]) * f);
-                  if (!CLUSTER) { const float2 back = __half22float2(hh); sum_r += back.x + back.y; }
-                  h[i >> 1] = *reinterpret_cast<const uint32_t *>(&hh);
-                }
-                stage_row_chunk(stg, lane, hc, h);
-              }
-              if (lead && g == NCH / 2 - 1) stamp_fine(p, it, 6);
-              fence_proxy_async_smem();
-              __syncwarp();
-              if (lane == 0) {
-                if (rows_live) tma_store_3d(&tmO, stg, col0 + g * 64, row0, b);
-                tma_store_commit();
-              }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              if (rows_live) tma_store_3d(&tmO, stg, col0 + g * 64, row0, b);
+              tma_store_commit();
             }
           }
         }
@@ -927,36 +983,54 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           p.tile_stats[(static_cast<int64_t>(b) * p.M + row) * p.num_nb + nb] = make_float2(lm, sum_r + other->y);
         named_bar_sync(1 + q, 64);
       }
-      if (lead && it == 0 && p.timeline_mode == 0) stamp(p.timeline, 4);
-      if (lead) { stamp_tile(p, it, 3); stamp_fine(p, it, 7); }
+      if (lead && it == 0) WTC_STAMP(p, TS_STAGED);
     }
-    if (lane == 0) tma_store_wait_all();
-    if (lead && p.timeline_mode == 0) stamp(p.timeline, 5);
+    if (lane == 0) tma_store_wait_read();
+    if (lead) WTC_STAMP(p, TS_STORED);
   }
 
-  }   // warps 0-3 of the relay form, every warp of the others
+  }   // warps 0-3 of the relay form, warps 0-1 of the single-tile form, every warp of the split form
 
   // ---- teardown: nothing in flight, peers done with our shared memory, TMEM freed ----
   if (p.status && *reinterpret_cast<volatile int *>(p.status) != 0) {
     // a wait gave up somewhere: give copies that were already issued time to land
     for (int i = 0; i < 200; ++i) __nanosleep(1000);
   }
+  if (threadIdx.x == 0) WTC_STAMP(p, TS_TEARDOWN);
+  if (CLUSTER && !cluster_waited) cluster_wait_acquire();   // (whole warps: the role split is by warp)
   tc_fence_before_sync();
   __syncthreads();
   if (CLUSTERED) cluster_sync_all();
+  if (threadIdx.x == 0) WTC_STAMP(p, TS_CLSYNC);
   if (warp == 1) { if (PAIR) tmem_dealloc_pair(tmem_base, 2 * BN); else tmem_dealloc(tmem_base, 2 * BN); }
+  if (threadIdx.x == 0) WTC_STAMP(p, TS_EXIT);
 }
 
-template <int BN, int STAGES, bool CLUSTER, int OUT_TILES, bool RELAY, bool PAIR, int EW, bool OUT32 = false, bool SINGLE = false>
+// Per-device launch facts of one kernel instance: the dynamic shared memory opt-in and how
+// many clusters of each size the device holds at once.
+struct DeviceFacts {
+  bool attr_set = false;
+  int max_clusters[2 * kMaxCluster + 1] = {0};
+  int registers = 0;
+};
+
+template <int BN, int STAGES, bool CLUSTER, int EPI, bool PAIR, bool OUT32>
 cudaError_t launch_impl(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO, TcParams p,
                         int cluster_n, int num_sms, cudaStream_t s, TcLaunchInfo *info) {
-  using L = SmemLayout<BN, STAGES, CLUSTER, OUT_TILES, RELAY, PAIR, EW, OUT32, SINGLE>;
-  auto kern = fused_tc_kernel<BN, STAGES, CLUSTER, OUT_TILES, RELAY, PAIR, EW, OUT32, SINGLE>;
-  static bool attr_set = false;   // per template instance
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
+  using L = SmemLayout<BN, STAGES, CLUSTER, EPI, PAIR, OUT32>;
+  auto kern = fused_tc_kernel<BN, STAGES, CLUSTER, EPI, PAIR, OUT32>;
+  static DeviceFacts facts[64];   // per template instance, per device
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  DeviceFacts &df = facts[dev];
+  if (!df.attr_set) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
     if (e != cudaSuccess) return e;
-    attr_set = true;
+    cudaFuncAttributes fa;
+    if (cudaFuncGetAttributes(&fa, kern) == cudaSuccess) df.registers = fa.numRegs;
+    df.attr_set = true;
   }
   // work items: row units (128 rows, or 256 for a CTA pair) x (column blocks when tiled)
   p.num_ru = PAIR ? (p.num_rb + 1) / 2 : p.num_rb;
@@ -964,7 +1038,7 @@ cudaError_t launch_impl(const CUtensorMap &tmA, const CUtensorMap &tmB, const CU
   const int cluster_size = (CLUSTER ? cluster_n : 1) * (PAIR ? 2 : 1);
 
   cudaLaunchConfig_t cfg = {};
-  cfg.blockDim = dim3(kThreadsFor(EW, RELAY), 1, 1);
+  cfg.blockDim = dim3(kThreadsFor(EPI), 1, 1);
   cfg.dynamicSmemBytes = L::kDynamic;
   cfg.stream = s;
   cudaLaunchAttribute attr[2];
@@ -983,17 +1057,16 @@ cudaError_t launch_impl(const CUtensorMap &tmA, const CUtensorMap &tmB, const CU
     ++nattr;
     cfg.attrs = attr;
     cfg.numAttrs = nattr;
-    static int max_clusters_cache[2 * kMaxCluster + 1] = {0};   // per template instance, by cluster size
-    if (!max_clusters_cache[cluster_size]) {
+    if (!df.max_clusters[cluster_size]) {
       cfg.gridDim = dim3(cluster_size, 1, 1);
       int mc = 0;
-      cudaError_t e = cudaOccupancyMaxActiveClusters(&mc, kern, &cfg);
+      e = cudaOccupancyMaxActiveClusters(&mc, kern, &cfg);
       if (e != cudaSuccess) return e;
       if (mc < 1) return cudaErrorInvalidConfiguration;
-      max_clusters_cache[cluster_size] = mc;
+      df.max_clusters[cluster_size] = mc;
     }
-    const int max_clusters = max_clusters_cache[cluster_size];
-    if (SINGLE && p.num_items > max_clusters) return cudaErrorNotSupported;   // some CTA would own two tiles: the caller takes another form
+    const int max_clusters = df.max_clusters[cluster_size];
+    if (EPI == EPI_SINGLE && p.num_items > max_clusters) return cudaErrorNotSupported;   // some CTA would own two tiles: the caller takes another form
     const int clusters = p.num_items < max_clusters ? p.num_items : max_clusters;
     grid = clusters * cluster_size;
   } else {
@@ -1002,68 +1075,50 @@ cudaError_t launch_impl(const CUtensorMap &tmA, const CUtensorMap &tmB, const CU
     cfg.numAttrs = nattr;
   }
   cfg.gridDim = dim3(grid, 1, 1);
-  if (info) { info->grid = grid; info->cluster = cluster_size; info->smem_bytes = L::kDynamic; info->threads = kThreadsFor(EW, RELAY); }
+  if (info) {
+    info->grid = grid; info->cluster = cluster_size; info->smem_bytes = L::kDynamic; info->threads = kThreadsFor(EPI);
+    info->stages = STAGES; info->registers = df.registers;
+  }
   return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmO, p);
 }
 
 } // namespace
 
-// Variant choice.  pair: two CTAs share one 256-row MMA (a third less L2 operand traffic per
-// flop).  Measured on B200 the contraction runs at the same rate either way, and an
-// eight-CTA cluster fits the chip only 15 times, so the cluster flavour pairs only on
-// request; the tiled flavour (clusters of two) pairs when the K loop is long.  relay: sixteen
-// epilogue warps in two groups that overlap consecutive tiles (cluster flavour, f16, staged
-// stores).  store: swizzled staging + TMA stores by default, direct register stores on request.
+// Form choice of the cluster flavour.  f32 probabilities and 128-column tiles: the split
+// epilogue.  256-column f16 tiles: the relay when a CTA sees several tiles (its two groups
+// then overlap), its single-tile form when every cluster fits the chip at once, the split
+// form otherwise or on request.
 cudaError_t launch_fused_cluster(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO,
                                  const TcParams &p, int bn, int cluster_n, int num_sms, cudaStream_t s,
                                  TcLaunchInfo *info) {
   if (cluster_n < 1 || cluster_n > kMaxCluster) return cudaErrorInvalidValue;
   if (p.out_f32)
-    return bn == 128 ? launch_impl<128, 4, true, 2, false, false, 8, true>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info)
-                     : launch_impl<kTcBlockN, 3, true, 2, false, false, 8, true>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
-  // 128-column tiles (a tile choice of best.json): the default schedule only
-  if (bn == 128) return launch_impl<128, 4, true, 2, false, false, 8>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
-  const bool pair = p.pair_mode == 2 && 2 * cluster_n <= kMaxCluster;
-  const bool tma = p.store_mode == 1;
-  if (pair) {
-    if (tma) return launch_impl<kTcBlockN, 4, true, 2, false, true, 8>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
-    return launch_impl<kTcBlockN, 6, true, 0, false, true, 8>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+    return bn == 128 ? launch_impl<128, 4, true, EPI_SPLIT, false, true>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info)
+                     : launch_impl<kTcBlockN, 3, true, EPI_SPLIT, false, true>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+  if (bn == 128) return launch_impl<128, 4, true, EPI_SPLIT, false, false>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+  const int resident = num_sms / cluster_n;
+  const int tiles_per_cta = (p.batch * p.num_rb + resident - 1) / (resident > 0 ? resident : 1);
+  const bool relay = p.epilogue_mode == kEpilogueRelay || (p.epilogue_mode == kEpilogueAuto && tiles_per_cta >= kRelayMinTiles);
+  if (relay) return launch_impl<kTcBlockN, 3, true, EPI_RELAY, false, false>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+  if (p.epilogue_mode == kEpilogueAuto) {
+    // one tile per CTA; the single-tile form declines (before launching) when the clusters do not all fit at once
+    const cudaError_t e = launch_impl<kTcBlockN, 4, true, EPI_SINGLE, false, false>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+    if (e != cudaErrorNotSupported) return e;
   }
-  if (tma) {
-    // the relay pays when a CTA sees several tiles: its two groups then overlap
-    const int resident = num_sms / cluster_n;
-    const int tiles_per_cta = (p.batch * p.num_rb + resident - 1) / (resident > 0 ? resident : 1);
-    const bool relay = p.epilogue_mode == 2 || (p.epilogue_mode == 0 && tiles_per_cta >= kRelayMinTiles);
-    if (relay) return launch_impl<kTcBlockN, 3, true, 1, true, false, 16>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
-    // one tile per CTA: the single-tile relay form (both groups share the tile's store phase), unless
-    // a form was asked for; it declines (before launching) when the clusters do not all fit at once
-    if (p.epilogue_mode == 0 && p.epilogue_warps != 16) {
-      const cudaError_t e = launch_impl<kTcBlockN, 3, true, 1, true, false, 16, false, true>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
-      if (e != cudaErrorNotSupported) return e;
-    }
-    // sixteen epilogue warps (a row's columns split four ways) on request: measured on B200 it
-    // does not beat eight (the exp and pack phases are bound by the special-function unit)
-    if (p.epilogue_warps == 16)
-      return launch_impl<kTcBlockN, 3, true, 1, false, false, 16>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
-    return launch_impl<kTcBlockN, 3, true, 2, false, false, 8>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
-  }
-  return launch_impl<kTcBlockN, 4, true, 0, false, false, 8>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+  return launch_impl<kTcBlockN, 3, true, EPI_SPLIT, false, false>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
 }
 
+// Tiled flavour.  pair: two CTAs share one 256-row MMA (a third less L2 operand traffic per
+// flop), taken when the K loop is long and there are at least two row blocks.
 cudaError_t launch_tiled_partial(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO,
                                  const TcParams &p, int bn, int num_sms, cudaStream_t s, TcLaunchInfo *info) {
   if (p.out_f32)
-    return bn == 128 ? launch_impl<128, 6, false, 1, false, false, 8, true>(tmA, tmB, tmO, p, 1, num_sms, s, info)
-                     : launch_impl<kTcBlockN, 4, false, 1, false, false, 8, true>(tmA, tmB, tmO, p, 1, num_sms, s, info);
-  if (bn == 128) return launch_impl<128, 6, false, 1, false, false, 8>(tmA, tmB, tmO, p, 1, num_sms, s, info);
-  const bool pair = p.pair_mode == 2 || (p.pair_mode == 0 && p.num_rb >= 2 && p.num_kb >= 8);
-  const bool tma = p.store_mode == 1;
-  if (pair) {
-    if (tma) return launch_impl<kTcBlockN, 6, false, 1, false, true, 8>(tmA, tmB, tmO, p, 1, num_sms, s, info);
-    return launch_impl<kTcBlockN, 6, false, 0, false, true, 8>(tmA, tmB, tmO, p, 1, num_sms, s, info);
-  }
-  if (tma) return launch_impl<kTcBlockN, 4, false, 1, false, false, 8>(tmA, tmB, tmO, p, 1, num_sms, s, info);
-  return launch_impl<kTcBlockN, 4, false, 0, false, false, 8>(tmA, tmB, tmO, p, 1, num_sms, s, info);
+    return bn == 128 ? launch_impl<128, 6, false, EPI_SPLIT, false, true>(tmA, tmB, tmO, p, 1, num_sms, s, info)
+                     : launch_impl<kTcBlockN, 4, false, EPI_SPLIT, false, true>(tmA, tmB, tmO, p, 1, num_sms, s, info);
+  if (bn == 128) return launch_impl<128, 6, false, EPI_SPLIT, false, false>(tmA, tmB, tmO, p, 1, num_sms, s, info);
+  const bool pair = p.num_rb >= 2 && (p.pair_mode == 2 || (p.pair_mode == 0 && p.num_kb >= 8));
+  if (pair) return launch_impl<kTcBlockN, 6, false, EPI_SPLIT, true, false>(tmA, tmB, tmO, p, 1, num_sms, s, info);
+  return launch_impl<kTcBlockN, 4, false, EPI_SPLIT, false, false>(tmA, tmB, tmO, p, 1, num_sms, s, info);
 }
 
 } // namespace wtc

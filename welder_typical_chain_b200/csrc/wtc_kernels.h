@@ -8,12 +8,8 @@
 
 namespace wtc {
 
-// UMMA shared-memory descriptor geometry, kept as data so a known-answer run
-// can check the operand layouts without a rebuild.  Bytes.
-struct UmmaGeom {
-  uint32_t a_lbo, a_sbo, a_kstep;
-  uint32_t b_lbo, b_sbo, b_kstep;
-};
+// Epilogue forms of the tensor-core kernel (TcParams::epilogue_mode; 0 lets the launcher choose).
+enum : int { kEpilogueAuto = 0, kEpilogueSplit = 1, kEpilogueRelay = 2 };
 
 struct TcParams {
   int batch, M, N, K;
@@ -24,26 +20,21 @@ struct TcParams {
   int num_items;   // work items: cluster mode batch*num_rb, tiled mode batch*num_rb*num_nb
   int b_batched;   // B has its own batch dimension
   int group_rb;    // tiled mode: row blocks per rasterisation group
-  void *out;       // output base, row stride and batch stride (elements) for the direct-store epilogue
-  long long ldo, o_batch_stride;
   int out_f32;     // f32 probabilities (else f16)
-  int out_align32; // every output row starts on a 32-byte boundary
-  int store_mode;  // 0 direct register->global stores, 1 swizzled shared staging + TMA stores
-  int epilogue_warps;  // 0 choose, 8 or 16 (cluster flavour with staged stores)
-  int pair_mode;   // 0 choose, 1 never pair CTAs, 2 pair whenever the cluster allows
-  int epilogue_mode;  // 0 choose by tiles per CTA, 1 all warps share a tile, 2 two warp groups relay consecutive tiles
+  int pair_mode;   // tiled flavour: 0 choose, 1 never pair CTAs, 2 pair whenever the shape allows
+  int epilogue_mode;  // cluster flavour: kEpilogue*
   int use_pdl;     // launch with programmatic stream serialisation
   int round_logits_f16;  // chain spelled with an f16 matmul result: round s to f16 before the softmax
   float c2;        // scale * log2(e)
   float2 *tile_stats;    // tiled mode: [batch*M][num_nb] (max in log2 domain, sum of 2^(v-max))
   int *status;     // device status word (0 = ok)
-  int timeline_mode;     // 0: phases of the first tile; 1: four points of the first four tiles
-  long long *timeline;   // optional [grid][16] nanosecond stamps of the first tile (bring-up / profiling)
-  UmmaGeom geom;
+#ifdef WTC_BRINGUP
+  long long *timeline;   // optional [grid][48] stamps of each CTA's first tile: %globaltimer ns in 0..23, clock64 in 24..47
+#endif
 };
 
 struct TcLaunchInfo {
-  int grid, cluster, smem_bytes, threads;
+  int grid, cluster, smem_bytes, threads, stages, registers;
 };
 
 // Fused cluster kernel: a cluster of ceil(N/BN) CTAs owns 128 full rows, exchanges

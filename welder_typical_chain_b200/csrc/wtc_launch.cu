@@ -35,13 +35,11 @@ int cuda_fail(cudaError_t e, const char *what) {
   return fail(WTC_E_CUDA, "%s: %s", what, cudaGetErrorString(e));
 }
 
-// built-in UMMA descriptor geometry (bytes):
-//   A (K-major, 128-byte swizzle): 8-row groups are 1024 B apart; one 16-wide K step is 32 B.
-//   B (MN-major, 128-byte swizzle): 64-column blocks are 64 k-rows * 128 B = 8192 B apart
-//   (leading), 8-k-row groups are 1024 B apart (stride); one 16-deep K step is 16 * 128 B.
-constexpr wtc::UmmaGeom kDefaultGeom = {16, 1024, 32, 8192, 1024, 2048};
-wtc::UmmaGeom g_geom = kDefaultGeom;
-long long *g_timeline = nullptr;
+#ifdef WTC_BRINGUP
+long long *g_timeline = nullptr;   // four regions of 148*48 stamps, used round-robin by consecutive launches
+unsigned g_timeline_launch = 0;
+#endif
+// environment, read once
 const int g_use_pdl = [] { const char *e = getenv("WTC_NO_PDL"); return (e && e[0] == '1') ? 0 : 1; }();
 
 struct Resolved {
@@ -163,14 +161,20 @@ int resolve(const wtc_chain_desc *in, Resolved &r) {
       const int64_t resident = 148 / r.num_nb;
       const int64_t units = static_cast<int64_t>(d.batch) * r.num_rb;
       const int64_t tiles_per_cta = (units + resident - 1) / resident;
-      // relay epilogue (twenty warps) when a CTA sees several tiles, its single-tile form when every
-      // cluster fits the chip at once; otherwise the eight-warp split form
+      // relay epilogue (twenty warps) when a CTA sees several tiles; the single-tile form (eighteen
+      // warps, four operand stages: the staging tiles lie over them) when every cluster fits the
+      // chip at once; otherwise, or on request, the eight-warp split form
       static const int kResidentClusters[9] = {0, 148, 72, 47, 35, 27, 22, 18, 15};
-      if (plain && (tiles_per_cta >= wtc::kRelayMinTiles || units <= kResidentClusters[r.num_nb])) p.threads = 640;
+      const bool want_split = d.flags & WTC_FLAG_EPILOGUE_SPLIT, want_relay = d.flags & WTC_FLAG_EPILOGUE_RELAY;
+      if (plain && !want_split) {
+        if (want_relay || tiles_per_cta >= wtc::kRelayMinTiles) p.threads = 640;
+        else if (units <= kResidentClusters[r.num_nb]) { p.threads = 576; p.stages = 4; }
+      }
     } else {
       p.kernel = WTC_KERNEL_TC_TILED;
       p.launches = 2;
-      p.stages = (r.bn == 128 || (plain && r.num_rb >= 2 && r.num_kb >= 8)) ? 6 : 4;   // 6: 128-column tiles, or CTA pairs (long K)
+      const bool pair = plain && !(d.flags & WTC_FLAG_NO_PAIR) && r.num_rb >= 2 && ((d.flags & WTC_FLAG_PAIR) || r.num_kb >= 8);
+      p.stages = (r.bn == 128 || pair) ? 6 : 4;   // 6: 128-column tiles, or CTA pairs (long K)
       p.workspace_bytes = static_cast<size_t>(d.batch) * d.M * r.num_nb * sizeof(float2);
     }
   } else {
@@ -212,19 +216,31 @@ struct MapKey {
     return ptr == o.ptr && d0 == o.d0 && d1 == o.d1 && d2 == o.d2 && s1 == o.s1 && s2 == o.s2 && b0 == o.b0 && b1 == o.b1;
   }
 };
-struct MapEntry { MapKey key; CUtensorMap map; };
-std::vector<MapEntry> g_maps;   // small LRU-ish cache, newest at the back
-constexpr size_t kMaxMaps = 256;
+struct MapEntry { MapKey key; CUtensorMap map; bool used; };
+// Encoded tensor maps, per host thread: a direct-mapped table looked up without a lock (a launch
+// needs three maps; encoding one costs about a microsecond, a hit a few nanoseconds).
+constexpr size_t kMapSlots = 512;
+struct MapTable { MapEntry e[kMapSlots]; };
+MapTable *map_table() {
+  thread_local MapTable *t = nullptr;
+  if (!t) t = new (std::nothrow) MapTable();
+  return t;
+}
 
 // rank-3 f16 tensor (d0 innermost, contiguous), 128-byte swizzle, zero fill
 int get_map(const void *ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1_bytes, uint64_t s2_bytes, uint32_t b0,
             uint32_t b1, CUtensorMap *out, bool f32 = false) {
-  MapKey key{ptr, d0, d1, d2, s1_bytes, s2_bytes, b0 | (f32 ? 0x80000000u : 0u), b1};
-  std::lock_guard<std::mutex> lk(g_mu);
-  for (size_t i = g_maps.size(); i-- > 0;)
-    if (g_maps[i].key == key) { *out = g_maps[i].map; return WTC_OK; }
-  int rc = get_encoder();
-  if (rc) return rc;
+  const MapKey key{ptr, d0, d1, d2, s1_bytes, s2_bytes, b0 | (f32 ? 0x80000000u : 0u), b1};
+  MapTable *tab = map_table();
+  uint64_t h = reinterpret_cast<uintptr_t>(ptr) * 0x9E3779B97F4A7C15ull;
+  h ^= (d0 * 31 + d1) * 0xC2B2AE3D27D4EB4Full + d2 + s1_bytes + (static_cast<uint64_t>(key.b0) << 20) + b1;
+  MapEntry *slot = tab ? &tab->e[(h >> 40) % kMapSlots] : nullptr;
+  if (slot && slot->used && slot->key == key) { *out = slot->map; return WTC_OK; }
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    int rc = get_encoder();
+    if (rc) return rc;
+  }
   cuuint64_t dims[3] = {d0, d1, d2};
   cuuint64_t strides[2] = {s1_bytes, s2_bytes};
   cuuint32_t box[3] = {b0, b1, 1};
@@ -237,8 +253,7 @@ int get_map(const void *ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1_
     return fail(WTC_E_CUDA, "cuTensorMapEncodeTiled failed (%d) for dims=(%llu,%llu,%llu) strides=(%llu,%llu) box=(%u,%u)",
                 (int)cr, (unsigned long long)d0, (unsigned long long)d1, (unsigned long long)d2,
                 (unsigned long long)s1_bytes, (unsigned long long)s2_bytes, b0, b1);
-  if (g_maps.size() >= kMaxMaps) g_maps.erase(g_maps.begin(), g_maps.begin() + kMaxMaps / 2);
-  g_maps.push_back({key, m});
+  if (slot) { slot->key = key; slot->map = m; slot->used = true; }
   *out = m;
   return WTC_OK;
 }
@@ -255,15 +270,19 @@ int num_sms() {
   return cached[dev];
 }
 
-// per-device status word used when the caller passes none
+// Per-device status word used when the caller passes none: a word of the library's own device
+// image (zero when the module loads), so reporting through it never allocates.  The symbol's
+// name is a host-side handle; the address kernels can use is looked up once per device.
+__device__ int g_default_status_word;
 int *default_status() {
   static int *words[64] = {nullptr};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
   std::lock_guard<std::mutex> lk(g_mu);
   if (!words[dev]) {
-    if (cudaMalloc(&words[dev], sizeof(int)) != cudaSuccess) return nullptr;
-    cudaMemset(words[dev], 0, sizeof(int));
+    int *ptr = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_default_status_word) != cudaSuccess) return nullptr;
+    words[dev] = ptr;
   }
   return words[dev];
 }
@@ -348,18 +367,14 @@ int launch_resolved(Resolved &r, const void *A, const void *B, void *Out, void *
     p.round_logits_f16 = d.acc_dtype == WTC_F16;
     p.c2 = d.scale * 1.4426950408889634f;
     p.status = status ? status : default_status();
-    p.geom = g_geom;
-    p.timeline = g_timeline;
+#ifdef WTC_BRINGUP
+    p.timeline = g_timeline ? g_timeline + static_cast<size_t>(g_timeline_launch++ % 4) * 148 * 48 : nullptr;
+#endif
     p.use_pdl = g_use_pdl;
     p.out_f32 = out32;
-    p.out = Out; p.ldo = d.ldo; p.o_batch_stride = d.o_batch_stride;
-    p.out_align32 = ((reinterpret_cast<uintptr_t>(Out) & 31) == 0) && ((d.ldo & 15) == 0) && ((d.o_batch_stride & 15) == 0);
-    if (const char *e = getenv("WTC_TL_MODE")) p.timeline_mode = atoi(e);
-    p.store_mode = 1;
-    if (const char *e = getenv("WTC_EW")) p.epilogue_warps = atoi(e);
-    if (const char *e = getenv("WTC_STORE")) p.store_mode = !strcmp(e, "direct") ? 0 : 1;
-    if (const char *e = getenv("WTC_PAIR")) p.pair_mode = e[0] == '0' ? 1 : (e[0] == '1' ? 2 : 0);
-    if (const char *e = getenv("WTC_EPILOGUE")) p.epilogue_mode = !strcmp(e, "split") ? 1 : (!strcmp(e, "relay") ? 2 : 0);
+    p.pair_mode = (d.flags & WTC_FLAG_NO_PAIR) ? 1 : ((d.flags & WTC_FLAG_PAIR) ? 2 : 0);
+    p.epilogue_mode = (d.flags & WTC_FLAG_EPILOGUE_SPLIT) ? wtc::kEpilogueSplit
+                      : ((d.flags & WTC_FLAG_EPILOGUE_RELAY) ? wtc::kEpilogueRelay : wtc::kEpilogueAuto);
     wtc::TcLaunchInfo info;
     cudaError_t e;
     if (!tiled) {
@@ -459,11 +474,14 @@ int wtc_matmul_softmax_finish_launch(const wtc_chain_desc *desc, void *Out, cons
 int wtc_check_device_status(const int *device_status, void *stream) {
   cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail(e, "cudaStreamSynchronize");
-  const int *src = device_status ? device_status : default_status();
+  int *own = device_status ? nullptr : default_status();
+  const int *src = device_status ? device_status : own;
   if (!src) return fail(WTC_E_CUDA, "no status word");
   int v = 0;
   e = cudaMemcpy(&v, src, sizeof(int), cudaMemcpyDeviceToHost);
   if (e != cudaSuccess) return cuda_fail(e, "reading the device status word");
+  // the library's own word is reported once, then cleared (a caller's word is the caller's to clear)
+  if (v != 0 && own) cudaMemsetAsync(own, 0, sizeof(int), static_cast<cudaStream_t>(stream));
   return status_result(v);
 }
 
@@ -511,7 +529,7 @@ int wtc_matmul_softmax_host(const wtc_chain_desc *desc, const void *hostA, const
   if (!hostA || !hostB || !hostOut) return fail(WTC_E_ARG, "null host pointer");
   const size_t in_sz = d.in_dtype == WTC_F16 ? 2 : 4, out_sz = d.out_dtype == WTC_F16 ? 2 : 4;
   const size_t a_bytes = static_cast<size_t>(d.batch) * d.a_batch_stride * in_sz;
-  const size_t b_bytes = static_cast<size_t>(r.b_batched ? d.batch : 1) * d.K * d.ldb * in_sz;
+  const size_t b_bytes = (r.b_batched ? static_cast<size_t>(d.batch) * d.b_batch_stride : static_cast<size_t>(d.K) * d.ldb) * in_sz;
   const size_t o_bytes = static_cast<size_t>(d.batch) * d.o_batch_stride * out_sz;
   const size_t w_bytes = r.plan.workspace_bytes;
 
@@ -615,23 +633,15 @@ int wtc_matmul_softmax_host(const wtc_chain_desc *desc, const void *hostA, const
   e = cudaMemcpyAsync(host_status, dev_status, sizeof(int), cudaMemcpyDeviceToHost, ln.out);
   if (e == cudaSuccess) e = cudaStreamSynchronize(ln.out);
   if (e != cudaSuccess) return cuda_fail(e, "waiting for the results");
+  if (*host_status != 0) cudaMemsetAsync(default_status(), 0, sizeof(int), ln.out);   // reported once, then cleared
   return status_result(*host_status);
-}
-
-int wtc_debug_set_umma_geometry(uint32_t a_lbo, uint32_t a_sbo, uint32_t a_kstep, uint32_t b_lbo, uint32_t b_sbo,
-                                uint32_t b_kstep) {
-  if (!a_lbo && !a_sbo && !a_kstep && !b_lbo && !b_sbo && !b_kstep) g_geom = kDefaultGeom;
-  else g_geom = wtc::UmmaGeom{a_lbo, a_sbo, a_kstep, b_lbo, b_sbo, b_kstep};
-  return WTC_OK;
 }
 
 // ---- the entry point that allocates nothing -----------------------------------
 // Scratch for wtc_matmul_softmax_launch_static: one array that lives in the
 // library's device image (every GPU that loads the library carries it until the
-// process exits).  First 256 bytes: the device status word.  Rest: the per-tile
-// (max, sum) pairs of the two-pass schedule.
+// process exits): the per-tile (max, sum) pairs of the two-pass schedule.
 constexpr size_t kStaticScratchBytes = WTC_STATIC_SCRATCH_BYTES;
-constexpr size_t kStaticStatusBytes = 256;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 // The array's name is only a host-side handle here; the address kernels can use has to
@@ -649,7 +659,6 @@ unsigned char *static_scratch_for_current_device(int *rc_out) {
     e = cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_static_scratch);
     if (e != cudaSuccess || !ptr) { *rc_out = cuda_fail(e, "cudaGetSymbolAddress(static scratch)"); return nullptr; }
     ptrs[dev] = ptr;
-    g_maps.reserve(kMaxMaps);   // keep the tensor-map cache from growing later
   }
   return ptrs[dev];
 }
@@ -659,33 +668,36 @@ int wtc_matmul_softmax_launch_static(const wtc_chain_desc *desc, const void *A, 
   Resolved r;
   int rc = resolve(desc, r);
   if (rc) return rc;
-  if (!r.tc_ok)
-    return fail(WTC_E_UNSUPPORTED, "the static-scratch entry point covers the tensor-core two-pass schedule only "
-                                   "(f16 operands and output, K, N and row strides multiples of 8)");
-  const size_t need = static_cast<size_t>(r.d.batch) * r.d.M * r.num_nb * sizeof(float2);
-  if (need > kStaticScratchBytes - kStaticStatusBytes)
-    return fail(WTC_E_WORKSPACE, "this shape needs %zu bytes of scratch; the static scratch holds %zu "
-                                 "(use wtc_matmul_softmax_launch with a caller-provided workspace)",
-                need, kStaticScratchBytes - kStaticStatusBytes);
-  unsigned char *base = static_scratch_for_current_device(&rc);
-  if (!base) return rc;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  // the array keeps whatever the previous call left: the status word must start at zero,
-  // the (max, sum) pairs are all rewritten before they are read
-  if (!device_status) {
-    cudaError_t e = cudaMemsetAsync(base, 0, sizeof(int), s);
-    if (e != cudaSuccess) return cuda_fail(e, "clearing the static status word");
-  }
+  if (r.d.M == 0 || r.d.N == 0) return WTC_OK;        // nothing to compute, as for the other entry points
+  // this entry point always runs the two-pass schedule: size the scratch for the tiles it will use
   r.d.flags |= WTC_FLAG_FORCE_TILED;
   rc = resolve(&r.d, r);
   if (rc) return rc;
-  return launch_resolved(r, A, B, Out, base + kStaticStatusBytes, kStaticScratchBytes - kStaticStatusBytes, nullptr, 0, s,
-                         device_status ? device_status : reinterpret_cast<int *>(base));
+  if (!r.tc_ok)
+    return fail(WTC_E_UNSUPPORTED, "the static-scratch entry point covers the tensor-core two-pass schedule only "
+                                   "(f16 operands and output, K, N and row strides multiples of 8)");
+  if (!aligned16(A) || !aligned16(B) || !aligned16(Out))
+    return fail(WTC_E_UNSUPPORTED, "the static-scratch entry point needs A, B and Out on 16-byte boundaries");
+  const size_t need = static_cast<size_t>(r.d.batch) * r.d.M * r.num_nb * sizeof(float2);
+  if (need > kStaticScratchBytes)
+    return fail(WTC_E_WORKSPACE, "this shape needs %zu bytes of scratch (%d-column tiles); the static scratch holds %zu "
+                                 "(use wtc_matmul_softmax_launch with a caller-provided workspace)",
+                need, r.bn, kStaticScratchBytes);
+  unsigned char *base = static_scratch_for_current_device(&rc);
+  if (!base) return rc;
+  // the array keeps whatever the previous call left: the (max, sum) pairs are all rewritten
+  // before they are read, so nothing has to be cleared
+  return launch_resolved(r, A, B, Out, base, kStaticScratchBytes, nullptr, 0, static_cast<cudaStream_t>(stream), device_status);
 }
 
-int wtc_debug_set_timeline(void *device_buffer) {
+#ifdef WTC_BRINGUP
+// Bring-up builds only: a device buffer of grid*48 int64 that the tensor-core kernels stamp
+// (see fused_tc_kernel.cu); NULL switches the stamps off.
+int wtc_bringup_set_timeline(void *device_buffer) {
   g_timeline = static_cast<long long *>(device_buffer);
+  g_timeline_launch = 0;
   return WTC_OK;
 }
+#endif
 
 } // extern "C"

@@ -82,6 +82,17 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
   }
 }
 
+// One probe of the barrier, no loop: non-zero if the phase with `parity` has completed.
+__device__ __forceinline__ uint32_t mbar_try_wait(uint64_t *bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}\n"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok;
+}
+
 // ---- cluster / distributed shared memory ------------------------------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -114,6 +125,10 @@ __device__ __forceinline__ void mbar_arrive_remote_release(uint32_t cluster_bar_
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// The two halves of the cluster barrier, for code that has work to do between them.  Every
+// thread that arrives must wait before it arrives again.
+__device__ __forceinline__ void cluster_arrive_release() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait_acquire() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 // Bounded wait with cluster-scope acquire: pairs with mbar_arrive_remote_release.
 __device__ __forceinline__ bool mbar_wait_cluster(uint64_t *bar, uint32_t parity) {
   const uint32_t addr = smem_u32(bar);
@@ -169,6 +184,12 @@ __device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *m
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
+// Asks for one box of the tensor to be brought into L2; nothing is written to shared memory and
+// nothing completes on a barrier.
+__device__ __forceinline__ void tma_prefetch_l2_3d(const CUtensorMap *m, int x, int y, int z) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(z) : "memory");
+}
 // CTA-pair form: the copy lands in THIS CTA's shared memory, its bytes are counted on the
 // barrier at the same offset in the pair's even-ranked CTA (bit 24 of a shared::cluster
 // address selects the odd CTA of a pair).  No multicast.
@@ -187,6 +208,18 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap *m, const void *s
   asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4}], [%1];"
                ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
                : "memory");
+}
+// Same store, with an L2 eviction policy for the lines it writes (createpolicy value).
+__device__ __forceinline__ void tma_store_3d_hint(const CUtensorMap *m, const void *smem_src, int x, int y, int z, uint64_t policy) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group.L2::cache_hint [%0, {%2, %3, %4}], [%1], %5;"
+               ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(smem_src)), "r"(x), "r"(y), "r"(z), "l"(policy)
+               : "memory");
+}
+// L2 policy "evict first": lines written with it are the first to make room for new ones.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
 }
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
@@ -345,25 +378,6 @@ __device__ __forceinline__ float rcp_approx(float x) {
 __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t *>(&h);
-}
-
-// ---- direct global stores -------------------------------------------------------
-// One thread writes 32 consecutive f16 (64 bytes) of its own row.  With 32-byte aligned
-// rows each instruction fills a whole 32-byte sector (256-bit stores); otherwise 128-bit.
-// `lim` = how many of the 32 columns exist (a multiple of 8).
-__device__ __forceinline__ void st_global_row32(void *dst, const uint32_t (&h)[16], bool align32, int lim) {
-  if (lim >= 32 && align32) {
-    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-                 ::"l"(dst), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]), "r"(h[4]), "r"(h[5]), "r"(h[6]), "r"(h[7]) : "memory");
-    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-                 ::"l"(static_cast<char *>(dst) + 32), "r"(h[8]), "r"(h[9]), "r"(h[10]), "r"(h[11]), "r"(h[12]), "r"(h[13]), "r"(h[14]), "r"(h[15]) : "memory");
-  } else {
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-      if (j * 8 < lim)
-        asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};"
-                     ::"l"(static_cast<char *>(dst) + j * 16), "r"(h[4 * j]), "r"(h[4 * j + 1]), "r"(h[4 * j + 2]), "r"(h[4 * j + 3]) : "memory");
-  }
 }
 
 // ---- named barrier among a subset of warps ------------------------------------

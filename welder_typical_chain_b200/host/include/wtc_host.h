@@ -17,6 +17,12 @@ namespace ir {
 
 // What the recogniser extracts from `func @main`.
 struct ChainSpec {
+  // which chain the function spells: "matmul_softmax" (the operator this build serves), or one of
+  // the row-only chains of the reference's backend inputs: "row_softmax"
+  // (backend/welder/mlir_pipeline/softmax_row_chain.mlir) and "layernorm_variance"
+  // (backend/welder/mlir_pipeline/layernorm_variance_chain.mlir); for those K = 0
+  std::string kind = "matmul_softmax";
+  double meanFactor = 0.0, varFactor = 0.0;   // layernorm_variance: the constants applied to the two row sums
   std::string funcName = "main";
   int64_t batch = 1, M = 0, N = 0, K = 0;
   bool batched = false;        // linalg.batch_matmul + softmax over the last of 3 dims
@@ -34,6 +40,9 @@ struct ChainSpec {
 // Parses the restricted grammar (see chain_ir.cpp).  Comments are ignored, so the
 // tagged file parses like the canonical one.
 bool parseChain(const std::string &mlirText, ChainSpec &spec, std::string &diag);
+// The dataflow matcher behind parseChain (chain_match.cpp): `text` has comments stripped and
+// aliases expanded.
+bool matchChain(const std::string &text, ChainSpec &spec, std::string &diag);
 bool parseChainFile(const std::string &path, ChainSpec &spec, std::string &diag);
 std::string chainToJson(const ChainSpec &spec);
 

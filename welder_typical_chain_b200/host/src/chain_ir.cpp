@@ -125,26 +125,6 @@ bool parseTensorType(const std::string &s, TensorType &t) {
   return true;
 }
 
-std::vector<TensorType> allTensorTypes(const std::string &s) {
-  std::vector<TensorType> out;
-  static const std::regex re(R"(tensor<(?:[0-9]+x)+(?:f16|f32)>)");
-  for (auto it = std::sregex_iterator(s.begin(), s.end(), re); it != std::sregex_iterator(); ++it) {
-    TensorType t;
-    if (parseTensorType(it->str(), t)) out.push_back(t);
-  }
-  return out;
-}
-
-// text of the parenthesised group that starts at s[open] == '('
-std::string parenGroup(const std::string &s, size_t open) {
-  int depth = 0;
-  for (size_t i = open; i < s.size(); ++i) {
-    if (s[i] == '(') ++depth;
-    else if (s[i] == ')' && --depth == 0) return s.substr(open + 1, i - open - 1);
-  }
-  return "";
-}
-
 std::string typeStr(const std::vector<int64_t> &dims, const std::string &elem) {
   std::string s = "tensor<";
   for (int64_t d : dims) s += std::to_string(d) + "x";
@@ -222,93 +202,7 @@ std::string decomposedSoftmax(const std::string &input, const std::string &resul
 bool parseChain(const std::string &rawText, ChainSpec &spec, std::string &diag) {
   const std::string text = expandAliases(stripComments(rawText));
   spec = ChainSpec();
-
-  // ---- function signature
-  static const std::regex fnRe(R"(func\.func\s+@([A-Za-z_][\w]*)\s*\()");
-  std::smatch fm;
-  if (!std::regex_search(text, fm, fnRe)) { diag = "no func.func found"; return false; }
-  spec.funcName = fm[1].str();
-  const size_t open = static_cast<size_t>(fm.position(0) + fm.length(0) - 1);
-  const std::string args = parenGroup(text, open);
-  const std::vector<TensorType> argTypes = allTensorTypes(args);
-  if (argTypes.size() != 2) { diag = "expected exactly two tensor arguments (A, B), found " + std::to_string(argTypes.size()); return false; }
-  const size_t arrow = text.find("->", open + args.size());
-  TensorType resType;
-  if (arrow == std::string::npos || !parseTensorType(text.substr(arrow, 200), resType)) { diag = "function result must be a static f16/f32 tensor"; return false; }
-
-  // ---- the contraction
-  size_t mm = text.find("linalg.batch_matmul");
-  spec.batched = mm != std::string::npos;
-  if (!spec.batched) mm = text.find("linalg.matmul");
-  if (mm == std::string::npos) { diag = "no linalg.matmul / linalg.batch_matmul in the chain"; return false; }
-  const size_t insPos = text.find("ins(", mm), outsPos = text.find("outs(", mm);
-  if (insPos == std::string::npos || outsPos == std::string::npos || insPos - mm > 400 || outsPos - mm > 800) { diag = "matmul without ins(...) outs(...)"; return false; }
-  const std::vector<TensorType> ins = allTensorTypes(parenGroup(text, insPos + 3));
-  const std::vector<TensorType> outs = allTensorTypes(parenGroup(text, outsPos + 4));
-  if (ins.size() != 2 || outs.size() != 1) { diag = "matmul needs two inputs and one output tensor"; return false; }
-  const TensorType &a = ins[0], &b = ins[1], &c = outs[0];
-  const size_t rank = spec.batched ? 3 : 2;
-  if (a.dims.size() != rank || c.dims.size() != rank || (b.dims.size() != rank)) { diag = "matmul operand ranks do not match the op"; return false; }
-  const size_t o = spec.batched ? 1 : 0;
-  spec.batch = spec.batched ? a.dims[0] : 1;
-  spec.bBatched = spec.batched;
-  spec.M = a.dims[o]; spec.K = a.dims[o + 1]; spec.N = b.dims[o + 1];
-  if (b.dims[o] != spec.K) { diag = "K mismatch between A and B"; return false; }
-  if (c.dims[o] != spec.M || c.dims[o + 1] != spec.N || (spec.batched && (b.dims[0] != spec.batch || c.dims[0] != spec.batch))) { diag = "matmul result shape does not match its operands"; return false; }
-  if (a.elem != b.elem) { diag = "A and B must share an element type"; return false; }
-  if (a.dims != argTypes[0].dims || b.dims != argTypes[1].dims) { diag = "matmul must consume the function arguments (shapes differ)"; return false; }
-  if (argTypes[0].elem != argTypes[1].elem) { diag = "A and B arguments must share an element type"; return false; }
-  if (a.elem != argTypes[0].elem) {
-    // the one accepted indirection: f32 arguments rounded to f16 by arith.truncf generics ahead of the matmul
-    static const std::regex truncRe(R"(arith\.truncf\s+%[\w.]+\s*:\s*f32\s+to\s+f16)");
-    const std::string head = text.substr(0, mm);
-    const auto nTrunc = std::distance(std::sregex_iterator(head.begin(), head.end(), truncRe), std::sregex_iterator());
-    if (!(argTypes[0].elem == "f32" && a.elem == "f16" && nTrunc >= 2)) {
-      diag = "matmul must consume the function arguments directly, or f32 arguments rounded to f16 by arith.truncf";
-      return false;
-    }
-  }
-  spec.argType = argTypes[0].elem;
-  spec.inType = a.elem;
-  spec.accType = c.elem;
-  if (resType.dims != c.dims) { diag = "function result shape must equal the matmul result shape"; return false; }
-  spec.outType = resType.elem;
-
-  // ---- the softmax
-  spec.matmulCount = countContains(text, "linalg.matmul") + countContains(text, "linalg.batch_matmul");
-  spec.genericCount = countContains(text, "linalg.generic");
-  spec.reductionCount = countContains(text, "\"reduction\"");
-  spec.expCount = countContains(text, "math.exp");
-  spec.divCount = countContains(text, "arith.divf");
-  if (spec.matmulCount != 1) { diag = "expected exactly one matmul in the chain"; return false; }
-  static const std::regex smRe(R"(linalg\.softmax\s+dimension\(\s*([0-9]+)\s*\))");
-  std::smatch sm;
-  if (std::regex_search(text, sm, smRe)) {
-    spec.namedSoftmax = true;
-    if (std::stoul(sm[1].str()) != rank - 1) { diag = "linalg.softmax must reduce the last dimension (row softmax)"; return false; }
-  } else {
-    const bool hasMax = text.find("arith.maximumf") != std::string::npos || text.find("arith.maxnumf") != std::string::npos ||
-                        text.find("arith.maxf") != std::string::npos;
-    if (!hasMax || spec.expCount < 1 || spec.divCount < 1 || text.find("arith.addf") == std::string::npos || spec.reductionCount < 2) {
-      diag = "no softmax found: need linalg.softmax, or max/exp/sum/div generics with two row reductions";
-      return false;
-    }
-  }
-
-  // ---- scale: constant factors applied with arith.mulf
-  std::map<std::string, double> consts;
-  static const std::regex cRe(R"((%[\w.]+)\s*=\s*arith\.constant\s+([-+0-9.eE]+(?:[eE][-+]?[0-9]+)?)\s*:\s*(?:f16|f32))");
-  for (auto it = std::sregex_iterator(text.begin(), text.end(), cRe); it != std::sregex_iterator(); ++it)
-    consts[(*it)[1].str()] = std::strtod((*it)[2].str().c_str(), nullptr);
-  static const std::regex mulRe(R"(arith\.mulf\s+(%[\w.]+)\s*,\s*(%[\w.]+))");
-  for (auto it = std::sregex_iterator(text.begin(), text.end(), mulRe); it != std::sregex_iterator(); ++it) {
-    auto c1 = consts.find((*it)[1].str()), c2 = consts.find((*it)[2].str());
-    if (c1 != consts.end()) spec.scale *= c1->second;
-    else if (c2 != consts.end()) spec.scale *= c2->second;
-    else { diag = "arith.mulf in the chain must have a constant operand (the scale)"; return false; }
-  }
-  diag.clear();
-  return true;
+  return matchChain(text, spec, diag);
 }
 
 bool parseChainFile(const std::string &path, ChainSpec &spec, std::string &diag) {
@@ -322,6 +216,7 @@ std::string chainToJson(const ChainSpec &s) {
   snprintf(scale, sizeof scale, "%.9g", s.scale);
   std::ostringstream o;
   o << "{\n"
+    << "  \"kind\": \"" << s.kind << "\",\n"
     << "  \"func\": \"" << s.funcName << "\",\n"
     << "  \"batch\": " << s.batch << ", \"M\": " << s.M << ", \"N\": " << s.N << ", \"K\": " << s.K << ",\n"
     << "  \"batched\": " << (s.batched ? "true" : "false") << ", \"b_batched\": " << (s.bBatched ? "true" : "false") << ",\n"

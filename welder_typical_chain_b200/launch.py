@@ -16,6 +16,7 @@ _LIB = None
 F32, F16 = 0, 1
 VARIANT_FUSED, VARIANT_BASELINE = 0, 1
 FLAG_FORCE_SIMT, FLAG_FORCE_TILED, FLAG_MATMUL_F16 = 0x1, 0x2, 0x4
+FLAG_EPILOGUE_SPLIT, FLAG_EPILOGUE_RELAY, FLAG_NO_PAIR, FLAG_PAIR = 0x8, 0x10, 0x20, 0x40
 KERNEL_SIMT_FUSED, KERNEL_TC_CLUSTER, KERNEL_TC_TILED, KERNEL_SIMT_UNFUSED = 0, 1, 2, 3
 KERNEL_NAMES = {0: "simt_fused", 1: "tc_cluster", 2: "tc_tiled", 3: "simt_unfused"}
 
@@ -23,7 +24,7 @@ EXPORTS = [
     "wtc_abi_version", "wtc_last_error", "wtc_plan_query", "wtc_matmul_softmax_workspace_bytes",
     "wtc_matmul_softmax_launch", "wtc_matmul_softmax_partial_launch", "wtc_matmul_softmax_finish_launch",
     "wtc_matmul_softmax_host", "wtc_check_device_status", "wtc_matmul_softmax_time",
-    "wtc_debug_set_umma_geometry", "wtc_debug_set_timeline", "wtc_matmul_softmax_launch_static",
+    "wtc_matmul_softmax_launch_static",
 ]
 
 
@@ -80,8 +81,6 @@ def lib() -> C.CDLL:
         L.wtc_matmul_softmax_host.argtypes = [dp, vp, vp, vp]
         L.wtc_check_device_status.argtypes = [vp, vp]
         L.wtc_matmul_softmax_time.argtypes = [dp, vp, vp, vp, vp, sz, vp, C.c_int, C.c_int, C.POINTER(C.c_float)]
-        L.wtc_debug_set_umma_geometry.argtypes = [C.c_uint32] * 6
-        L.wtc_debug_set_timeline.argtypes = [vp]
         L.wtc_matmul_softmax_launch_static.argtypes = [dp, vp, vp, vp, vp, vp]
         _LIB = L
     return _LIB
@@ -120,15 +119,6 @@ def workspace_bytes(desc: ChainDesc) -> int:
     n = C.c_size_t(0)
     _check(lib().wtc_matmul_softmax_workspace_bytes(C.byref(desc), C.byref(n)))
     return int(n.value)
-
-
-def set_umma_geometry(a_lbo=0, a_sbo=0, a_kstep=0, b_lbo=0, b_sbo=0, b_kstep=0) -> None:
-    _check(lib().wtc_debug_set_umma_geometry(a_lbo, a_sbo, a_kstep, b_lbo, b_sbo, b_kstep))
-
-
-def set_timeline(buf=None) -> None:
-    """buf: a CUDA int64 tensor of at least grid*16 elements, or None to switch the stamps off."""
-    _check(lib().wtc_debug_set_timeline(C.c_void_p(buf.data_ptr()) if buf is not None else None))
 
 
 # ------------------------------------------------------------------ torch side
