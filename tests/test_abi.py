@@ -37,7 +37,7 @@ def test_struct_layout_matches_header(wtc_lib):
 
 @pytest.mark.parametrize("shape,kernel,cluster,launches,threads,stages", [
     ((1, 4096, 1024, 1024), "tc_cluster", 4, 1, 576, 4),      # f16 native chain: one tile per CTA, sixteen epilogue warps, staging over the operand stages (four stages)
-    ((64, 2048, 2048, 128), "tc_cluster", 8, 1, 640, 3),      # batched attention scores: many tiles per CTA, relay epilogue
+    ((64, 2048, 2048, 128), "tc_cluster", 8, 1, 640, 2),      # batched attention scores: many tiles per CTA, relay epilogue (short K: two operand stages, two staging tiles)
     ((1, 8192, 32000, 4096), "tc_tiled", 1, 2, 320, 6),       # vocab-wide logits: online two-pass, CTA pairs
     ((1, 16, 32000, 4096), "tc_tiled", 1, 2, 320, 4),         # skinny decode
     ((1, 8192, 128, 64), "tc_cluster", 1, 1, 320, 4),         # the reference's own shape: rows of 128 columns take the 128-column tile

@@ -75,7 +75,7 @@ struct SmemLayout {
   // 32-row x 64-column f16 (32 x 32 f32) staging tiles per storing warp: two let a warp's
   // column groups go out without waiting for each other's TMA read; the tiled flavour and
   // the relay take one and spend the room on operand stages
-  static constexpr int kOutTiles = (RELAY || SINGLE || !CLUSTER) ? 1 : 2;
+  static constexpr int kOutTiles = RELAY ? (STAGES <= 2 ? 2 : 1) : ((SINGLE || !CLUSTER) ? 1 : 2);
   static constexpr int kOutWarpBytes = kOutTiles * 4096;
   static constexpr int kOutBytes = SINGLE ? 0 : 8 * kOutWarpBytes;   // single-tile form: staging lies over the operand stages
   static constexpr int kPairBytes = (SINGLE ? 4 : 2) * BM * 8;        // [part][row] float2
@@ -139,7 +139,8 @@ __device__ __forceinline__ void stamp(long long *timeline, int slot) {
 #endif
 // stamp slots
 enum : int { TS_ENTRY = 0, TS_SETUP = 1, TS_DEPS = 2, TS_TMA0 = 3, TS_FULL0 = 4, TS_MMA_DONE = 5, TS_ACCUM = 6, TS_EXP = 7,
-             TS_STATS = 8, TS_STAGED = 9, TS_STORED = 10, TS_EXIT = 11, TS_LOADED = 12, TS_MAX = 13, TS_TEARDOWN = 14, TS_CLSYNC = 15, TS_MMA_READY = 16, TS_PACKED = 17, TS_PRODUCER_END = 18 };
+             TS_STATS = 8, TS_STAGED = 9, TS_STORED = 10, TS_EXIT = 11, TS_LOADED = 12, TS_MAX = 13, TS_TEARDOWN = 14, TS_CLSYNC = 15, TS_MMA_READY = 16, TS_PACKED = 17, TS_PRODUCER_END = 18,
+             TS_R_ACCUM8 = 19, TS_R_EXP8 = 20, TS_R_ACCUM9 = 21, TS_R_XDONE8 = 22, TS_R_STORED8 = 23 };
 
 // ---- extreme of 32 raw accumulators folded into four running chains ----
 template <bool POS>
@@ -372,29 +373,29 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     inv_gl = rcp_approx(((t[0] + t[1]) + (t[2] + t[3])) + ((t[4] + t[5]) + (t[6] + t[7])));
   };
 
-  // Relay epilogue: register reallocation between aligned groups of four warps.  The exp
-  // group needs a whole row share (128 values) in registers, the others need little; each
-  // role's code sits under its own reallocation so the allocator sees one budget per region.
+  // Relay epilogue: warps 0-3 are the producer, the MMA issuer and two idle warps (the two
+  // groups below are aligned groups of four warps each), warps 4-11 the exp group, warps
+  // 12-19 the store group.
   const int relay_role = !RELAY ? 0 : (warp < 4 ? 0 : (warp < 12 ? 1 : 2));
   bool cluster_waited = PAIR;     // this thread has completed the set-up's cluster barrier
   if (RELAY && relay_role == 1) {
+    // register reallocation between aligned groups of four warps: this group holds a whole
+    // row share (128 values) in registers: 152 a thread here, 64 in the store group (one
+    // 16-column chunk in flight, one being packed), 48 in warps 0-3 (they need little)
     setmaxnreg_inc<152>();
     cluster_wait_acquire();
     cluster_waited = true;
-    // ======================= softmax epilogue, two-stage relay ==============
-    // Two groups of eight epilogue warps work on consecutive tiles at the same time.  The
-    // first group (warps 4-11, 152 registers a thread after the reallocation above) turns
-    // the accumulator into exp values in place in tensor memory and sends the row
-    // statistics round the cluster; the second group (warps 12-19, 64 registers) waits for
-    // the cluster's statistics, reads the exp values back 32 columns at a time, scales,
-    // packs and stores them.  The exchange latency and the store phase of tile i are
-    // hidden behind the exp phase of tile i+1.  Warps 2 and 3 only fill up the first
-    // warpgroup (register reallocation works on aligned groups of four warps).
+    // ======================= softmax epilogue, two-stage relay: exp group ==============
+    // Two groups of eight epilogue warps work on consecutive tiles at the same time.  This
+    // group turns a tile's accumulator into exp values in place in tensor memory and sends
+    // the row statistics round the cluster; the store group waits for the cluster's
+    // statistics, reads the exp values back 16 columns at a time (the next chunk's load in
+    // flight while one is scaled and packed), and stores them.  The exchange latency and
+    // the store phase of tile i are hidden behind the exp phase of tile i+1.
     const int q = warp & 3;                       // TMEM lane quarter this warp may touch
     const int row_in_tile = q * 32 + lane;
     const float c2 = p.c2;
-    float *mh = reinterpret_cast<float *>(smem + L::kOffMh);   // [2][2][BM]: each half's own maximum, per tile parity
-    // ---------------- first group: max, exp in place, statistics out ----------------
+    float *mh = reinterpret_cast<float *>(smem + L::kOffMh);   // [2 tile parity][2 half][BM]: each half's own maximum
     const int half = (warp - 4) >> 2;
     const bool stamper = threadIdx.x == 128;
     float2 *mine = &pair[half * BM + row_in_tile];
@@ -408,6 +409,8 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       if (!mbar_wait(&accum_full[ab], tile_phase)) { record_failure(p.status, WTC_DEV_TIMEOUT_ACCUM); break; }
       tc_fence_after_sync();
       if (stamper && it == 0) WTC_STAMP(p, TS_ACCUM);
+      if (stamper && it == 8) WTC_STAMP(p, TS_R_ACCUM8);
+      if (stamper && it == 9) WTC_STAMP(p, TS_R_ACCUM9);
       const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ab * BN + half * HC;
       const int col0 = nb * BN + half * HC;
       const int valid = max(0, min(HC, p.N - col0));
@@ -507,14 +510,16 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(&xdone[ab]);                    // exp values parked, maxima published
+      if (stamper && it == 8) WTC_STAMP(p, TS_R_EXP8);
     }
   } else if (RELAY && relay_role == 2) {
     setmaxnreg_dec<64>();
     cluster_wait_acquire();
     cluster_waited = true;
+    // ======================= softmax epilogue, two-stage relay: store group ==============
     const int q = warp & 3;                       // TMEM lane quarter this warp may touch
     const int row_in_tile = q * 32 + lane;
-    float *mh = reinterpret_cast<float *>(smem + L::kOffMh);   // [2][2][BM]: each half's own maximum, per tile parity
+    const float *mh = reinterpret_cast<const float *>(smem + L::kOffMh);
     const int yw = warp - 12;
     const int half = yw >> 2;
     const bool lead = threadIdx.x == 384;
@@ -528,67 +533,58 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       if (lead) mbar_expect_tx(&stats_bar[sset], cluster_n * BM * 8);
       if (!mbar_wait(&xdone[ab], tile_phase)) { record_failure(p.status, WTC_DEV_TIMEOUT_ACCUM); break; }
       tc_fence_after_sync();
-      if (!mbar_wait_cluster(&stats_bar[sset], (it >> 2) & 1)) { record_failure(p.status, WTC_DEV_TIMEOUT_STATS); break; }
-      float gm, inv_gl;
-      combine_cluster_stats(sset, row_in_tile, gm, inv_gl);
-      const float f = ex2_approx(mh[((it & 1) * 2 + half) * BM + row_in_tile] - gm) * inv_gl;
+      if (lead && it == 8) WTC_STAMP(p, TS_R_XDONE8);
       const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ab * BN + half * HC;
       const int col0 = nb * BN + half * HC;
       const int valid = max(0, min(HC, p.N - col0));
       const int row0 = rb * BM + q * 32;
       const bool rows_live = row0 < p.M;
-      // 32 columns at a time through one register buffer (the scheduler's other warps cover
-      // the load latency).  The first 64 columns are staged as they are packed, the last 64
-      // wait packed in registers, so the accumulator buffer goes back to the MMA thread after
-      // the fourth load and before anything waits for a store.
-      static_assert(!RELAY || NCH == 4, "relay epilogue: a thread owns 128 columns");
-      if (valid == 0) { tc_fence_before_sync(); release_accumulator(ab); }
-      if (lane == 0) tma_store_wait_read();         // the previous tile's store has read the staging tile
+      // 16 columns at a time through two small register buffers: the next chunk's load is in
+      // flight while one is scaled, packed and staged; the first is on its way from tensor
+      // memory while the cluster's statistics arrive
+      constexpr int NC16 = HC / 16;
+      uint32_t r[2][16];
+      if (valid > 0) tmem_ld_32x32b_x16(tbase, r[0]);
+      else { tc_fence_before_sync(); release_accumulator(ab); }
+      if (!mbar_wait_cluster(&stats_bar[sset], (it >> 2) & 1)) { record_failure(p.status, WTC_DEV_TIMEOUT_STATS); break; }
+      float gm, inv_gl;
+      combine_cluster_stats(sset, row_in_tile, gm, inv_gl);
+      const float f = ex2_approx(mh[((it & 1) * 2 + half) * BM + row_in_tile] - gm) * inv_gl;
+      if (lane == 0) tma_store_wait_read();         // the previous tile's stores have read the staging tiles
       __syncwarp();
-      uint32_t h[2][16];
 #pragma unroll
-      for (int c = 0; c < NCH; ++c) {
-        uint32_t hc[16];
-        if (c * 32 < valid) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(tbase + c * 32, r);
+      for (int c = 0; c < NC16; ++c) {
+        uint8_t *tile = stg + (OUT_TILES == 2 ? (c >> 2) * 4096 : 0);
+        if (c * 16 < valid) {
           tmem_ld_wait();
-          if ((c + 1) * 32 >= valid) {                // that was my last read of this accumulator buffer
-            tc_fence_before_sync();
-            release_accumulator(ab);
+          if ((c + 1) * 16 < valid && c + 1 < NC16) tmem_ld_32x32b_x16(tbase + (c + 1) * 16, r[(c + 1) & 1]);
+          else { tc_fence_before_sync(); release_accumulator(ab); }   // that was my last read of this accumulator buffer
+          if (OUT_TILES == 1 && c == 4) {           // one staging tile: the first store must have read it
+            if (lane == 0) tma_store_wait_read();
+            __syncwarp();
           }
-          scale_pack(r, f, hc);
-        } else {
+          uint8_t *row = tile + lane * 128;
 #pragma unroll
-          for (int i = 0; i < 16; ++i) hc[i] = 0u;
+          for (int j = 0; j < 2; ++j) {
+            const uint32_t (&v)[16] = r[c & 1];
+            const uint4 h = make_uint4(pack_f16x2(__uint_as_float(v[8 * j]) * f, __uint_as_float(v[8 * j + 1]) * f),
+                                       pack_f16x2(__uint_as_float(v[8 * j + 2]) * f, __uint_as_float(v[8 * j + 3]) * f),
+                                       pack_f16x2(__uint_as_float(v[8 * j + 4]) * f, __uint_as_float(v[8 * j + 5]) * f),
+                                       pack_f16x2(__uint_as_float(v[8 * j + 6]) * f, __uint_as_float(v[8 * j + 7]) * f));
+            *reinterpret_cast<uint4 *>(row + ((((c & 3) * 2 + j) ^ (lane & 7)) * 16)) = h;   // 128-byte swizzle
+          }
         }
-        if (c < 2) stage_row_chunk(stg, lane, c & 1, hc);
-        else {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) h[c - 2][i] = hc[i];
-        }
-      }
-      if (valid > 0) {
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          if (rows_live) tma_store_3d(&tmO, stg, col0, row0, b);
-          tma_store_commit();
-        }
-      }
-      if (valid > 64) {
-        if (lane == 0) tma_store_wait_read();
-        __syncwarp();
-        stage_row_chunk(stg, lane, 0, h[0]);
-        stage_row_chunk(stg, lane, 1, h[1]);
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          if (rows_live) tma_store_3d(&tmO, stg, col0 + 64, row0, b);
-          tma_store_commit();
+        if ((c & 3) == 3 && (c - 3) * 16 < valid) {
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (rows_live) tma_store_3d(&tmO, tile, col0 + (c >> 2) * 64, row0, b);
+            tma_store_commit();
+          }
         }
       }
       if (lead && it == 0) WTC_STAMP(p, TS_STAGED);
+      if (lead && it == 8) WTC_STAMP(p, TS_R_STORED8);
     }
     if (lane == 0) tma_store_wait_read();
   } else if (SINGLE && warp >= 2) {
@@ -758,6 +754,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const int ab = it & 1;
         if (!mbar_wait(&accum_empty[ab], ((it >> 1) & 1) ^ 1)) { record_failure(p.status, WTC_DEV_TIMEOUT_TMEM); ok = false; break; }
         tc_fence_after_sync();
+        if (it == 8) WTC_STAMP(p, TS_LOADED);
         const uint32_t d_tmem = tmem_base + ab * BN;
         for (int kb = 0; kb < p.num_kb; ++kb) {
           if (!landed && !mbar_wait(&full[s], ph)) { record_failure(p.status, WTC_DEV_TIMEOUT_FULL); ok = false; break; }
@@ -786,6 +783,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           if (PAIR) umma_commit_pair(&accum_full[ab], pair_mask);
           else umma_commit(&accum_full[ab]);
           if (it == 0) WTC_STAMP(p, TS_MMA_DONE);
+          if (it == 8) WTC_STAMP(p, TS_MAX);
         }
       }
     }
@@ -1099,7 +1097,10 @@ cudaError_t launch_fused_cluster(const CUtensorMap &tmA, const CUtensorMap &tmB,
   const int resident = num_sms / cluster_n;
   const int tiles_per_cta = (p.batch * p.num_rb + resident - 1) / (resident > 0 ? resident : 1);
   const bool relay = p.epilogue_mode == kEpilogueRelay || (p.epilogue_mode == kEpilogueAuto && tiles_per_cta >= kRelayMinTiles);
-  if (relay) return launch_impl<kTcBlockN, 3, true, EPI_RELAY, false, false>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+  // (a short K loop needs no third operand stage: the room goes to a second staging tile per storing warp)
+  if (relay)
+    return p.num_kb <= 3 ? launch_impl<kTcBlockN, 2, true, EPI_RELAY, false, false>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info)
+                         : launch_impl<kTcBlockN, 3, true, EPI_RELAY, false, false>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
   if (p.epilogue_mode == kEpilogueAuto) {
     // one tile per CTA; the single-tile form declines (before launching) when the clusters do not all fit at once
     const cudaError_t e = launch_impl<kTcBlockN, 4, true, EPI_SINGLE, false, false>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);

@@ -167,7 +167,7 @@ int resolve(const wtc_chain_desc *in, Resolved &r) {
       static const int kResidentClusters[9] = {0, 148, 72, 47, 35, 27, 22, 18, 15};
       const bool want_split = d.flags & WTC_FLAG_EPILOGUE_SPLIT, want_relay = d.flags & WTC_FLAG_EPILOGUE_RELAY;
       if (plain && !want_split) {
-        if (want_relay || tiles_per_cta >= wtc::kRelayMinTiles) p.threads = 640;
+        if (want_relay || tiles_per_cta >= wtc::kRelayMinTiles) { p.threads = 640; if (r.num_kb <= 3) p.stages = 2; }
         else if (units <= kResidentClusters[r.num_nb]) { p.threads = 576; p.stages = 4; }
       }
     } else {
