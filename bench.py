@@ -38,6 +38,8 @@ WORKLOADS = {
                  desc="vocab-wide logits 8192x4096 . 4096x32000, online two-pass"),
     "cfg5": dict(batch=1, M=16, N=32000, K=4096, scale=1.0, sigma_b=0.02, b_batched=False, dtype="f16", shard="replica",
                  desc="skinny decode 16x4096 . 4096x32000"),
+    "cfg4s": dict(batch=1, M=1024, N=32000, K=4096, scale=1.0, sigma_b=0.02, b_batched=False, dtype="f16", shard="cols",
+                  desc="vocab-wide logits at an eighth of the rows (1024x4096 . 4096x32000): the size profiler captures of the two-pass kernels use"),
     "ref": dict(batch=1, M=8192, N=128, K=64, scale=1.0, sigma_b=1.0, b_batched=False, dtype="f16", shard="rows",
                 desc="the reference's own shape 8192x64 . 64x128"),
 }

@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define WTC_ABI_VERSION 1
+#define WTC_ABI_VERSION 2
 
 /* element types */
 #define WTC_F32 0
@@ -102,6 +102,11 @@ typedef struct wtc_plan_info {
   int32_t stages;       /* shared-memory pipeline depth */
   int32_t tile_substituted; /* 1 if a requested tile_* was not legal and was replaced */
   size_t workspace_bytes;
+  /* compiler facts of the main kernel's template instance (0 where not recorded) */
+  int32_t registers;    /* registers per thread at launch */
+  int32_t spill_bytes;  /* bytes of spill stores in the whole kernel (all warp roles) */
+  int32_t stack_bytes;  /* local-memory stack frame */
+  int32_t reserved;
 } wtc_plan_info;
 
 /* ABI version of the loaded library (== WTC_ABI_VERSION of its build). */

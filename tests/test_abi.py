@@ -22,7 +22,7 @@ def test_launch_header_symbols_exported(wtc_lib):
     for s in syms:
         assert hasattr(L, s), f"{s} declared in include/wtc_launch.h but not exported"
     assert sorted(wtc_lib.launch.EXPORTS) == [s for s in syms if s in wtc_lib.launch.EXPORTS]
-    assert L.wtc_abi_version() == 1
+    assert L.wtc_abi_version() == 2
 
 
 def test_struct_layout_matches_header(wtc_lib):

@@ -1082,44 +1082,84 @@ cudaError_t launch_impl(const CUtensorMap &tmA, const CUtensorMap &tmB, const CU
 
 } // namespace
 
-// Form choice of the cluster flavour.  f32 probabilities and 128-column tiles: the split
-// epilogue.  256-column f16 tiles: the relay when a CTA sees several tiles (its two groups
-// then overlap), its single-tile form when every cluster fits the chip at once, the split
-// form otherwise or on request.
+// Every instantiated variant, once: X(BN, STAGES, CLUSTER, EPI, PAIR, OUT32).
+#define WTC_TC_VARIANTS(X)                                                                        \
+  X(128, 4, true, EPI_SPLIT, false, true) X(kTcBlockN, 3, true, EPI_SPLIT, false, true)            \
+  X(128, 4, true, EPI_SPLIT, false, false) X(kTcBlockN, 3, true, EPI_SPLIT, false, false)          \
+  X(kTcBlockN, 2, true, EPI_RELAY, false, false) X(kTcBlockN, 3, true, EPI_RELAY, false, false)    \
+  X(kTcBlockN, 4, true, EPI_SINGLE, false, false)                                                  \
+  X(128, 6, false, EPI_SPLIT, false, true) X(kTcBlockN, 4, false, EPI_SPLIT, false, true)          \
+  X(128, 6, false, EPI_SPLIT, false, false) X(kTcBlockN, 4, false, EPI_SPLIT, false, false)        \
+  X(kTcBlockN, 6, false, EPI_SPLIT, true, false)
+
+// Form choice.  Cluster flavour: f32 probabilities and 128-column tiles take the split
+// epilogue; 256-column f16 tiles take the relay when a CTA sees several tiles (its two groups
+// then overlap; a short K loop needs no third operand stage: the room goes to a second staging
+// tile per storing warp), the single-tile form when every cluster fits the chip at once, the
+// split form otherwise or on request.  Tiled flavour: two CTAs share one 256-row MMA (a third
+// less L2 operand traffic per flop) when the K loop is long and there are two row blocks.
+TcVariant tc_choose_variant(bool tiled, int bn, bool out_f32, int batch, int num_rb, int num_kb, int cluster_n,
+                            int epilogue_mode, int pair_mode, int num_sms, int resident) {
+  if (tiled) {
+    if (out_f32) return bn == 128 ? TcVariant{128, 6, 0, EPI_SPLIT, 0, 1} : TcVariant{kTcBlockN, 4, 0, EPI_SPLIT, 0, 1};
+    if (bn == 128) return TcVariant{128, 6, 0, EPI_SPLIT, 0, 0};
+    const bool pair = num_rb >= 2 && (pair_mode == 2 || (pair_mode == 0 && num_kb >= 8));
+    return pair ? TcVariant{kTcBlockN, 6, 0, EPI_SPLIT, 1, 0} : TcVariant{kTcBlockN, 4, 0, EPI_SPLIT, 0, 0};
+  }
+  if (out_f32) return bn == 128 ? TcVariant{128, 4, 1, EPI_SPLIT, 0, 1} : TcVariant{kTcBlockN, 3, 1, EPI_SPLIT, 0, 1};
+  if (bn == 128) return TcVariant{128, 4, 1, EPI_SPLIT, 0, 0};
+  const int per_round = num_sms / (cluster_n > 0 ? cluster_n : 1);
+  const int units = batch * num_rb;
+  const int tiles_per_cta = (units + per_round - 1) / (per_round > 0 ? per_round : 1);
+  const bool relay = epilogue_mode == kEpilogueRelay || (epilogue_mode == kEpilogueAuto && tiles_per_cta >= kRelayMinTiles);
+  if (relay) return TcVariant{kTcBlockN, num_kb <= 3 ? 2 : 3, 1, EPI_RELAY, 0, 0};
+  if (epilogue_mode == kEpilogueAuto && units <= resident) return TcVariant{kTcBlockN, 4, 1, EPI_SINGLE, 0, 0};
+  return TcVariant{kTcBlockN, 3, 1, EPI_SPLIT, 0, 0};
+}
+
+int tc_variant_smem_bytes(const TcVariant &v) {
+#define X(BN, ST, CL, EP, PA, O32) \
+  if (v.bn == BN && v.stages == ST && (v.cluster != 0) == CL && v.epi == EP && (v.pair != 0) == PA && (v.out32 != 0) == O32) \
+    return SmemLayout<BN, ST, CL, EP, PA, O32>::kDynamic;
+  WTC_TC_VARIANTS(X)
+#undef X
+  return 0;
+}
+
+int tc_variant_threads(const TcVariant &v) { return kThreadsFor(v.epi); }
+
+namespace {
+cudaError_t launch_variant(const TcVariant &v, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO,
+                           const TcParams &p, int cluster_n, int num_sms, cudaStream_t s, TcLaunchInfo *info) {
+#define X(BN, ST, CL, EP, PA, O32) \
+  if (v.bn == BN && v.stages == ST && (v.cluster != 0) == CL && v.epi == EP && (v.pair != 0) == PA && (v.out32 != 0) == O32) \
+    return launch_impl<BN, ST, CL, EP, PA, O32>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+  WTC_TC_VARIANTS(X)
+#undef X
+  return cudaErrorInvalidConfiguration;
+}
+} // namespace
+
 cudaError_t launch_fused_cluster(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO,
                                  const TcParams &p, int bn, int cluster_n, int num_sms, cudaStream_t s,
                                  TcLaunchInfo *info) {
   if (cluster_n < 1 || cluster_n > kMaxCluster) return cudaErrorInvalidValue;
-  if (p.out_f32)
-    return bn == 128 ? launch_impl<128, 4, true, EPI_SPLIT, false, true>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info)
-                     : launch_impl<kTcBlockN, 3, true, EPI_SPLIT, false, true>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
-  if (bn == 128) return launch_impl<128, 4, true, EPI_SPLIT, false, false>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
-  const int resident = num_sms / cluster_n;
-  const int tiles_per_cta = (p.batch * p.num_rb + resident - 1) / (resident > 0 ? resident : 1);
-  const bool relay = p.epilogue_mode == kEpilogueRelay || (p.epilogue_mode == kEpilogueAuto && tiles_per_cta >= kRelayMinTiles);
-  // (a short K loop needs no third operand stage: the room goes to a second staging tile per storing warp)
-  if (relay)
-    return p.num_kb <= 3 ? launch_impl<kTcBlockN, 2, true, EPI_RELAY, false, false>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info)
-                         : launch_impl<kTcBlockN, 3, true, EPI_RELAY, false, false>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
-  if (p.epilogue_mode == kEpilogueAuto) {
-    // one tile per CTA; the single-tile form declines (before launching) when the clusters do not all fit at once
-    const cudaError_t e = launch_impl<kTcBlockN, 4, true, EPI_SINGLE, false, false>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+  // the single-tile form is tried whenever one tile per CTA is possible at all; it declines
+  // (before launching) when the clusters do not all fit the chip at once, and the split form runs
+  TcVariant v = tc_choose_variant(false, bn, p.out_f32 != 0, p.batch, p.num_rb, p.num_kb, cluster_n, p.epilogue_mode, p.pair_mode,
+                                  num_sms, /*resident=*/1 << 30);
+  if (v.epi == EPI_SINGLE) {
+    const cudaError_t e = launch_variant(v, tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
     if (e != cudaErrorNotSupported) return e;
+    v = TcVariant{kTcBlockN, 3, 1, EPI_SPLIT, 0, 0};
   }
-  return launch_impl<kTcBlockN, 3, true, EPI_SPLIT, false, false>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+  return launch_variant(v, tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
 }
 
-// Tiled flavour.  pair: two CTAs share one 256-row MMA (a third less L2 operand traffic per
-// flop), taken when the K loop is long and there are at least two row blocks.
 cudaError_t launch_tiled_partial(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO,
                                  const TcParams &p, int bn, int num_sms, cudaStream_t s, TcLaunchInfo *info) {
-  if (p.out_f32)
-    return bn == 128 ? launch_impl<128, 6, false, EPI_SPLIT, false, true>(tmA, tmB, tmO, p, 1, num_sms, s, info)
-                     : launch_impl<kTcBlockN, 4, false, EPI_SPLIT, false, true>(tmA, tmB, tmO, p, 1, num_sms, s, info);
-  if (bn == 128) return launch_impl<128, 6, false, EPI_SPLIT, false, false>(tmA, tmB, tmO, p, 1, num_sms, s, info);
-  const bool pair = p.num_rb >= 2 && (p.pair_mode == 2 || (p.pair_mode == 0 && p.num_kb >= 8));
-  if (pair) return launch_impl<kTcBlockN, 6, false, EPI_SPLIT, true, false>(tmA, tmB, tmO, p, 1, num_sms, s, info);
-  return launch_impl<kTcBlockN, 4, false, EPI_SPLIT, false, false>(tmA, tmB, tmO, p, 1, num_sms, s, info);
+  const TcVariant v = tc_choose_variant(true, bn, p.out_f32 != 0, p.batch, p.num_rb, p.num_kb, 1, p.epilogue_mode, p.pair_mode, num_sms, 0);
+  return launch_variant(v, tmA, tmB, tmO, p, 1, num_sms, s, info);
 }
 
 } // namespace wtc

@@ -37,6 +37,20 @@ struct TcLaunchInfo {
   int grid, cluster, smem_bytes, threads, stages, registers;
 };
 
+// One instantiation of the tensor-core kernel template: column tile, operand stages, flavour
+// (cluster / tiled), epilogue form (0 split, 1 relay, 2 single tile), CTA pairing, f32 output.
+struct TcVariant {
+  int bn, stages, cluster, epi, pair, out32;
+};
+// The variant the launchers below take for a call, worked out without a device: `resident` is how
+// many clusters of `cluster_n` CTAs the chip holds at once (the launchers ask the runtime; a plan
+// made without a device uses the figures measured on a 148-SM part).
+TcVariant tc_choose_variant(bool tiled, int bn, bool out_f32, int batch, int num_rb, int num_kb, int cluster_n,
+                            int epilogue_mode, int pair_mode, int num_sms, int resident);
+// Dynamic shared memory and threads per CTA of a variant (0 if it is not instantiated).
+int tc_variant_smem_bytes(const TcVariant &v);
+int tc_variant_threads(const TcVariant &v);
+
 // Fused cluster kernel: a cluster of ceil(N/BN) CTAs owns 128 full rows, exchanges
 // per-row (max, sum) through distributed shared memory and writes probabilities.
 cudaError_t launch_fused_cluster(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO,

@@ -42,6 +42,19 @@ unsigned g_timeline_launch = 0;
 // environment, read once
 const int g_use_pdl = [] { const char *e = getenv("WTC_NO_PDL"); return (e && e[0] == '1') ? 0 : 1; }();
 
+// registers / spills / stack of every instance of the tensor-core kernel template, from the
+// `ptxas -v` report of this build (generated beside the objects)
+struct KernelFacts { int bn, stages, cluster, epi, pair, out32, registers, spill_store, spill_load, stack; };
+const KernelFacts kKernelFacts[] = {
+#include "build/kernel_facts.inc"
+};
+const KernelFacts *facts_of(const wtc::TcVariant &v) {
+  for (const KernelFacts &f : kKernelFacts)
+    if (f.bn == v.bn && f.stages == v.stages && f.cluster == (v.cluster != 0) && f.epi == v.epi && f.pair == (v.pair != 0) && f.out32 == (v.out32 != 0))
+      return &f;
+  return nullptr;
+}
+
 struct Resolved {
   wtc_chain_desc d;  // strides filled in
   wtc_plan_info plan;
@@ -149,32 +162,28 @@ int resolve(const wtc_chain_desc *in, Resolved &r) {
     p.tile_m = 8; p.tile_n = static_cast<int32_t>(d.N); p.tile_k = 64;
   } else if (r.tc_ok) {
     p.tile_m = wtc::kTcBlockM; p.tile_n = r.bn; p.tile_k = wtc::kTcBlockK;
-    p.threads = 320;
     p.tmem_columns = 2 * r.bn;
-    // threads / stages as the launchers choose them on a 148-SM part (the plan is made without a device)
-    const bool plain = r.bn == wtc::kTcBlockN && d.out_dtype == WTC_F16;
-    if (r.num_nb <= 8 && !(d.flags & WTC_FLAG_FORCE_TILED)) {
+    // variant, threads, stages as the launchers choose them on a 148-SM part (the plan is made
+    // without a device): clusters of n CTAs resident at once, measured (8: 15; others: one short of 148 / n)
+    static const int kResidentClusters[9] = {0, 148, 72, 47, 35, 27, 22, 18, 15};
+    const int pair_mode = (d.flags & WTC_FLAG_NO_PAIR) ? 1 : ((d.flags & WTC_FLAG_PAIR) ? 2 : 0);
+    const int epi_mode = (d.flags & WTC_FLAG_EPILOGUE_SPLIT) ? wtc::kEpilogueSplit
+                         : ((d.flags & WTC_FLAG_EPILOGUE_RELAY) ? wtc::kEpilogueRelay : wtc::kEpilogueAuto);
+    const bool cluster = r.num_nb <= 8 && !(d.flags & WTC_FLAG_FORCE_TILED);
+    const wtc::TcVariant v = wtc::tc_choose_variant(!cluster, r.bn, d.out_dtype == WTC_F32, d.batch, r.num_rb, r.num_kb,
+                                                    cluster ? r.num_nb : 1, epi_mode, pair_mode, 148,
+                                                    cluster ? kResidentClusters[r.num_nb] : 0);
+    p.threads = wtc::tc_variant_threads(v);
+    p.stages = v.stages;
+    p.smem_bytes = wtc::tc_variant_smem_bytes(v);
+    if (const KernelFacts *f = facts_of(v)) { p.registers = f->registers; p.spill_bytes = f->spill_store; p.stack_bytes = f->stack; }
+    if (cluster) {
       p.kernel = WTC_KERNEL_TC_CLUSTER;
       p.launches = 1;
       p.cluster_n = r.num_nb;
-      p.stages = r.bn == 128 ? 4 : 3;
-      const int64_t resident = 148 / r.num_nb;
-      const int64_t units = static_cast<int64_t>(d.batch) * r.num_rb;
-      const int64_t tiles_per_cta = (units + resident - 1) / resident;
-      // relay epilogue (twenty warps) when a CTA sees several tiles; the single-tile form (eighteen
-      // warps, four operand stages: the staging tiles lie over them) when every cluster fits the
-      // chip at once; otherwise, or on request, the eight-warp split form
-      static const int kResidentClusters[9] = {0, 148, 72, 47, 35, 27, 22, 18, 15};
-      const bool want_split = d.flags & WTC_FLAG_EPILOGUE_SPLIT, want_relay = d.flags & WTC_FLAG_EPILOGUE_RELAY;
-      if (plain && !want_split) {
-        if (want_relay || tiles_per_cta >= wtc::kRelayMinTiles) { p.threads = 640; if (r.num_kb <= 3) p.stages = 2; }
-        else if (units <= kResidentClusters[r.num_nb]) { p.threads = 576; p.stages = 4; }
-      }
     } else {
       p.kernel = WTC_KERNEL_TC_TILED;
       p.launches = 2;
-      const bool pair = plain && !(d.flags & WTC_FLAG_NO_PAIR) && r.num_rb >= 2 && ((d.flags & WTC_FLAG_PAIR) || r.num_kb >= 8);
-      p.stages = (r.bn == 128 || pair) ? 6 : 4;   // 6: 128-column tiles, or CTA pairs (long K)
       p.workspace_bytes = static_cast<size_t>(d.batch) * d.M * r.num_nb * sizeof(float2);
     }
   } else {

@@ -177,6 +177,10 @@ bool validatePostbufferizeArtifacts(const std::string &artifactDir, std::string 
     << "pipeline_stages=" << planInt("stages") << "\n"
     << "tmem_columns=" << planInt("tmem_columns") << "\n"
     << "workspace_bytes=" << planInt("workspace_bytes") << "\n"
+    << "shared_memory_bytes=" << planInt("smem_bytes") << "\n"
+    << "registers_per_thread=" << planInt("registers") << "\n"
+    << "spill_store_bytes=" << planInt("spill_bytes") << "\n"
+    << "stack_frame_bytes=" << planInt("stack_bytes") << "\n"
     << "tcgen05_mma_per_tile=" << (tc ? (planInt("K") + 63) / 64 * 4 : 0) << "\n";
   if (!writeAll((out / "postbufferize_report.txt").string(), r.str())) { diagnostic = "failed to write postbufferize report"; return false; }
   diagnostic.clear();

@@ -179,7 +179,8 @@ std::string runnableText(const ir::ChainSpec &s, const CompileRequest &req, cons
     << ", substituted = " << p.tile_substituted << "}\n"
     << "  wtc.plan {variant = \"" << (req.fused ? "fused" : "baseline") << "\", kernel = \"" << kKernelNames[p.kernel] << "\", launches = " << p.launches
     << ", cluster_n = " << p.cluster_n << ", threads = " << p.threads << ", stages = " << p.stages << ", tmem_columns = " << p.tmem_columns
-    << ", workspace_bytes = " << p.workspace_bytes << "}\n"
+    << ", workspace_bytes = " << p.workspace_bytes << ", smem_bytes = " << p.smem_bytes << ", registers = " << p.registers
+    << ", spill_bytes = " << p.spill_bytes << ", stack_bytes = " << p.stack_bytes << "}\n"
     << "  func.func @" << s.funcName << "(%A: !wtc.device_ptr, %B: !wtc.device_ptr, %Out: !wtc.device_ptr, %workspace: !wtc.device_ptr) {\n";
   for (int i = 0; i < p.launches; ++i)
     o << "    gpu.launch_func @wtc_kernels::@" << kKernelNames[p.kernel] << "_" << i << " args(%A, %B, %Out, %workspace)\n";

@@ -54,6 +54,7 @@ class PlanInfo(C.Structure):
         ("cluster_n", C.c_int32), ("grid", C.c_int32), ("threads", C.c_int32), ("smem_bytes", C.c_int32),
         ("tmem_columns", C.c_int32), ("stages", C.c_int32), ("tile_substituted", C.c_int32),
         ("workspace_bytes", C.c_size_t),
+        ("registers", C.c_int32), ("spill_bytes", C.c_int32), ("stack_bytes", C.c_int32), ("reserved", C.c_int32),
     ]
 
 
