@@ -66,7 +66,10 @@ extern "C" {
 #define WTC_KERNEL_SIMT_FUSED 0
 #define WTC_KERNEL_TC_CLUSTER 1   /* tcgen05, cluster of CTAs per 128 rows, one launch   */
 #define WTC_KERNEL_TC_TILED 2     /* tcgen05 tiles + row rescale, two launches           */
-#define WTC_KERNEL_SIMT_UNFUSED 3 /* five launches (baseline variant)                    */
+#define WTC_KERNEL_SIMT_UNFUSED 3 /* five launches (baseline variant, f32 chains)        */
+#define WTC_KERNEL_TC_UNFUSED 4   /* baseline variant of f16 chains: the tcgen05 contraction
+                                     writes f32 logits to global memory, four more kernels
+                                     do max / exp / sum / divide                         */
 
 /*
  * The chain, as the compiler front-end recognised it.  Strides are in elements;

@@ -71,9 +71,12 @@ def test_plan_fallbacks_and_variants(wtc_lib):
     assert w.plan_query(w.make_desc(1, 256, 1024, 1024, flags=w.FLAG_FORCE_TILED)).tile_n == 256
     assert w.plan_query(w.make_desc(1, 100, 72, 64, flags=w.FLAG_FORCE_SIMT)).kernel == w.KERNEL_SIMT_FUSED
     assert w.plan_query(w.make_desc(1, 100, 512, 64, flags=w.FLAG_FORCE_TILED)).kernel == w.KERNEL_TC_TILED
+    # the baseline variant: five kernels; f16 chains keep the tcgen05 contraction, f32 chains (and shapes TMA cannot take) run SIMT
     p = w.plan_query(w.make_desc(2, 100, 72, 64, variant=w.VARIANT_BASELINE))
-    assert p.kernel == w.KERNEL_SIMT_UNFUSED and p.launches == 5
+    assert p.kernel == w.KERNEL_TC_UNFUSED and p.launches == 5 and p.tile_n == 128 and p.registers > 0
     assert p.workspace_bytes == (2 * 200 * 72 + 2 * 200) * 4
+    for d in (w.make_desc(2, 100, 72, 64, w.F32, w.F32, variant=w.VARIANT_BASELINE), w.make_desc(2, 100, 70, 64, variant=w.VARIANT_BASELINE)):
+        assert w.plan_query(d).kernel == w.KERNEL_SIMT_UNFUSED and w.plan_query(d).launches == 5
     # tile hints: legal ones pass, others are replaced and flagged
     assert w.plan_query(w.make_desc(1, 4096, 1024, 1024, tile_m=128, tile_n=256, tile_k=64)).tile_substituted == 0
     assert w.plan_query(w.make_desc(1, 4096, 1024, 1024, tile_m=64, tile_n=128, tile_k=32)).tile_substituted == 1

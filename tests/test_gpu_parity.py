@@ -163,11 +163,24 @@ def test_simt_odd_shapes(w, cuda_dev, M, N, K):
 
 
 def test_baseline_variant_matches_fused(w, cuda_dev):
+    """The five-kernel baseline (logits, max, exp, sum, divide through global memory): the tcgen05
+    contraction for f16 chains -- ragged shapes, both column tiles, batched, a long K loop, the f16
+    matmul result -- and SIMT FMAs for f32 chains and for shapes TMA cannot take."""
     A = oracle.normal((257, 96), 7)
     B = oracle.normal((96, 200), 8)
     ref = oracle.chain(A, B, 0.2)
     _check(_run(w, cuda_dev, A, B, 0.2, variant=w.VARIANT_BASELINE), ref)
     _check(_run(w, cuda_dev, A, B, 0.2, variant=w.VARIANT_BASELINE, out_dtype=w.F32), ref)
+    _check(_run(w, cuda_dev, A, B, 0.2, variant=w.VARIANT_BASELINE, flags=w.FLAG_FORCE_SIMT), ref)
+    for (sa, sb, scale) in (((300, 640), (640, 1032), 0.05), ((3, 200, 64), (3, 64, 520), 0.125), ((130, 72), (72, 96), -0.3)):
+        A = oracle.normal(sa, 17); B = oracle.normal(sb, 18)
+        ref = np.stack([oracle.chain(A[i], B[i], scale) for i in range(sa[0])]) if len(sa) == 3 else oracle.chain(A, B, scale)
+        _check(_run(w, cuda_dev, A, B, scale, variant=w.VARIANT_BASELINE), ref)
+    A = oracle.normal((200, 72), 9) * np.float16(0.25); B = oracle.normal((72, 768), 10) * np.float16(0.25)
+    got = _run(w, cuda_dev, A, B, 1.0, variant=w.VARIANT_BASELINE, acc_dtype=w.F16, out_dtype=w.F32)
+    assert np.abs(got.astype(np.float64) - oracle.chain(A, B, 1.0, acc=oracle.ACC_F16_SEQ)).max() < 5e-3
+    A32 = oracle.fill((64, 48), "random", 1); B32 = oracle.fill((48, 80), "random", 1)
+    _check(_run(w, cuda_dev, A32, B32, 1.0, variant=w.VARIANT_BASELINE), oracle.chain(A32, B32, 1.0))
 
 
 def test_f16_matmul_result_chain(w, cuda_dev):

@@ -10,7 +10,7 @@ from .launch import (  # noqa: F401
     time_launch, check_device_status, PreparedCall, PreparedShardCall, current_stream_ptr, matmul_softmax_static,
     F32, F16, VARIANT_FUSED, VARIANT_BASELINE, FLAG_FORCE_SIMT, FLAG_FORCE_TILED, FLAG_MATMUL_F16,
     FLAG_EPILOGUE_SPLIT, FLAG_EPILOGUE_RELAY, FLAG_NO_PAIR, FLAG_PAIR,
-    KERNEL_SIMT_FUSED, KERNEL_TC_CLUSTER, KERNEL_TC_TILED, KERNEL_SIMT_UNFUSED,
+    KERNEL_SIMT_FUSED, KERNEL_TC_CLUSTER, KERNEL_TC_TILED, KERNEL_SIMT_UNFUSED, KERNEL_TC_UNFUSED,
 )
 
 __all__ = [n for n in dir() if not n.startswith("_")]

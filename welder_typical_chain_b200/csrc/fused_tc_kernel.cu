@@ -837,6 +837,27 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
           for (int i = 0; i < 32; ++i) r[c][i] = __float_as_uint(__half2float(__float2half_rn(__uint_as_float(r[c][i]))));
       }
+      if (OUT32 && !CLUSTER && p.logits_only) {
+        // the unfused baseline's first kernel: scale * A . B as f32 logits, nothing else
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+          if (c * 32 < valid) {
+            if (lane == 0) tma_store_wait_read();
+            __syncwarp();
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[c][i]) * p.scale;
+            stage_row_f32(stg, lane, v);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              if (rows_live) tma_store_3d(&tmO, stg, col0 + c * 32, row0, b);
+              tma_store_commit();
+            }
+          }
+        }
+        continue;
+      }
       const float m_half = share_extreme<NCH>(r, valid, c2);
       if (lead && it == 0) WTC_STAMP(p, TS_MAX);
 

@@ -226,12 +226,18 @@ cudaError_t launch_simt_unfused(const void *A, const void *B, void *Out, void *w
   if (blocks > 0x7fffffff) return cudaErrorInvalidConfiguration;
   if (p.in_f16) unfused_matmul_kernel<R, true><<<static_cast<unsigned>(blocks), kSimtThreads, smem, s>>>(A, B, C32, p);
   else unfused_matmul_kernel<R, false><<<static_cast<unsigned>(blocks), kSimtThreads, smem, s>>>(A, B, C32, p);
+  return launch_softmax_passes(C32, E, mx, sum, Out, rows, p.M, p.N, p.ldo, p.o_batch_stride, p.out_f16, s);
+}
+
+cudaError_t launch_softmax_passes(const float *C32, float *E, float *mx, float *sum, void *Out, int64_t rows, int64_t rows_per_batch,
+                                  int N, int64_t ldo, int64_t o_batch_stride, int out_f16, cudaStream_t s) {
+  const int64_t total = rows * N;
   const unsigned row_grid = static_cast<unsigned>((rows + 7) / 8);
   const unsigned ew_grid = static_cast<unsigned>(total / 256 + 1 < 148 * 16 ? total / 256 + 1 : 148 * 16);
-  rowmax_kernel<<<row_grid, 256, 0, s>>>(C32, mx, rows, p.N);
-  exp_kernel<<<ew_grid, 256, 0, s>>>(C32, mx, E, total, p.N);
-  rowsum_kernel<<<row_grid, 256, 0, s>>>(E, sum, rows, p.N);
-  div_kernel<<<ew_grid, 256, 0, s>>>(E, sum, Out, p.M, total, p.N, p.ldo, p.o_batch_stride, p.out_f16);
+  rowmax_kernel<<<row_grid, 256, 0, s>>>(C32, mx, rows, N);
+  exp_kernel<<<ew_grid, 256, 0, s>>>(C32, mx, E, total, N);
+  rowsum_kernel<<<row_grid, 256, 0, s>>>(E, sum, rows, N);
+  div_kernel<<<ew_grid, 256, 0, s>>>(E, sum, Out, rows_per_batch, total, N, ldo, o_batch_stride, out_f16);
   return cudaGetLastError();
 }
 

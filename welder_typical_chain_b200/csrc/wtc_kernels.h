@@ -25,6 +25,8 @@ struct TcParams {
   int epilogue_mode;  // cluster flavour: kEpilogue*
   int use_pdl;     // launch with programmatic stream serialisation
   int round_logits_f16;  // chain spelled with an f16 matmul result: round s to f16 before the softmax
+  int logits_only; // tiled flavour, f32 output: store scale * A . B and stop (the unfused baseline's first kernel)
+  float scale;     // the chain's scale factor
   float c2;        // scale * log2(e)
   float2 *tile_stats;    // tiled mode: [batch*M][num_nb] (max in log2 domain, sum of 2^(v-max))
   int *status;     // device status word (0 = ok)
@@ -75,6 +77,11 @@ cudaError_t launch_rescale_rows(void *out, int out_f32, int64_t rows, int N, int
 // src[b * batch_stride + r * ld + c] (f32).
 cudaError_t launch_round_to_f16(const float *src, void *dst, int batch, int64_t rows, int64_t cols, int64_t ld,
                                 int64_t batch_stride, cudaStream_t s);
+
+// The four softmax passes of the unfused baseline on logits C32[rows, N] already in global
+// memory: row max -> exp -> row sum -> divide (intermediates E[rows, N], mx[rows], sum[rows]).
+cudaError_t launch_softmax_passes(const float *C32, float *E, float *mx, float *sum, void *Out, int64_t rows, int64_t rows_per_batch,
+                                  int N, int64_t ldo, int64_t o_batch_stride, int out_f16, cudaStream_t s);
 
 // SIMT kernels: any shape, f32 or f16 operands, f32 or f16 output.
 struct SimtParams {

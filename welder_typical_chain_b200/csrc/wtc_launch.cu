@@ -154,12 +154,23 @@ int resolve(const wtc_chain_desc *in, Resolved &r) {
   r.tc_ok = tc_shape && !(d.flags & WTC_FLAG_FORCE_SIMT) && d.variant == WTC_VARIANT_FUSED;
 
   if (d.variant == WTC_VARIANT_BASELINE) {
-    p.kernel = WTC_KERNEL_SIMT_UNFUSED;
+    // five kernels with C32[rows,N], E[rows,N], max[rows], sum[rows] in global memory.  For f16
+    // chains the first is the same tcgen05 contraction the fused kernel runs (so that fused
+    // against baseline measures the fusion, not the arithmetic unit); f32 chains take SIMT FMAs.
     p.launches = 5;
-    p.threads = 256;
     const size_t rows = static_cast<size_t>(d.batch) * d.M;
     p.workspace_bytes = (2 * rows * d.N + 2 * rows) * sizeof(float);
-    p.tile_m = 8; p.tile_n = static_cast<int32_t>(d.N); p.tile_k = 64;
+    if (tc_shape && !(d.flags & WTC_FLAG_FORCE_SIMT)) {
+      p.kernel = WTC_KERNEL_TC_UNFUSED;
+      const wtc::TcVariant v = wtc::tc_choose_variant(true, r.bn, true, d.batch, r.num_rb, r.num_kb, 1, 0, 1, 148, 0);
+      p.tile_m = wtc::kTcBlockM; p.tile_n = r.bn; p.tile_k = wtc::kTcBlockK;
+      p.threads = wtc::tc_variant_threads(v); p.stages = v.stages; p.tmem_columns = 2 * r.bn; p.smem_bytes = wtc::tc_variant_smem_bytes(v);
+      if (const KernelFacts *f = facts_of(v)) { p.registers = f->registers; p.spill_bytes = f->spill_store; p.stack_bytes = f->stack; }
+    } else {
+      p.kernel = WTC_KERNEL_SIMT_UNFUSED;
+      p.threads = 256;
+      p.tile_m = 8; p.tile_n = static_cast<int32_t>(d.N); p.tile_k = 64;
+    }
   } else if (r.tc_ok) {
     p.tile_m = wtc::kTcBlockM; p.tile_n = r.bn; p.tile_k = wtc::kTcBlockK;
     p.tmem_columns = 2 * r.bn;
@@ -343,12 +354,46 @@ int launch_resolved(Resolved &r, const void *A, const void *B, void *Out, void *
     return launch_resolved(ri, base, base + r.stage_a, Out, base + r.stage_a + r.stage_b, ws_bytes - r.stage_a - r.stage_b, row_stats, 0, s, status);
   }
 
-  if (r.plan.kernel == WTC_KERNEL_SIMT_UNFUSED) {
+  if (r.plan.kernel == WTC_KERNEL_SIMT_UNFUSED || r.plan.kernel == WTC_KERNEL_TC_UNFUSED) {
     if (mode != 0) return fail(WTC_E_UNSUPPORTED, "the baseline variant has no sharded form");
     if (!ws || ws_bytes < r.plan.workspace_bytes)
       return fail(WTC_E_WORKSPACE, "baseline variant needs %zu workspace bytes, got %zu", r.plan.workspace_bytes, ws_bytes);
-    cudaError_t e = wtc::launch_simt_unfused(A, B, Out, ws, simt_params(r), s);
-    return e == cudaSuccess ? WTC_OK : cuda_fail(e, "unfused pipeline launch");
+    const bool tc = r.plan.kernel == WTC_KERNEL_TC_UNFUSED && aligned16(A) && aligned16(B) && aligned16(ws) &&
+                    (d.batch == 1 || d.o_batch_stride == d.M * d.ldo);
+    if (!tc) {
+      cudaError_t e = wtc::launch_simt_unfused(A, B, Out, ws, simt_params(r), s);
+      return e == cudaSuccess ? WTC_OK : cuda_fail(e, "unfused pipeline launch");
+    }
+    const int sms = num_sms();
+    if (sms <= 0) return fail(WTC_E_CUDA, "no usable CUDA device");
+    const int64_t rows = static_cast<int64_t>(d.batch) * d.M;
+    float *C32 = static_cast<float *>(ws);
+    float *E = C32 + rows * d.N, *mx = E + rows * d.N, *sum = mx + rows;
+    CUtensorMap tmA, tmB, tmC;
+    int rc = get_map(A, d.K, d.M, d.batch, d.lda * 2, d.a_batch_stride * 2, wtc::kTcBlockK, wtc::kTcBlockM, &tmA);
+    if (!rc) rc = get_map(B, d.N, d.K, r.b_batched ? d.batch : 1, d.ldb * 2, (r.b_batched ? d.b_batch_stride : d.K * d.ldb) * 2, 64, wtc::kTcBlockK, &tmB);
+    if (!rc) rc = get_map(C32, d.N, d.M, d.batch, d.N * 4, d.M * d.N * 4, 32, 32, &tmC, true);
+    if (rc) return rc;
+    wtc::TcParams p;
+    memset(&p, 0, sizeof(p));
+    p.batch = d.batch; p.M = (int)d.M; p.N = (int)d.N; p.K = (int)d.K;
+    p.num_rb = r.num_rb; p.num_nb = r.num_nb; p.num_kb = r.num_kb;
+    p.b_batched = r.b_batched;
+    p.group_rb = 16;
+    p.round_logits_f16 = d.acc_dtype == WTC_F16;
+    p.scale = d.scale;
+    p.c2 = d.scale * 1.4426950408889634f;
+    p.status = status ? status : default_status();
+    p.use_pdl = g_use_pdl;
+    p.out_f32 = 1;
+    p.logits_only = 1;
+    p.pair_mode = 1;
+    p.num_items = d.batch * r.num_rb * r.num_nb;
+    wtc::TcLaunchInfo info;
+    cudaError_t e = wtc::launch_tiled_partial(tmA, tmB, tmC, p, r.bn, sms, s, &info);
+    if (e == cudaSuccess)
+      e = wtc::launch_softmax_passes(C32, E, mx, sum, Out, rows, d.M, (int)d.N, d.ldo, d.o_batch_stride, d.out_dtype == WTC_F16, s);
+    return e == cudaSuccess ? WTC_OK : cuda_fail(e, "unfused tensor-core pipeline launch");
   }
 
   const bool ptr_ok = aligned16(A) && aligned16(B) && aligned16(Out);
@@ -560,11 +605,13 @@ int wtc_matmul_softmax_host(const wtc_chain_desc *desc, const void *hostA, const
     }
   }
   constexpr int kMaxSlabs = 8;
-  struct Lanes { cudaStream_t in = nullptr, run = nullptr, out = nullptr; cudaEvent_t b_in = nullptr, a_in[kMaxSlabs] = {}, done[kMaxSlabs] = {}; int dev = -1; };
+  // two copy-in streams, used alternately: the set-up of one host-to-device copy runs under the
+  // transfer of the other (a lone stream of 1-2 MB copies reaches about half of the link's rate)
+  struct Lanes { cudaStream_t in[2] = {nullptr, nullptr}, run = nullptr, out = nullptr; cudaEvent_t b_in = nullptr, a_in[kMaxSlabs] = {}, done[kMaxSlabs] = {}; int dev = -1; };
   thread_local Lanes ln;
   if (ln.dev != dev) {
     ln = Lanes();
-    for (cudaStream_t *st : {&ln.in, &ln.run, &ln.out}) {
+    for (cudaStream_t *st : {&ln.in[0], &ln.in[1], &ln.run, &ln.out}) {
       e = cudaStreamCreateWithFlags(st, cudaStreamNonBlocking);
       if (e != cudaSuccess) return cuda_fail(e, "cudaStreamCreate");
     }
@@ -589,8 +636,8 @@ int wtc_matmul_softmax_host(const wtc_chain_desc *desc, const void *hostA, const
   if (slabs > units) slabs = units;
   const int64_t per = (units + slabs - 1) / slabs;
 
-  e = cudaMemcpyAsync(bufs[1].p, hostB, b_bytes, cudaMemcpyHostToDevice, ln.in);
-  if (e == cudaSuccess) e = cudaEventRecord(ln.b_in, ln.in);
+  e = cudaMemcpyAsync(bufs[1].p, hostB, b_bytes, cudaMemcpyHostToDevice, ln.in[0]);
+  if (e == cudaSuccess) e = cudaEventRecord(ln.b_in, ln.in[0]);
   if (e == cudaSuccess) e = cudaStreamWaitEvent(ln.run, ln.b_in, 0);
   if (e != cudaSuccess) return cuda_fail(e, "copy of B to the device");
   int n = 0;
@@ -614,8 +661,9 @@ int wtc_matmul_softmax_host(const wtc_chain_desc *desc, const void *hostA, const
     Resolved sr;
     rc = resolve(&sd, sr);
     if (rc) return rc;
-    e = cudaMemcpyAsync(static_cast<char *>(bufs[0].p) + a_off, static_cast<const char *>(hostA) + a_off, a_len, cudaMemcpyHostToDevice, ln.in);
-    if (e == cudaSuccess) e = cudaEventRecord(ln.a_in[n], ln.in);
+    cudaStream_t in = ln.in[(n + 1) & 1];     // slab 0 goes beside B, not behind it
+    e = cudaMemcpyAsync(static_cast<char *>(bufs[0].p) + a_off, static_cast<const char *>(hostA) + a_off, a_len, cudaMemcpyHostToDevice, in);
+    if (e == cudaSuccess) e = cudaEventRecord(ln.a_in[n], in);
     if (e == cudaSuccess) e = cudaStreamWaitEvent(ln.run, ln.a_in[n], 0);
     if (e != cudaSuccess) return cuda_fail(e, "copy of A to the device");
     rc = launch_resolved(sr, static_cast<char *>(bufs[0].p) + a_off, static_cast<char *>(bufs[1].p) + b_off,
@@ -627,7 +675,8 @@ int wtc_matmul_softmax_host(const wtc_chain_desc *desc, const void *hostA, const
     if (e != cudaSuccess) return cuda_fail(e, "copy of the result to the host");
   }
   // the next call's first copy must not overtake this call's last kernel or read-back
-  e = cudaStreamWaitEvent(ln.in, ln.done[n - 1], 0);
+  e = cudaStreamWaitEvent(ln.in[0], ln.done[n - 1], 0);
+  if (e == cudaSuccess) e = cudaStreamWaitEvent(ln.in[1], ln.done[n - 1], 0);
   if (e != cudaSuccess) return cuda_fail(e, "cudaStreamWaitEvent");
   // the device status word rides back on the copy-out stream into pinned memory: one wait
   // covers the results and the status (no separate blocking read)

@@ -23,7 +23,7 @@
 namespace wtc::transform {
 namespace {
 
-const char *kKernelNames[] = {"simt_fused", "tc_cluster", "tc_tiled", "simt_unfused"};
+const char *kKernelNames[] = {"simt_fused", "tc_cluster", "tc_tiled", "simt_unfused", "tc_unfused"};
 
 std::string moduleDir() {
   Dl_info info;
