@@ -200,6 +200,36 @@ int wtc_matmul_softmax_host(const wtc_chain_desc *desc, const void *hostA, const
 int wtc_matmul_softmax_launch_static(const wtc_chain_desc *desc, const void *A, const void *B, void *Out,
                                      void *stream, int *device_status);
 
+/*
+ * The two row-only chains among the reference's backend inputs, which share this operator's
+ * row-statistics machinery but have no contraction in front:
+ *   WTC_ROW_SOFTMAX   Out[i,:] = softmax(X[i,:])   (max -> exp(x - max) -> sum -> divide;
+ *                     backend/welder/mlir_pipeline/softmax_row_chain.mlir:10-75)
+ *   WTC_ROW_VARIANCE  Out[i,j] = var_factor * sum_j (X[i,j] - mean_factor * sum_j X[i,j])^2 for every j
+ *                     (two dependent row reductions and a broadcast;
+ *                     backend/welder/mlir_pipeline/layernorm_variance_chain.mlir:12-104)
+ * The reference compiles them with its backend tools and runs them with welder-profiler; here
+ * each is one fused kernel.  X and Out are device pointers to `rows` rows of N elements of
+ * `dtype` (WTC_F32 or WTC_F16; arithmetic in f32), row strides ld_in / ld_out in elements
+ * (0 = dense).  Asynchronous on `stream`; needs no workspace.
+ */
+#define WTC_ROW_SOFTMAX 0
+#define WTC_ROW_VARIANCE 1
+typedef struct wtc_row_chain_desc {
+  int32_t struct_size; /* sizeof(wtc_row_chain_desc) */
+  int32_t kind;        /* WTC_ROW_* */
+  int64_t rows, N;
+  int64_t ld_in, ld_out;
+  int32_t dtype;       /* WTC_F32 | WTC_F16 */
+  float mean_factor;   /* WTC_ROW_VARIANCE: the chain's 1/N constants, as written in its input */
+  float var_factor;
+  int32_t reserved;
+} wtc_row_chain_desc;
+int wtc_row_chain_launch(const wtc_row_chain_desc *desc, const void *X, void *Out, void *stream);
+/* Timed loop of the same launch (warm-up, then `iters` launches between two CUDA events). */
+int wtc_row_chain_time(const wtc_row_chain_desc *desc, const void *X, void *Out, void *stream, int warmup, int iters,
+                       float *avg_ms);
+
 /* Synchronise `stream`, read a device status word, 0 if clean else WTC_E_DEVICE.
  * device_status NULL reads the library's own per-device word (the one kernels use when a
  * launch was given no status pointer) and clears it after a non-zero report; a caller's

@@ -164,6 +164,29 @@ def chain_loops_f32(A: np.ndarray, B: np.ndarray, scale: float = 1.0, threads: i
 
 # ---------------------------------------------------------------- comparison
 
+def row_softmax(X: np.ndarray) -> np.ndarray:
+    """Row softmax of a given matrix in float64, op for op as the row-only chain spells it
+    (backend/welder/mlir_pipeline/softmax_row_chain.mlir:10-75: max from -3.4028235e38, exp(x - max),
+    sum from 0, divide)."""
+    x = np.asarray(X, dtype=np.float64)
+    m = np.maximum(x.max(axis=-1, keepdims=True), -3.4028235e38)
+    e = np.exp(x - m)
+    return e / e.sum(axis=-1, keepdims=True)
+
+
+def row_variance(A: np.ndarray, mean_factor: float | None = None, var_factor: float | None = None) -> np.ndarray:
+    """The layernorm-style variance chain in float64 (backend/welder/mlir_pipeline/layernorm_variance_chain.mlir:12-104):
+    sum -> mean = sum * c1 -> (a - mean)^2 -> sum -> var = sum * c2 -> broadcast along the row.
+    c1 and c2 default to 1/N as in the reference input (0.00390625 for N = 256)."""
+    a = np.asarray(A, dtype=np.float64)
+    n = a.shape[-1]
+    c1 = 1.0 / n if mean_factor is None else float(mean_factor)
+    c2 = 1.0 / n if var_factor is None else float(var_factor)
+    mean = a.sum(axis=-1, keepdims=True) * c1
+    var = ((a - mean) ** 2).sum(axis=-1, keepdims=True) * c2
+    return np.broadcast_to(var, a.shape).copy()
+
+
 def compare(out: np.ndarray, ref_probs: np.ndarray, out_is_f16: bool | None = None) -> dict:
     """The parity contract: max |p - p_ref| <= 2e-3, |row sum - 1| <= 1e-3 and the
     same row argmax.  Near-ties: the kernel's argmax must lie in the set of

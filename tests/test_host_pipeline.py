@@ -390,3 +390,40 @@ def test_generated_chains_round_trip_through_the_recogniser(tmp_path):
         assert abs(c["scale"] - scale) <= 1e-6 * scale and c["softmax_form"] == ("named" if named else "decomposed"), case
         best = json.load(open(out / "search" / "best.json"))
         assert best["tileM"] > 0 and best["tileN"] > 0 and best["tileK"] > 0
+
+
+def test_row_only_chains_through_the_backend_compiler(tmp_path):
+    """The two chains without a matmul (row softmax of a given matrix; the layernorm-style
+    variance chain) are recognised by their dataflow and compiled to a one-kernel plan by the
+    backend compiler; the front-end refuses them at the canonicalize stage, as the reference's
+    does (its canonical form must contain a matmul)."""
+    gen = _chain_gen()
+    wc = os.path.join(BK, "welder-compiler")
+    tiles = ["--force-tile-m", "32", "--force-tile-n", "64", "--force-tile-k", "16", "--thread-tile-m", "2", "--thread-tile-n", "2"]
+    cases = [("softmax_row_chain.mlir", None, "row_softmax", 32, 256), ("layernorm_variance_chain.mlir", None, "layernorm_variance", 32, 256),
+             (None, gen.row_softmax_chain(1000, 4104, named=True), "row_softmax", 1000, 4104),
+             (None, gen.row_softmax_chain(7, 24, aliases=False), "row_softmax", 7, 24),
+             (None, gen.layernorm_variance_chain(513, 1000, aliases=False), "layernorm_variance", 513, 1000)]
+    for name, text, kind, M, N in cases:
+        if text is None:
+            path = os.path.join(MLIR, name)
+        else:
+            path = str(tmp_path / "in.mlir")
+            open(path, "w").write(text)
+        out = tmp_path / f"o_{kind}_{M}"
+        r = subprocess.run([wc, path, *tiles, "--emit-all-stages", "--output", str(out / "03.after_postbufferize.mlir")], capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr
+        plan = open(out / "05.out.nvvm.runnable.mlir").read()
+        assert f'kind = "{kind}"' in plan and f"M = {M}, N = {N}, K = 0" in plan and "launches = 1" in plan
+        if kind == "layernorm_variance":
+            m = re.search(r"mean_factor = ([-+0-9.e]+), var_factor = ([-+0-9.e]+)", plan)
+            assert abs(float(m.group(1)) - 1.0 / N) < 1e-9 and abs(float(m.group(2)) - 1.0 / N) < 1e-9
+        for f in ("03.after_postbufferize.mlir", "04.after_workgroup_launch.mlir", "04c.after_linalg_to_loops.mlir", "compile.log"):
+            assert (out / f).stat().st_size > 0
+    r = run(["--input", os.path.join(MLIR, "softmax_row_chain.mlir"), "--out-dir", str(tmp_path / "fe")])
+    assert r.returncode == 1 and "matmul" in r.stderr
+    # broken variants are refused by the backend compiler too
+    bad = gen.layernorm_variance_chain(32, 256, aliases=False).replace("%s = arith.mulf %d, %d : f32", "%s = arith.mulf %d, %a : f32")
+    open(tmp_path / "bad.mlir", "w").write(bad)
+    r = subprocess.run([wc, str(tmp_path / "bad.mlir"), *tiles, "--emit-all-stages", "--output", str(tmp_path / "b" / "03.mlir")], capture_output=True, text=True)
+    assert r.returncode != 0 and "(a - mean)^2" in r.stderr

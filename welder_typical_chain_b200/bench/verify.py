@@ -65,8 +65,12 @@ def plan_attrs(path):
         m = re.search(r'\b%s\s*=\s*"([^"]*)"' % k, text)
         return m.group(1) if m else d
     m = re.search(r"\bscale\s*=\s*([-+0-9.eE]+)", text)
+    def getf(k, d=0.0):
+        mm = re.search(r"\b%s\s*=\s*([-+0-9.eE]+)" % k, text)
+        return float(mm.group(1)) if mm else d
     return dict(batch=geti("batch", 1), M=geti("M"), N=geti("N"), K=geti("K"), in_dtype=gets("in_dtype", "f32"),
-                arg_dtype=gets("arg_dtype", None), acc_dtype=gets("acc_dtype", "f32"), scale=float(m.group(1)) if m else 1.0)
+                arg_dtype=gets("arg_dtype", None), acc_dtype=gets("acc_dtype", "f32"), scale=float(m.group(1)) if m else 1.0,
+                kind=gets("kind", "matmul_softmax"), mean_factor=getf("mean_factor"), var_factor=getf("var_factor"))
 
 
 def main():
@@ -96,9 +100,11 @@ def main():
     out = np.lib.stride_tricks.as_strided(raw[int(meta["offset"]):], shape=(dump_m, dump_n),
                                           strides=(s0 * raw.itemsize, s1 * raw.itemsize)).astype(np.float64)
     k, scale, f16 = args.k, args.scale, args.matmul_f16
+    kind, c1, c2 = "matmul_softmax", 0.0, 0.0
     if args.plan:
         p = plan_attrs(args.plan)
         k, scale, f16 = p["K"], p["scale"], p["in_dtype"] == "f16"
+        kind, c1, c2 = p["kind"], p["mean_factor"], p["var_factor"]
         if f16 and p["arg_dtype"] == "f32":
             args.f16_rne = True      # f32 buffers rounded on the device by arith.truncf: round to nearest even
     m = dump_m if args.m <= 0 else args.m
@@ -120,14 +126,27 @@ def main():
             return x.astype(np.float64)
         return (x.astype(np.float16) if args.f16_rne else to_f16_profiler(x)).astype(np.float64)
 
-    B = as_operand(gen(k * n)).reshape(k, n)
-    a_flat = gen((max(rows) + 1) * k)
+    row_only = kind in ("row_softmax", "layernorm_variance")   # the chains without a matmul: one input X[m, n]
+    if row_only:
+        x_flat = gen((max(rows) + 1) * n)
+    else:
+        B = as_operand(gen(k * n)).reshape(k, n)
+        a_flat = gen((max(rows) + 1) * k)
     ok, max_abs, max_rel = True, 0.0, 0.0
     for i in rows:
-        a = as_operand(a_flat[i * k:(i + 1) * k])
-        c = scale * (a @ B)
-        e = np.exp(c - c.max())
-        ref = e / e.sum()
+        if row_only:
+            x = as_operand(x_flat[i * n:(i + 1) * n])
+            if kind == "row_softmax":
+                e = np.exp(x - x.max())
+                ref = e / e.sum()
+            else:
+                mean = x.sum() * c1
+                ref = np.full(n, ((x - mean) ** 2).sum() * c2)
+        else:
+            a = as_operand(a_flat[i * k:(i + 1) * k])
+            c = scale * (a @ B)
+            e = np.exp(c - c.max())
+            ref = e / e.sum()
         got = out[i, :n]
         if not np.isfinite(got).all():
             print("FAIL: output contains NaN/Inf")

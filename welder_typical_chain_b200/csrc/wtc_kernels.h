@@ -83,6 +83,11 @@ cudaError_t launch_round_to_f16(const float *src, void *dst, int batch, int64_t 
 cudaError_t launch_softmax_passes(const float *C32, float *E, float *mx, float *sum, void *Out, int64_t rows, int64_t rows_per_batch,
                                   int N, int64_t ldo, int64_t o_batch_stride, int out_f16, cudaStream_t s);
 
+// Row-only chains (row_chain_kernels.cu).  kind 0: Out = softmax_row(X); kind 1: Out[i, :] =
+// c2 * sum_j (X[i,j] - c1 * sum_j X[i,j])^2.  Row strides in elements.
+cudaError_t launch_row_chain(int kind, const void *X, void *Out, int64_t rows, int64_t N, int64_t ld_in, int64_t ld_out, int in_f16,
+                             int out_f16, float c1, float c2, cudaStream_t s);
+
 // SIMT kernels: any shape, f32 or f16 operands, f32 or f16 output.
 struct SimtParams {
   int batch, M, N, K;

@@ -748,6 +748,60 @@ int wtc_matmul_softmax_launch_static(const wtc_chain_desc *desc, const void *A, 
   return launch_resolved(r, A, B, Out, base, kStaticScratchBytes, nullptr, 0, static_cast<cudaStream_t>(stream), device_status);
 }
 
+// ---- the row-only chains ---------------------------------------------------------------------
+namespace {
+int check_row_desc(const wtc_row_chain_desc *d, int64_t &ld_in, int64_t &ld_out) {
+  if (!d) return fail(WTC_E_ARG, "null descriptor");
+  if (d->struct_size != static_cast<int32_t>(sizeof(wtc_row_chain_desc)))
+    return fail(WTC_E_ARG, "descriptor struct_size %d does not match this library (%zu)", d->struct_size, sizeof(wtc_row_chain_desc));
+  if (d->kind != WTC_ROW_SOFTMAX && d->kind != WTC_ROW_VARIANCE) return fail(WTC_E_ARG, "unknown row chain kind %d", d->kind);
+  if (d->rows < 0 || d->N < 0 || d->N > 0x7fffffff) return fail(WTC_E_ARG, "bad extents rows=%lld N=%lld", (long long)d->rows, (long long)d->N);
+  if (d->dtype != WTC_F32 && d->dtype != WTC_F16) return fail(WTC_E_ARG, "unknown dtype %d", d->dtype);
+  ld_in = d->ld_in ? d->ld_in : d->N;
+  ld_out = d->ld_out ? d->ld_out : d->N;
+  if (ld_in < d->N || ld_out < d->N) return fail(WTC_E_ARG, "row stride smaller than the row");
+  return WTC_OK;
+}
+} // namespace
+
+int wtc_row_chain_launch(const wtc_row_chain_desc *desc, const void *X, void *Out, void *stream) {
+  int64_t ld_in = 0, ld_out = 0;
+  int rc = check_row_desc(desc, ld_in, ld_out);
+  if (rc) return rc;
+  if (desc->rows == 0 || desc->N == 0) return WTC_OK;
+  if (!X || !Out) return fail(WTC_E_ARG, "null operand pointer");
+  const int f16 = desc->dtype == WTC_F16;
+  cudaError_t e = wtc::launch_row_chain(desc->kind, X, Out, desc->rows, desc->N, ld_in, ld_out, f16, f16, desc->mean_factor,
+                                        desc->var_factor, static_cast<cudaStream_t>(stream));
+  return e == cudaSuccess ? WTC_OK : cuda_fail(e, "row chain kernel launch");
+}
+
+int wtc_row_chain_time(const wtc_row_chain_desc *desc, const void *X, void *Out, void *stream, int warmup, int iters,
+                       float *avg_ms) {
+  if (!avg_ms || iters < 1 || warmup < 0) return fail(WTC_E_ARG, "bad timing arguments");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int rc = 0;
+  for (int i = 0; i < warmup && rc == 0; ++i) rc = wtc_row_chain_launch(desc, X, Out, stream);
+  if (rc) return rc;
+  cudaEvent_t e0, e1;
+  cudaError_t e = cudaEventCreate(&e0);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaEventCreate");
+  e = cudaEventCreate(&e1);
+  if (e != cudaSuccess) { cudaEventDestroy(e0); return cuda_fail(e, "cudaEventCreate"); }
+  cudaEventRecord(e0, s);
+  for (int i = 0; i < iters && rc == 0; ++i) rc = wtc_row_chain_launch(desc, X, Out, stream);
+  cudaEventRecord(e1, s);
+  e = cudaEventSynchronize(e1);
+  float ms = 0.f;
+  if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, e0, e1);
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  if (rc) return rc;
+  if (e != cudaSuccess) return cuda_fail(e, "timed launch loop");
+  *avg_ms = ms / static_cast<float>(iters);
+  return WTC_OK;
+}
+
 #ifdef WTC_BRINGUP
 // Bring-up builds only: a device buffer of grid*48 int64 that the tensor-core kernels stamp
 // (see fused_tc_kernel.cu); NULL switches the stamps off.

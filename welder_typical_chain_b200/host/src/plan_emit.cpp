@@ -188,6 +188,53 @@ std::string runnableText(const ir::ChainSpec &s, const CompileRequest &req, cons
   return o.str();
 }
 
+// ---- the row-only chains (row softmax of a given matrix; row variance broadcast along the row):
+// one fused kernel each, no tiles to choose, no workspace
+bool isRowChain(const ir::ChainSpec &s) { return s.kind == "row_softmax" || s.kind == "layernorm_variance"; }
+
+std::string rowChainStage(const ir::ChainSpec &s, int stage) {
+  const bool sm = s.kind == "row_softmax";
+  const char *kernel = sm ? "row_softmax" : "row_variance";
+  const bool warpRows = s.N <= 2048;
+  const long long grid = warpRows ? (s.M + 7) / 8 : s.M;
+  const std::string t = "memref<" + std::to_string(s.M) + "x" + std::to_string(s.N) + "x" + s.inType + ">";
+  char f1[64], f2[64];
+  snprintf(f1, sizeof f1, "%.9g", s.meanFactor);
+  snprintf(f2, sizeof f2, "%.9g", s.varFactor);
+  std::ostringstream o;
+  if (stage == 3) {
+    o << "// wtc stage 03: the row chain on buffers\nmodule {\n  func.func @" << s.funcName << "(%X: " << t << ", %Out: " << t << ") {\n";
+    if (sm) o << "    wtc.row_softmax %X -> %Out : " << t << "  {max, exp, sum, div fused; reduction over d1}\n";
+    else o << "    wtc.row_variance %X -> %Out : " << t << "  {sum, mean = " << f1 << " * sum, squared differences, sum, var = " << f2
+           << " * sum, broadcast; reductions over d1}\n";
+    o << "    return\n  }\n}\n";
+  } else if (stage == 4) {
+    o << "// wtc stage 04: launch plan for sm_100a (kernel " << kernel << ")\nmodule attributes {gpu.container_module} {\n"
+      << "  func.func @" << s.funcName << "(%X: !wtc.device_ptr, %Out: !wtc.device_ptr) {\n"
+      << "    gpu.launch blocks(" << grid << ", 1, 1) threads(256, 1, 1) {   // "
+      << (warpRows ? "one warp per row, the row in registers between the passes" : "one CTA per row, three passes (the later ones from L2)")
+      << "\n      wtc." << kernel << " %X, %Out\n      gpu.terminator\n    }\n    return\n  }\n}\n";
+  } else if (stage == 40) {
+    o << "// wtc stage 04c: loop structure per " << (warpRows ? "warp" : "CTA") << " (kernel " << kernel << ")\n"
+      << "scf.for %row = mine {\n";
+    if (sm) o << "  %m = max_j X[%row, j]\n  %e[j] = exp(X[%row, j] - %m)\n  %s = sum_j %e[j]\n  Out[%row, j] = %e[j] / %s\n";
+    else o << "  %mean = " << f1 << " * sum_j X[%row, j]\n  %var = " << f2 << " * sum_j (X[%row, j] - %mean)^2\n  Out[%row, j] = %var\n";
+    o << "}\n";
+  } else {
+    o << "// wtc stage 05: runnable plan.  The kernels are precompiled for sm_100a in libwtc_launch.so;\n"
+      << "// the runner rebuilds the descriptor from the attributes below and calls wtc_row_chain_launch.\n"
+      << "module attributes {gpu.container_module, wtc.target = \"sm_100a\"} {\n"
+      << "  wtc.chain {kind = \"" << s.kind << "\", batch = 1, M = " << s.M << ", N = " << s.N << ", K = 0, b_batched = 0, arg_dtype = \"" << s.inType
+      << "\", in_dtype = \"" << s.inType << "\", acc_dtype = \"f32\", out_dtype = \"" << s.outType << "\", scale = 1, mean_factor = " << f1
+      << ", var_factor = " << f2 << "}\n"
+      << "  wtc.plan {variant = \"fused\", kernel = \"" << kernel << "\", launches = 1, cluster_n = 1, threads = 256, stages = 0, tmem_columns = 0, workspace_bytes = 0"
+      << ", smem_bytes = " << (warpRows ? 0 : 32) << ", registers = 0, spill_bytes = 0, stack_bytes = 0}\n"
+      << "  func.func @" << s.funcName << "(%X: !wtc.device_ptr, %Out: !wtc.device_ptr) {\n"
+      << "    gpu.launch_func @wtc_kernels::@" << kernel << "_0 args(%X, %Out)\n    return\n  }\n}\n";
+  }
+  return o.str();
+}
+
 } // namespace
 
 std::string findLaunchLibrary() {
@@ -205,7 +252,7 @@ std::string findLaunchLibrary() {
 int emitPostbufferizeStage(const CompileRequest &req, const std::string &outputPath, std::string &error) {
   ir::ChainSpec spec;
   if (!ir::parseChainFile(req.inputMlirPath, spec, error)) return 2;
-  if (!writeAll(outputPath, postbufferizeText(spec, req))) { error = "cannot open output file: " + outputPath; return 2; }
+  if (!writeAll(outputPath, isRowChain(spec) ? rowChainStage(spec, 3) : postbufferizeText(spec, req))) { error = "cannot open output file: " + outputPath; return 2; }
   return 0;
 }
 
@@ -222,6 +269,21 @@ int compileChainToPlan(const CompileRequest &req, std::string &error) {
   ir::ChainSpec spec;
   std::string perr;
   if (!ir::parseChainFile(req.inputMlirPath, spec, perr)) return failWith("chain recogniser: " + perr);
+  if (isRowChain(spec)) {
+    if (spec.inType != spec.outType) return failWith("row chain: the result must have the argument's element type");
+    std::ostringstream rlog;
+    rlog << "[wtc.compile] input=" << req.inputMlirPath << "\n[wtc.compile] row chain kind=" << spec.kind << " rows=" << spec.M << " N=" << spec.N
+         << " dtype=" << spec.inType << ": one fused kernel, no tile choice, no workspace (requested tile " << req.tileM << "x" << req.tileN << "x"
+         << req.tileK << " recorded only)\n";
+    if (!writeAll((out / "03.after_postbufferize.mlir").string(), rowChainStage(spec, 3)) ||
+        !writeAll((out / "04.after_workgroup_launch.mlir").string(), rowChainStage(spec, 4)) ||
+        !writeAll((out / "04c.after_linalg_to_loops.mlir").string(), rowChainStage(spec, 40)) ||
+        !writeAll((out / "05.out.nvvm.runnable.mlir").string(), rowChainStage(spec, 5)) ||
+        !writeAll((out / "compile.log").string(), rlog.str()))
+      return failWith("failed to write compile artifacts under " + req.outDir);
+    error.clear();
+    return 0;
+  }
   PlanResult pr;
   if (!queryPlan(spec, req, pr, perr)) return failWith(perr);
 

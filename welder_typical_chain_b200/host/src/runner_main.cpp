@@ -119,6 +119,85 @@ void fillPattern(std::vector<float> &dst, const std::string &mode, uint64_t seed
 
 #define CK(call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) { std::cerr << "CUDA error in " #call ": " << cudaGetErrorString(e_) << "\n"; return 2; } } while (0)
 
+// The row-only chains: one input buffer %X[M,N], one output of the same shape and type.
+int runRowChain(const std::string &plan, const std::string &kind, long long M, long long N, const std::string &elemT, const std::string &init,
+                uint64_t seed, int warmup, int iters, const std::string &dumpPath, bool dumpAsF32, bool rne, bool listMemrefs, long long runM) {
+  if (runM > 0 && runM <= M) M = runM;
+  const size_t sz = elemT == "f16" ? 2 : 4, elems = static_cast<size_t>(M) * N;
+  if (listMemrefs) {
+    std::cout << "%X rank=2 elem_bytes=" << sz << " sizes=[" << M << ", " << N << "] role=input\n"
+              << "%Out rank=2 elem_bytes=" << sz << " sizes=[" << M << ", " << N << "] role=output\n";
+    return 0;
+  }
+  double c1 = 0.0, c2 = 0.0;
+  attrDouble(plan, "mean_factor", c1); attrDouble(plan, "var_factor", c2);
+  std::string lib;
+  if (const char *e = std::getenv("WTC_LAUNCH_LIB"); e && *e) lib = e;
+  else {
+    std::error_code ec;
+    std::filesystem::path dir = std::filesystem::read_symlink("/proc/self/exe", ec).parent_path();
+    for (int up = 0; up < 6 && lib.empty(); ++up, dir = dir.parent_path())
+      if (std::filesystem::exists(dir / "libwtc_launch.so")) lib = (dir / "libwtc_launch.so").string();
+  }
+  void *h = lib.empty() ? nullptr : dlopen(lib.c_str(), RTLD_NOW | RTLD_LOCAL);
+  if (!h) { std::cerr << "error: cannot load the launch library libwtc_launch.so (" << (lib.empty() ? "not found; set WTC_LAUNCH_LIB" : dlerror()) << ")\n"; return 2; }
+  auto launchFn = reinterpret_cast<decltype(&wtc_row_chain_launch)>(dlsym(h, "wtc_row_chain_launch"));
+  auto timeFn = reinterpret_cast<decltype(&wtc_row_chain_time)>(dlsym(h, "wtc_row_chain_time"));
+  auto lastError = reinterpret_cast<decltype(&wtc_last_error)>(dlsym(h, "wtc_last_error"));
+  if (!launchFn || !timeFn || !lastError) { std::cerr << "error: launch library lacks the row-chain entry points\n"; return 2; }
+  wtc_row_chain_desc d = {};
+  d.struct_size = sizeof d;
+  d.kind = kind == "row_softmax" ? WTC_ROW_SOFTMAX : WTC_ROW_VARIANCE;
+  d.rows = M; d.N = N;
+  d.dtype = elemT == "f16" ? WTC_F16 : WTC_F32;
+  d.mean_factor = static_cast<float>(c1); d.var_factor = static_cast<float>(c2);
+  std::vector<float> host(elems);
+  fillPattern(host, init, seed);
+  void *dX = nullptr, *dO = nullptr;
+  CK(cudaSetDevice(0));
+  CK(cudaMalloc(&dX, std::max<size_t>(elems * sz, 16)));
+  CK(cudaMalloc(&dO, std::max<size_t>(elems * sz, 16)));
+  if (sz == 2) {
+    std::vector<uint16_t> t(elems);
+    for (size_t i = 0; i < elems; ++i) t[i] = rne ? f16_rne(host[i]) : f16_profiler(host[i]);
+    CK(cudaMemcpy(dX, t.data(), elems * 2, cudaMemcpyHostToDevice));
+  } else {
+    CK(cudaMemcpy(dX, host.data(), elems * 4, cudaMemcpyHostToDevice));
+  }
+  CK(cudaMemset(dO, 0xFF, elems * sz));
+  cudaStream_t s;
+  CK(cudaStreamCreate(&s));
+  float avgMs = 0.f;
+  if (iters > 0) {
+    if (timeFn(&d, dX, dO, s, warmup, iters, &avgMs) != 0) { std::cerr << "error: " << lastError() << "\n"; return 2; }
+  } else if (launchFn(&d, dX, dO, s) != 0) { std::cerr << "error: " << lastError() << "\n"; return 2; }
+  CK(cudaStreamSynchronize(s));
+  if (!dumpPath.empty()) {
+    std::vector<unsigned char> raw(elems * sz), out;
+    CK(cudaMemcpy(raw.data(), dO, raw.size(), cudaMemcpyDeviceToHost));
+    size_t elemBytes = sz;
+    if (dumpAsF32 && sz == 2) {
+      out.resize(elems * 4);
+      for (size_t i = 0; i < elems; ++i) {
+        uint16_t hbits; std::memcpy(&hbits, &raw[i * 2], 2);
+        const float f = f16_to_f32(hbits);
+        std::memcpy(&out[i * 4], &f, 4);
+      }
+      elemBytes = 4;
+    } else out.swap(raw);
+    std::ofstream ofs(dumpPath, std::ios::binary);
+    ofs.write(reinterpret_cast<const char *>(out.data()), static_cast<std::streamsize>(out.size()));
+    std::ofstream meta(dumpPath + ".json");
+    meta << "{\n  \"sym\": \"%Out\",\n  \"rank\": 2,\n  \"elem_bytes\": " << elemBytes << ",\n  \"offset\": 0,\n  \"sizes\": [" << M << ", " << N
+         << "],\n  \"strides\": [" << N << ", 1],\n  \"bytes\": " << out.size() << "\n}\n";
+    if (!ofs || !meta) { std::cerr << "error: cannot write dump: " << dumpPath << "\n"; return 2; }
+  }
+  cudaFree(dX); cudaFree(dO);
+  std::printf("kernel_variant=%s shape=%lldx%lld\n", kind.c_str(), M, N);
+  std::printf("avg_ms=%.7g iters=%d warmup=%d\n", avgMs, iters, warmup);
+  return 0;
+}
+
 } // namespace
 
 int main(int argc, char **argv) {
@@ -163,6 +242,9 @@ int main(int argc, char **argv) {
     std::cerr << "error: " << planPath << " is not a wtc launch plan (no wtc.chain attributes)\n";
     return 2;
   }
+  std::string kind = "matmul_softmax";
+  attrStr(plan, "kind", kind);
+  if (kind == "row_softmax" || kind == "layernorm_variance") return runRowChain(plan, kind, M, N, inT, init, seed, warmup, iters, dumpPath, dumpAsF32, rne, listMemrefs, runM);
   if (!attrStr(plan, "arg_dtype", argT)) argT = inT;   // buffers hold arg_dtype; f32 buffers with in_dtype f16 are rounded on the device
   const bool roundOnDevice = argT == "f32" && inT == "f16";
   attrInt(plan, "b_batched", bBatched); attrDouble(plan, "scale", scale); attrStr(plan, "variant", variant);

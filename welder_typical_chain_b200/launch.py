@@ -24,7 +24,7 @@ EXPORTS = [
     "wtc_abi_version", "wtc_last_error", "wtc_plan_query", "wtc_matmul_softmax_workspace_bytes",
     "wtc_matmul_softmax_launch", "wtc_matmul_softmax_partial_launch", "wtc_matmul_softmax_finish_launch",
     "wtc_matmul_softmax_host", "wtc_check_device_status", "wtc_matmul_softmax_time",
-    "wtc_matmul_softmax_launch_static",
+    "wtc_matmul_softmax_launch_static", "wtc_row_chain_launch", "wtc_row_chain_time",
 ]
 
 
@@ -45,6 +45,17 @@ class ChainDesc(C.Structure):
         ("tile_m", C.c_int32), ("tile_n", C.c_int32), ("tile_k", C.c_int32),
         ("variant", C.c_int32), ("flags", C.c_int32),
     ]
+
+
+class RowChainDesc(C.Structure):
+    _fields_ = [
+        ("struct_size", C.c_int32), ("kind", C.c_int32), ("rows", C.c_int64), ("N", C.c_int64),
+        ("ld_in", C.c_int64), ("ld_out", C.c_int64), ("dtype", C.c_int32),
+        ("mean_factor", C.c_float), ("var_factor", C.c_float), ("reserved", C.c_int32),
+    ]
+
+
+ROW_SOFTMAX, ROW_VARIANCE = 0, 1
 
 
 class PlanInfo(C.Structure):
@@ -83,6 +94,8 @@ def lib() -> C.CDLL:
         L.wtc_check_device_status.argtypes = [vp, vp]
         L.wtc_matmul_softmax_time.argtypes = [dp, vp, vp, vp, vp, sz, vp, C.c_int, C.c_int, C.POINTER(C.c_float)]
         L.wtc_matmul_softmax_launch_static.argtypes = [dp, vp, vp, vp, vp, vp]
+        L.wtc_row_chain_launch.argtypes = [C.POINTER(RowChainDesc), vp, vp, vp]
+        L.wtc_row_chain_time.argtypes = [C.POINTER(RowChainDesc), vp, vp, vp, C.c_int, C.c_int, C.POINTER(C.c_float)]
         _LIB = L
     return _LIB
 
@@ -276,6 +289,41 @@ def matmul_softmax_static(A, B, scale: float, out, status=None, acc_dtype: int =
             C.byref(d), C.c_void_p(A.data_ptr()), C.c_void_p(B.data_ptr()), C.c_void_p(out.data_ptr()),
             _stream_ptr(), C.c_void_p(status.data_ptr()) if status is not None else None))
     return out
+
+
+def _row_chain(kind, X, out, mean_factor, var_factor):
+    torch = _torch()
+    if not X.is_cuda:
+        raise WtcError(-4, "operands must be CUDA tensors: this library has no CPU path")
+    if X.dim() < 2 or not X.is_contiguous():
+        raise ValueError("X must be a contiguous matrix (or a stack of matrices)")
+    N = X.shape[-1]
+    rows = X.numel() // N if N else 0
+    if out is None:
+        out = torch.empty_like(X)
+    elif tuple(out.shape) != tuple(X.shape) or out.dtype != X.dtype or not out.is_contiguous():
+        raise ValueError("out must match X in shape and dtype and be contiguous")
+    d = RowChainDesc()
+    d.struct_size = C.sizeof(RowChainDesc)
+    d.kind, d.rows, d.N, d.ld_in, d.ld_out = kind, rows, N, 0, 0
+    d.dtype = _dt(X)
+    d.mean_factor, d.var_factor = mean_factor, var_factor
+    with torch.cuda.device(X.device):
+        _check(lib().wtc_row_chain_launch(C.byref(d), C.c_void_p(X.data_ptr()), C.c_void_p(out.data_ptr()), _stream_ptr()))
+    return out
+
+
+def row_softmax(X, out=None):
+    """softmax over the last dimension of X (f32 or f16), one fused kernel: the row-only chain
+    max -> exp(x - max) -> sum -> divide."""
+    return _row_chain(ROW_SOFTMAX, X, out, 0.0, 0.0)
+
+
+def row_variance(X, mean_factor=None, var_factor=None, out=None):
+    """out[i, :] = var_factor * sum_j (X[i,j] - mean_factor * sum_j X[i,j])^2 (both factors default
+    to 1/N: the biased row variance, broadcast along the row)."""
+    n = X.shape[-1]
+    return _row_chain(ROW_VARIANCE, X, out, 1.0 / n if mean_factor is None else mean_factor, 1.0 / n if var_factor is None else var_factor)
 
 
 def check_device_status(status=None) -> None:
