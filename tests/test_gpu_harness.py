@@ -51,3 +51,19 @@ def test_search_with_on_device_profiling(tmp_path, wtc_lib, cuda_dev):
     assert len(open(tmp_path / "sp" / "profile_cache.tsv").read().splitlines()) == 2
     r = subprocess.run(["bash", script], capture_output=True, text=True, env=env)
     assert r.returncode == 0 and r.stdout.count("[wtc.profile] cache hit") == 2, r.stdout[-3000:]
+
+
+def test_native_multi_gpu_runner_on_one_gpu():
+    """welder-multi (one native process, one thread per GPU, NCCL for the column split) on the
+    GPUs this test has: every way of sharing the chain, reduced shapes, row sums checked by the
+    tool itself.  With one GPU the all-gather runs on a communicator of one rank."""
+    import json
+    import torch
+    tool = os.path.join(PKG, "backend", "welder", "compiler", "build", "welder-multi")
+    n = min(2, torch.cuda.device_count())
+    for wl, extra in (("rows", ["--m", "1024", "--n", "1024", "--k", "256"]), ("batch", ["--batch", "6", "--m", "512", "--n", "2048", "--k", "128"]),
+                      ("cols", ["--m", "512", "--n", "4104", "--k", "512"])):
+        r = subprocess.run([tool, "--workload", wl, "--gpus", str(n), "--steps", "5", "--warmup", "2", *extra], capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, r.stdout + r.stderr
+        line = json.loads(r.stdout.strip().splitlines()[-1])
+        assert line["gpus"] == n and line["row_sums_ok"] and line["us_per_step"] > 0 and len(line["us_per_step_per_gpu"]) == n
