@@ -272,16 +272,22 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     uint8_t *sb = sa + L::kABytes;
     mbar_expect_tx(&full[s], L::kStageBytes);
     tma_load_3d(sa, &tmA, &full[s], kb * BK, rb * BM, b);
+    if (p.b_blocks) tma_load_4d(sb, &tmB, &full[s], 0, kb * BK, nb * (BN / 64), bb);
+    else {
 #pragma unroll
-    for (int j = 0; j < BN / 64; ++j)
-      tma_load_3d(sb + j * (BK * 128), &tmB, &full[s], nb * BN + j * 64, kb * BK, bb);
+      for (int j = 0; j < BN / 64; ++j)
+        tma_load_3d(sb + j * (BK * 128), &tmB, &full[s], nb * BN + j * 64, kb * BK, bb);
+    }
   };
 
-  // ---- set-up.  Warp 0 creates the barriers and requests the first stages of the first tile on
-  // its own, while warp 1 allocates tensor memory: the loads' latency then runs under the rest of
-  // the set-up instead of after it.  (A CTA pair counts both CTAs' bytes on the even CTA's
-  // barrier, which must exist first: pairs start loading after the cluster barrier.)
-  const int early = PAIR ? 0 : (p.num_kb < STAGES ? p.num_kb : STAGES);
+  // ---- set-up.  Under programmatic dependent launch this CTA is resident a microsecond or two
+  // before the previous kernel on the stream is complete: everything that touches no global
+  // memory happens now (barriers, tensor memory, the cluster barrier's arrival), and ONLY the
+  // producer warp then waits for the previous kernel -- the MMA thread and the epilogue warps
+  // go straight to their shared-memory barriers, so the first MMA issues as soon as the first
+  // stage lands.  (They write global memory only after an accumulator is complete, which cannot
+  // happen before the producer's loads, which come after its wait.)
+  const int early = PAIR ? 0 : (p.num_kb < STAGES ? p.num_kb : STAGES);   // stages of the first tile the producer warp requests in one go
   if (warp == 0) {
     if (lane == 0) {
       for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -294,43 +300,6 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       mbar_fence_init();
     }
     __syncwarp();
-    if (!PAIR && first < p.num_items) {
-      int b, rb, nb; decode(first, b, rb, nb);
-      const int bb = p.b_batched ? b : 0;
-#ifndef WTC_EXP_NO_PREFETCH
-      if (CLUSTER) {
-        // Under programmatic dependent launch this CTA is resident a microsecond or two before
-        // the previous kernel on the stream is complete.  Shared memory may not be filled yet
-        // (the operands may be that kernel's output), but asking for them to be brought into L2
-        // is harmless, and turns the cold start of the pipeline into L2 hits.  The CTAs that
-        // share a panel split its K blocks: A[rb] among the cluster, B[nb] among the clusters;
-        // a lane per K block.
-        const int cl = static_cast<int>(cluster_n);
-        const int groups = stride < p.num_kb ? stride : p.num_kb;
-        for (int kb = lane; kb < p.num_kb; kb += 32) {
-          if (kb % cl == nb || kb < early) tma_prefetch_l2_3d(&tmA, kb * BK, rb * BM, b);
-          if (kb % groups == first % groups || kb < early) {
-#pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_prefetch_l2_3d(&tmB, nb * BN + j * 64, kb * BK, bb);
-          }
-        }
-      }
-#endif
-      // programmatic dependent launch: the operands may be the previous kernel's output
-      grid_dependency_wait();
-      if (lane == 0)
-        for (int s = 0; s < early; ++s) mbar_expect_tx(&full[s], L::kStageBytes);
-      __syncwarp();
-      // one box per lane: box 0 of a stage is A's, the others are B's 64-column blocks
-      constexpr int kBoxes = 1 + BN / 64;
-      for (int t = lane; t < early * kBoxes; t += 32) {
-        const int st = t / kBoxes, j = t - st * kBoxes;
-        uint8_t *sa = smem + st * L::kStageBytes;
-        if (j == 0) tma_load_3d(sa, &tmA, &full[st], st * BK, rb * BM, b);
-        else tma_load_3d(sa + L::kABytes + (j - 1) * (BK * 128), &tmB, &full[st], nb * BN + (j - 1) * 64, st * BK, bb);
-      }
-      if (lane == 0) WTC_STAMP(p, TS_TMA0);
-    }
   }
   if (warp == 1) {
     if (PAIR) { tmem_alloc_pair(tmem_slot, 2 * BN); tmem_relinquish_pair(); }
@@ -346,12 +315,37 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   if (CLUSTERED) cluster_arrive_release();
   if (PAIR) cluster_wait_acquire();
   if (threadIdx.x == 0) WTC_STAMP(p, TS_SETUP);
-  // Programmatic dependent launch: everything above overlapped the tail of the previous
-  // kernel on the stream; from here on global memory is touched, so wait for that kernel
-  // to finish, and let the next one start its own set-up as our CTAs retire.
-  grid_dependency_wait();
-  grid_launch_dependents();
-  if (threadIdx.x == 0) WTC_STAMP(p, TS_DEPS);
+  grid_launch_dependents();            // the next kernel on the stream may start its own set-up as our CTAs retire
+
+  // While the producer waits for the previous kernel, warp 2 (an epilogue warp, idle until the
+  // first accumulator is complete) asks for the first tile's operands to be brought into L2.
+  // Shared memory may not be filled yet (the operands may be that kernel's output), but an L2
+  // prefetch is harmless, and turns the cold start of the pipeline into L2 hits.  The first
+  // TMA instruction of a launch stalls its thread until the tensor map has been fetched
+  // (well over a microsecond), and each further one costs its thread a hundred cycles or
+  // more, which is why this is neither the producer's job nor part of the set-up that the
+  // whole CTA waits for.
+  // The CTAs that share a panel split its K blocks: A[rb] among the cluster, B[nb] among the clusters.
+  if (CLUSTER && !PAIR && warp == 2 && first < p.num_items) {
+    int b, rb, nb; decode(first, b, rb, nb);
+    const int bb = p.b_batched ? b : 0;
+    const int cl = static_cast<int>(cluster_n);
+    const int groups = stride < p.num_kb ? stride : p.num_kb;
+    for (int base = 0; base < p.num_kb; base += 4) {
+      const int kb = base + lane;
+      if (lane < 4 && kb < p.num_kb) {
+        if (kb % cl == nb || kb < early) tma_prefetch_l2_3d(&tmA, kb * BK, rb * BM, b);
+        if (kb % groups == first % groups || kb < early) {
+          if (p.b_blocks) tma_prefetch_l2_4d(&tmB, 0, kb * BK, nb * (BN / 64), bb);
+          else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_prefetch_l2_3d(&tmB, nb * BN + j * 64, kb * BK, bb);
+          }
+        }
+      }
+      __syncwarp();
+    }
+  }
 
   // hands accumulator buffer `ab` back to the MMA thread (of the pair's even CTA)
   auto release_accumulator = [&](int ab) {
@@ -692,11 +686,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-#ifdef WTC_EXP_EVICT_FIRST
-            if (valid > 0 && row0 < p.M) tma_store_3d_hint(&tmO, stg, col0, row0, b, l2_policy_evict_first());
-#else
             if (valid > 0 && row0 < p.M) tma_store_3d(&tmO, stg, col0, row0, b);
-#endif
             tma_store_commit();
             if (lead) WTC_STAMP(p, TS_STAGED);
             tma_store_wait_read();
@@ -708,9 +698,30 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   } else {
   if (RELAY) setmaxnreg_dec<48>();
   if (warp == 0) {
-    // ======================= TMA producer: one thread =======================
+    // ======================= TMA producer ====================================
+    // programmatic dependent launch: the operands may be the previous kernel's output
+    grid_dependency_wait();
+    if (lane == 0) WTC_STAMP(p, TS_DEPS);
+    if (!PAIR && first < p.num_items) {
+      // the first stages of the first tile, one box per lane (box 0 of a stage is A's, the
+      // others are B's 64-column blocks): twenty copies leave in the time of one
+      int b, rb, nb; decode(first, b, rb, nb);
+      const int bb = p.b_batched ? b : 0;
+      if (lane == 0)
+        for (int s = 0; s < early; ++s) mbar_expect_tx(&full[s], L::kStageBytes);
+      __syncwarp();
+      const int boxes = p.b_blocks ? 2 : 1 + BN / 64;
+      for (int t = lane; t < early * boxes; t += 32) {
+        const int st = t / boxes, j = t - st * boxes;
+        uint8_t *sa = smem + st * L::kStageBytes;
+        if (j == 0) tma_load_3d(sa, &tmA, &full[st], st * BK, rb * BM, b);
+        else if (p.b_blocks) tma_load_4d(sa + L::kABytes, &tmB, &full[st], 0, st * BK, nb * (BN / 64), bb);
+        else tma_load_3d(sa + L::kABytes + (j - 1) * (BK * 128), &tmB, &full[st], nb * BN + (j - 1) * 64, st * BK, bb);
+      }
+      if (lane == 0) WTC_STAMP(p, TS_TMA0);
+    }
     if (lane == 0) {
-      // (the first `early` stages of the first tile are already on their way)
+      // the rest, one thread: (the first `early` stages of the first tile are already on their way)
       uint32_t s = early == STAGES ? 0 : early, ph = early == STAGES ? 1 : 0;
       bool ok = true;
       for (int w = first; w < p.num_items && ok; w += stride) {
@@ -724,9 +735,12 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             uint8_t *sb = sa + L::kABytes;
             if (is_leader) mbar_expect_tx(&full[s], 2 * L::kStageBytes);
             tma_load_3d_pair(sa, &tmA, &full[s], kb * BK, rb * BM, b);
+            if (p.b_blocks) tma_load_4d_pair(sb, &tmB, &full[s], 0, kb * BK, nb * (BN / 64) + static_cast<int>(pair_rank) * (BN / 128), bb);
+            else {
 #pragma unroll
-            for (int j = 0; j < BN / 128; ++j)
-              tma_load_3d_pair(sb + j * (BK * 128), &tmB, &full[s], nb * BN + static_cast<int>(pair_rank) * (BN / 2) + j * 64, kb * BK, bb);
+              for (int j = 0; j < BN / 128; ++j)
+                tma_load_3d_pair(sb + j * (BK * 128), &tmB, &full[s], nb * BN + static_cast<int>(pair_rank) * (BN / 2) + j * 64, kb * BK, bb);
+            }
             if (w == first && kb == 0) WTC_STAMP(p, TS_TMA0);
           } else {
             load_stage(s, kb, rb, nb, b, bb);

@@ -19,6 +19,7 @@ struct TcParams {
   int num_ru;      // row units per batch: row blocks, or pairs of row blocks (set by the launcher)
   int num_items;   // work items: cluster mode batch*num_rb, tiled mode batch*num_rb*num_nb
   int b_batched;   // B has its own batch dimension
+  int b_blocks;    // tmB is the rank-4 view [batch][N/64][K][64] (N a multiple of 64): one copy per stage instead of one per 64 columns
   int group_rb;    // tiled mode: row blocks per rasterisation group
   int out_f32;     // f32 probabilities (else f16)
   int pair_mode;   // tiled flavour: 0 choose, 1 never pair CTAs, 2 pair whenever the shape allows

@@ -247,13 +247,13 @@ MapTable *map_table() {
   return t;
 }
 
-// rank-3 f16 tensor (d0 innermost, contiguous), 128-byte swizzle, zero fill
+// rank-3 tensor (d0 innermost, contiguous), or rank-4 when d3 > 0; f16 unless f32; 128-byte swizzle, zero fill
 int get_map(const void *ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1_bytes, uint64_t s2_bytes, uint32_t b0,
-            uint32_t b1, CUtensorMap *out, bool f32 = false) {
-  const MapKey key{ptr, d0, d1, d2, s1_bytes, s2_bytes, b0 | (f32 ? 0x80000000u : 0u), b1};
+            uint32_t b1, CUtensorMap *out, bool f32 = false, uint64_t d3 = 0, uint64_t s3_bytes = 0, uint32_t b2 = 1) {
+  const MapKey key{ptr, d0, d1, d2 ^ (d3 << 32), s1_bytes, s2_bytes ^ (s3_bytes << 20), b0 | (f32 ? 0x80000000u : 0u), b1 | (b2 << 16)};
   MapTable *tab = map_table();
   uint64_t h = reinterpret_cast<uintptr_t>(ptr) * 0x9E3779B97F4A7C15ull;
-  h ^= (d0 * 31 + d1) * 0xC2B2AE3D27D4EB4Full + d2 + s1_bytes + (static_cast<uint64_t>(key.b0) << 20) + b1;
+  h ^= (d0 * 31 + d1) * 0xC2B2AE3D27D4EB4Full + key.d2 + s1_bytes + (static_cast<uint64_t>(key.b0) << 20) + key.b1;
   MapEntry *slot = tab ? &tab->e[(h >> 40) % kMapSlots] : nullptr;
   if (slot && slot->used && slot->key == key) { *out = slot->map; return WTC_OK; }
   {
@@ -261,21 +261,38 @@ int get_map(const void *ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1_
     int rc = get_encoder();
     if (rc) return rc;
   }
-  cuuint64_t dims[3] = {d0, d1, d2};
-  cuuint64_t strides[2] = {s1_bytes, s2_bytes};
-  cuuint32_t box[3] = {b0, b1, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
+  const cuuint32_t rank = d3 ? 4 : 3;
+  cuuint64_t dims[4] = {d0, d1, d2, d3};
+  cuuint64_t strides[3] = {s1_bytes, s2_bytes, s3_bytes};
+  cuuint32_t box[4] = {b0, b1, b2, 1};
+  if (!d3) box[2] = 1;
+  cuuint32_t estr[4] = {1, 1, 1, 1};
   CUtensorMap m;
-  CUresult cr = g_encode(&m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(ptr), dims, strides, box, estr,
+  CUresult cr = g_encode(&m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, rank, const_cast<void *>(ptr), dims, strides, box, estr,
                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (cr != CUDA_SUCCESS)
-    return fail(WTC_E_CUDA, "cuTensorMapEncodeTiled failed (%d) for dims=(%llu,%llu,%llu) strides=(%llu,%llu) box=(%u,%u)",
-                (int)cr, (unsigned long long)d0, (unsigned long long)d1, (unsigned long long)d2,
-                (unsigned long long)s1_bytes, (unsigned long long)s2_bytes, b0, b1);
+    return fail(WTC_E_CUDA, "cuTensorMapEncodeTiled failed (%d) for rank %u dims=(%llu,%llu,%llu,%llu) strides=(%llu,%llu,%llu) box=(%u,%u,%u)",
+                (int)cr, rank, (unsigned long long)d0, (unsigned long long)d1, (unsigned long long)d2, (unsigned long long)d3,
+                (unsigned long long)s1_bytes, (unsigned long long)s2_bytes, (unsigned long long)s3_bytes, b0, b1, b2);
   if (slot) { slot->key = key; slot->map = m; slot->used = true; }
   *out = m;
   return WTC_OK;
+}
+
+// The map of B [batch][K][N] (N contiguous).  When N is a multiple of 64 it is the rank-4 view
+// [batch][N/64][K][64]: one copy then brings `blocks` 64-column blocks of a K block, each laid
+// out as the tensor core wants it (64 k-rows x 128 bytes); otherwise one copy per 64 columns.
+int get_map_b(const void *B, const Resolved &r, int blocks, CUtensorMap *out, int *b_blocks) {
+  const wtc_chain_desc &d = r.d;
+  const uint64_t nbatch = r.b_batched ? d.batch : 1;
+  const uint64_t bstride = (r.b_batched ? d.b_batch_stride : d.K * d.ldb) * 2;
+  if (d.N % 64 == 0) {
+    *b_blocks = 1;
+    return get_map(B, 64, d.K, d.N / 64, d.ldb * 2, 128, 64, wtc::kTcBlockK, out, false, nbatch, bstride, blocks);
+  }
+  *b_blocks = 0;
+  return get_map(B, d.N, d.K, nbatch, d.ldb * 2, bstride, 64, wtc::kTcBlockK, out);
 }
 
 int num_sms() {
@@ -371,7 +388,8 @@ int launch_resolved(Resolved &r, const void *A, const void *B, void *Out, void *
     float *E = C32 + rows * d.N, *mx = E + rows * d.N, *sum = mx + rows;
     CUtensorMap tmA, tmB, tmC;
     int rc = get_map(A, d.K, d.M, d.batch, d.lda * 2, d.a_batch_stride * 2, wtc::kTcBlockK, wtc::kTcBlockM, &tmA);
-    if (!rc) rc = get_map(B, d.N, d.K, r.b_batched ? d.batch : 1, d.ldb * 2, (r.b_batched ? d.b_batch_stride : d.K * d.ldb) * 2, 64, wtc::kTcBlockK, &tmB);
+    int b_blocks = 0;
+    if (!rc) rc = get_map_b(B, r, r.bn / 64, &tmB, &b_blocks);
     if (!rc) rc = get_map(C32, d.N, d.M, d.batch, d.N * 4, d.M * d.N * 4, 32, 32, &tmC, true);
     if (rc) return rc;
     wtc::TcParams p;
@@ -379,6 +397,7 @@ int launch_resolved(Resolved &r, const void *A, const void *B, void *Out, void *
     p.batch = d.batch; p.M = (int)d.M; p.N = (int)d.N; p.K = (int)d.K;
     p.num_rb = r.num_rb; p.num_nb = r.num_nb; p.num_kb = r.num_kb;
     p.b_batched = r.b_batched;
+    p.b_blocks = b_blocks;
     p.group_rb = 16;
     p.round_logits_f16 = d.acc_dtype == WTC_F16;
     p.scale = d.scale;
@@ -404,8 +423,11 @@ int launch_resolved(Resolved &r, const void *A, const void *B, void *Out, void *
     CUtensorMap tmA, tmB, tmO;
     int rc = get_map(A, d.K, d.M, d.batch, d.lda * 2, d.a_batch_stride * 2, wtc::kTcBlockK, wtc::kTcBlockM, &tmA);
     if (rc) return rc;
-    rc = get_map(B, d.N, d.K, r.b_batched ? d.batch : 1, d.ldb * 2, (r.b_batched ? d.b_batch_stride : d.K * d.ldb) * 2, 64,
-                 wtc::kTcBlockK, &tmB);
+    // (a CTA pair loads half of the tile's columns per CTA: the variant decides the box)
+    const int pm = (d.flags & WTC_FLAG_NO_PAIR) ? 1 : ((d.flags & WTC_FLAG_PAIR) ? 2 : 0);
+    const wtc::TcVariant v = wtc::tc_choose_variant(tiled, r.bn, d.out_dtype == WTC_F32, d.batch, r.num_rb, r.num_kb, tiled ? 1 : r.num_nb, 0, pm, sms, 0);
+    int b_blocks = 0;
+    rc = get_map_b(B, r, v.pair ? r.bn / 128 : r.bn / 64, &tmB, &b_blocks);
     if (rc) return rc;
     const bool out32 = d.out_dtype == WTC_F32;
     rc = out32 ? get_map(Out, d.N, d.M, d.batch, d.ldo * 4, d.o_batch_stride * 4, 32, 32, &tmO, true)
@@ -417,6 +439,7 @@ int launch_resolved(Resolved &r, const void *A, const void *B, void *Out, void *
     p.batch = d.batch; p.M = (int)d.M; p.N = (int)d.N; p.K = (int)d.K;
     p.num_rb = r.num_rb; p.num_nb = r.num_nb; p.num_kb = r.num_kb;
     p.b_batched = r.b_batched;
+    p.b_blocks = b_blocks;
     p.group_rb = 16;
     p.round_logits_f16 = d.acc_dtype == WTC_F16;
     p.c2 = d.scale * 1.4426950408889634f;
