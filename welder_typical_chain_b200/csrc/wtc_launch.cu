@@ -13,6 +13,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <ctime>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -627,18 +628,18 @@ int wtc_matmul_softmax_host(const wtc_chain_desc *desc, const void *hostA, const
       }
     }
   }
-  constexpr int kMaxSlabs = 8;
-  // two copy-in streams, used alternately: the set-up of one host-to-device copy runs under the
-  // transfer of the other (a lone stream of 1-2 MB copies reaches about half of the link's rate)
-  struct Lanes { cudaStream_t in[2] = {nullptr, nullptr}, run = nullptr, out = nullptr; cudaEvent_t b_in = nullptr, a_in[kMaxSlabs] = {}, done[kMaxSlabs] = {}; int dev = -1; };
+  constexpr int kMaxSlabs = 16;
+  // Streams: one for the copies in (two concurrent host-to-device copies only get in each
+  // other's way), one for the kernels, one for the copies back, so that the link is busy in
+  // both directions while the kernels of the slab in between run.
+  struct Lanes { cudaStream_t in = nullptr, run = nullptr, out = nullptr; cudaEvent_t a_in[kMaxSlabs] = {}, done[kMaxSlabs] = {}; int dev = -1; };
   thread_local Lanes ln;
   if (ln.dev != dev) {
     ln = Lanes();
-    for (cudaStream_t *st : {&ln.in[0], &ln.in[1], &ln.run, &ln.out}) {
+    for (cudaStream_t *st : {&ln.in, &ln.run, &ln.out}) {
       e = cudaStreamCreateWithFlags(st, cudaStreamNonBlocking);
       if (e != cudaSuccess) return cuda_fail(e, "cudaStreamCreate");
     }
-    e = cudaEventCreateWithFlags(&ln.b_in, cudaEventDisableTiming);
     for (int i = 0; i < kMaxSlabs && e == cudaSuccess; ++i) {
       e = cudaEventCreateWithFlags(&ln.a_in[i], cudaEventDisableTiming);
       if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ln.done[i], cudaEventDisableTiming);
@@ -647,61 +648,78 @@ int wtc_matmul_softmax_host(const wtc_chain_desc *desc, const void *hostA, const
     ln.dev = dev;
   }
 
-  // ---- slabs: about 6 MB of A + Out traffic each (measured on PCIe 5 x16: two or three slabs are best for
-  //      17 MB, each slab costs ~10 us of host enqueue time), at most kMaxSlabs; rows in multiples of the 128-row tile
-  const bool by_batch = d.batch > 1;
-  const int64_t units = by_batch ? d.batch : (d.M + wtc::kTcBlockM - 1) / wtc::kTcBlockM;
-  int64_t slabs = static_cast<int64_t>((a_bytes + o_bytes) / (6u << 20));
-  if (slabs < 1) slabs = 1;
-  if (slabs > kMaxSlabs) slabs = kMaxSlabs;
-  if (const char *ev = getenv("WTC_HOST_SLABS")) slabs = atoi(ev) > 0 ? atoi(ev) : 1;
-  if (slabs > kMaxSlabs) slabs = kMaxSlabs;
-  if (slabs > units) slabs = units;
-  const int64_t per = (units + slabs - 1) / slabs;
-
-  e = cudaMemcpyAsync(bufs[1].p, hostB, b_bytes, cudaMemcpyHostToDevice, ln.in[0]);
-  if (e == cudaSuccess) e = cudaEventRecord(ln.b_in, ln.in[0]);
-  if (e == cudaSuccess) e = cudaStreamWaitEvent(ln.run, ln.b_in, 0);
-  if (e != cudaSuccess) return cuda_fail(e, "copy of B to the device");
-  int n = 0;
-  for (int64_t u0 = 0; u0 < units; u0 += per, ++n) {
-    const int64_t u1 = u0 + per < units ? u0 + per : units;
-    wtc_chain_desc sd = d;
-    size_t a_off, o_off, a_len, o_len, b_off = 0;
-    if (by_batch) {
-      sd.batch = static_cast<int32_t>(u1 - u0);
-      a_off = static_cast<size_t>(u0) * d.a_batch_stride * in_sz;  a_len = static_cast<size_t>(u1 - u0) * d.a_batch_stride * in_sz;
-      o_off = static_cast<size_t>(u0) * d.o_batch_stride * out_sz; o_len = static_cast<size_t>(u1 - u0) * d.o_batch_stride * out_sz;
-      if (r.b_batched) b_off = static_cast<size_t>(u0) * d.b_batch_stride * in_sz;
-      else sd.b_batch_stride = -1;
-    } else {
-      const int64_t r0 = u0 * wtc::kTcBlockM, r1 = u1 * wtc::kTcBlockM < d.M ? u1 * wtc::kTcBlockM : d.M;
-      sd.M = r1 - r0;
-      sd.a_batch_stride = 0; sd.o_batch_stride = 0;
-      a_off = static_cast<size_t>(r0) * d.lda * in_sz;  a_len = static_cast<size_t>(r1 - r0) * d.lda * in_sz;
-      o_off = static_cast<size_t>(r0) * d.ldo * out_sz; o_len = static_cast<size_t>(r1 - r0) * d.ldo * out_sz;
+  // ---- slabs: rows in multiples of the 128-row tile (whole batches of a batched chain), about
+  //      4 MB of A each.  With equal slabs the call takes (copy in of everything) + (one slab's
+  //      kernels and copy back) + a hand-over between the engines per slab, which was measured at
+  //      about 20 us on PCIe 5 x16: two to four slabs are best for 8 MB of A, eight already lose.
+  //      A batched B travels with its slab.  The slab schedule of the last descriptor is kept,
+  //      so a caller that repeats a shape resolves it once.
+  struct Slab { Resolved r; size_t a_off, a_len, o_off, o_len, b_off, b_len; };
+  struct HostPlan { wtc_chain_desc key; int dev = -1; int slab_env = 0; int n = 0; Slab slabs[kMaxSlabs]; };
+  thread_local HostPlan hp;
+  int slab_env = 0;
+  if (const char *ev = getenv("WTC_HOST_SLABS")) slab_env = atoi(ev) > 0 ? atoi(ev) : 1;
+  if (hp.dev != dev || hp.slab_env != slab_env || std::memcmp(&hp.key, &d, sizeof(d)) != 0) {
+    hp.dev = -1;
+    const bool by_batch = d.batch > 1;
+    const int64_t units = by_batch ? d.batch : (d.M + wtc::kTcBlockM - 1) / wtc::kTcBlockM;
+    int64_t slabs = slab_env ? slab_env : static_cast<int64_t>(a_bytes >> 22);
+    if (slabs < 1) slabs = 1;
+    if (slabs > kMaxSlabs) slabs = kMaxSlabs;
+    if (slabs > units) slabs = units;
+    const int64_t per = (units + slabs - 1) / slabs;
+    int n = 0;
+    for (int64_t u0 = 0; u0 < units; u0 += per, ++n) {
+      const int64_t u1 = u0 + per < units ? u0 + per : units;
+      Slab &sl = hp.slabs[n];
+      wtc_chain_desc sd = d;
+      sl.b_off = 0; sl.b_len = 0;
+      if (by_batch) {
+        sd.batch = static_cast<int32_t>(u1 - u0);
+        sl.a_off = static_cast<size_t>(u0) * d.a_batch_stride * in_sz;  sl.a_len = static_cast<size_t>(u1 - u0) * d.a_batch_stride * in_sz;
+        sl.o_off = static_cast<size_t>(u0) * d.o_batch_stride * out_sz; sl.o_len = static_cast<size_t>(u1 - u0) * d.o_batch_stride * out_sz;
+        if (r.b_batched) { sl.b_off = static_cast<size_t>(u0) * d.b_batch_stride * in_sz; sl.b_len = static_cast<size_t>(u1 - u0) * d.b_batch_stride * in_sz; }
+        else sd.b_batch_stride = -1;
+      } else {
+        const int64_t r0 = u0 * wtc::kTcBlockM, r1 = u1 * wtc::kTcBlockM < d.M ? u1 * wtc::kTcBlockM : d.M;
+        sd.M = r1 - r0;
+        sd.a_batch_stride = 0; sd.o_batch_stride = 0;
+        sl.a_off = static_cast<size_t>(r0) * d.lda * in_sz;  sl.a_len = static_cast<size_t>(r1 - r0) * d.lda * in_sz;
+        sl.o_off = static_cast<size_t>(r0) * d.ldo * out_sz; sl.o_len = static_cast<size_t>(r1 - r0) * d.ldo * out_sz;
+      }
+      rc = resolve(&sd, sl.r);
+      if (rc) return rc;
     }
-    Resolved sr;
-    rc = resolve(&sd, sr);
-    if (rc) return rc;
-    cudaStream_t in = ln.in[(n + 1) & 1];     // slab 0 goes beside B, not behind it
-    e = cudaMemcpyAsync(static_cast<char *>(bufs[0].p) + a_off, static_cast<const char *>(hostA) + a_off, a_len, cudaMemcpyHostToDevice, in);
-    if (e == cudaSuccess) e = cudaEventRecord(ln.a_in[n], in);
+    hp.n = n; hp.key = d; hp.slab_env = slab_env; hp.dev = dev;
+  }
+
+#ifdef WTC_BRINGUP
+  timespec ts0, ts1, ts2;
+  clock_gettime(CLOCK_MONOTONIC, &ts0);
+#endif
+  if (!r.b_batched || d.batch == 1) {
+    e = cudaMemcpyAsync(bufs[1].p, hostB, b_bytes, cudaMemcpyHostToDevice, ln.in);
+    if (e != cudaSuccess) return cuda_fail(e, "copy of B to the device");
+  }
+  for (int n = 0; n < hp.n; ++n) {
+    Slab &sl = hp.slabs[n];
+    e = cudaSuccess;
+    if (sl.b_len) e = cudaMemcpyAsync(static_cast<char *>(bufs[1].p) + sl.b_off, static_cast<const char *>(hostB) + sl.b_off, sl.b_len, cudaMemcpyHostToDevice, ln.in);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(static_cast<char *>(bufs[0].p) + sl.a_off, static_cast<const char *>(hostA) + sl.a_off, sl.a_len, cudaMemcpyHostToDevice, ln.in);
+    if (e == cudaSuccess) e = cudaEventRecord(ln.a_in[n], ln.in);
     if (e == cudaSuccess) e = cudaStreamWaitEvent(ln.run, ln.a_in[n], 0);
-    if (e != cudaSuccess) return cuda_fail(e, "copy of A to the device");
-    rc = launch_resolved(sr, static_cast<char *>(bufs[0].p) + a_off, static_cast<char *>(bufs[1].p) + b_off,
-                         static_cast<char *>(bufs[2].p) + o_off, bufs[3].p, bufs[3].cap, nullptr, 0, ln.run, nullptr);
+    if (e != cudaSuccess) return cuda_fail(e, "copy of the operands to the device");
+    rc = launch_resolved(sl.r, static_cast<char *>(bufs[0].p) + sl.a_off, static_cast<char *>(bufs[1].p) + sl.b_off,
+                         static_cast<char *>(bufs[2].p) + sl.o_off, bufs[3].p, bufs[3].cap, nullptr, 0, ln.run, nullptr);
     if (rc) return rc;
     e = cudaEventRecord(ln.done[n], ln.run);
     if (e == cudaSuccess) e = cudaStreamWaitEvent(ln.out, ln.done[n], 0);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(static_cast<char *>(hostOut) + o_off, static_cast<char *>(bufs[2].p) + o_off, o_len, cudaMemcpyDeviceToHost, ln.out);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(static_cast<char *>(hostOut) + sl.o_off, static_cast<char *>(bufs[2].p) + sl.o_off, sl.o_len, cudaMemcpyDeviceToHost, ln.out);
     if (e != cudaSuccess) return cuda_fail(e, "copy of the result to the host");
   }
-  // the next call's first copy must not overtake this call's last kernel or read-back
-  e = cudaStreamWaitEvent(ln.in[0], ln.done[n - 1], 0);
-  if (e == cudaSuccess) e = cudaStreamWaitEvent(ln.in[1], ln.done[n - 1], 0);
-  if (e != cudaSuccess) return cuda_fail(e, "cudaStreamWaitEvent");
-  // the device status word rides back on the copy-out stream into pinned memory: one wait
+  // (the call returns only after the copy-back stream has drained, which waited for every kernel,
+  //  which waited for every copy in: the next call finds all three streams idle)
+  // the device status word rides back behind the last rows into pinned memory: one wait
   // covers the results and the status (no separate blocking read)
   thread_local int *host_status = nullptr;
   if (!host_status) {
@@ -712,7 +730,16 @@ int wtc_matmul_softmax_host(const wtc_chain_desc *desc, const void *hostA, const
   if (!dev_status) return fail(WTC_E_CUDA, "no status word");
   *host_status = 0;
   e = cudaMemcpyAsync(host_status, dev_status, sizeof(int), cudaMemcpyDeviceToHost, ln.out);
+#ifdef WTC_BRINGUP
+  clock_gettime(CLOCK_MONOTONIC, &ts1);
+#endif
   if (e == cudaSuccess) e = cudaStreamSynchronize(ln.out);
+#ifdef WTC_BRINGUP
+  clock_gettime(CLOCK_MONOTONIC, &ts2);
+  if (getenv("WTC_HOST_TRACE"))
+    fprintf(stderr, "host call: %d slabs, enqueue %.1f us, wait %.1f us\n", hp.n, (ts1.tv_sec - ts0.tv_sec) * 1e6 + (ts1.tv_nsec - ts0.tv_nsec) * 1e-3,
+            (ts2.tv_sec - ts1.tv_sec) * 1e6 + (ts2.tv_nsec - ts1.tv_nsec) * 1e-3);
+#endif
   if (e != cudaSuccess) return cuda_fail(e, "waiting for the results");
   if (*host_status != 0) cudaMemsetAsync(default_status(), 0, sizeof(int), ln.out);   // reported once, then cleared
   return status_result(*host_status);
