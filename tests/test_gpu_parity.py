@@ -346,7 +346,39 @@ def test_tile_choice_from_best_json_is_honoured(w, cuda_dev):
         ref = oracle.chain(A, B, 1 / 32)
         _check(_run(w, cuda_dev, A, B, 1 / 32, tiles=(128, 128, 64)), ref)
         _check(_run(w, cuda_dev, A, B, 1 / 32, tiles=(128, 256, 64)), ref)
-        _check(_run(w, cuda_dev, A, B, 1 / 32, tiles=(64, 128, 32)), ref)     # tileM / tileK replaced, tileN honoured
+        _check(_run(w, cuda_dev, A, B, 1 / 32, tiles=(64, 128, 32)), ref)     # tileM replaced, tileN and tileK honoured
+
+
+@pytest.mark.parametrize("tile_k", [32, 128])
+@pytest.mark.parametrize("M,N,K,tile_n,flags,used_k", [
+    (777, 1024, 200, 128, 0, None),          # cluster of 8 x 128 columns, ragged M, K tail shorter than a stage
+    (300, 520, 72, 128, 0, None),            # ragged N and K
+    (4096, 1024, 1024, 256, 0, {128: 64}),   # cluster of 4 x 256 columns: 128-deep stages have no kernel there
+    (256, 2304, 128, 256, 0, None),          # two-pass tiled schedule, 256-column tiles
+    (300, 1024, 256, 128, "tiled", None),    # two-pass tiled schedule, 128-column tiles
+    (130, 520, 40, 256, "tiled", None),      # K shorter than one 128-deep stage: the second box of A is all padding
+])
+def test_stage_depth_from_best_json_is_honoured(w, cuda_dev, M, N, K, tile_n, flags, used_k, tile_k):
+    """tileK = 32 / 128 is the K depth of one pipeline stage (64-byte-swizzled A rows; two 64-column
+    blocks of A per stage); the plan reports the depth it runs and whether it replaced the request."""
+    fl = w.FLAG_FORCE_TILED if flags == "tiled" else 0
+    want_k = (used_k or {}).get(tile_k, tile_k)
+    plan = w.plan_query(w.make_desc(1, M, N, K, flags=fl, tile_m=128, tile_n=tile_n, tile_k=tile_k))
+    assert (plan.tile_m, plan.tile_n, plan.tile_k) == (128, tile_n, want_k)
+    assert plan.tile_substituted == (0 if want_k == tile_k else 1)
+    A = oracle.normal((M, K), 71)
+    B = oracle.normal((K, N), 72)
+    _check(_run(w, cuda_dev, A, B, 0.05, flags=fl, tiles=(128, tile_n, tile_k)), oracle.chain(A, B, 0.05))
+
+
+def test_stage_depth_batched_many_tiles(w, cuda_dev):
+    """Several tiles per CTA and a B per batch with 32- and 128-deep stages (the operand ring runs on across tiles)."""
+    A = oracle.normal((3, 5000, 160), 73)
+    B = oracle.normal((3, 160, 1024), 74)
+    ref = np.stack([oracle.chain(A[b], B[b], 0.08) for b in range(3)])
+    for tile_k in (32, 128):
+        _check(_run(w, cuda_dev, A, B, 0.08, tiles=(128, 128, tile_k)), ref)
+    _check(_run(w, cuda_dev, A, B, 0.08, tiles=(128, 256, 32)), ref)
 
 
 def test_narrow_rows_take_the_128_column_tile(w, cuda_dev):

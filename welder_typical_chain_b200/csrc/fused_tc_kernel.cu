@@ -64,12 +64,18 @@ constexpr int kThreadsFor(int epi) { return epi == EPI_SPLIT ? 320 : (epi == EPI
 constexpr uint32_t kALbo = 16, kASbo = 1024, kAKstep = 32;
 constexpr uint32_t kBLbo = 8192, kBSbo = 1024, kBKstep = 2048;
 
-template <int BN, int STAGES, bool CLUSTER, int EPI, bool PAIR, bool OUT32>
+// KD: the K depth of one pipeline stage (the schedule's tileK): 64 by default; 32 and 128 for
+// the eight-warp epilogue forms.  A's 128 rows are then staged as 64-byte rows with the 64-byte
+// swizzle (32), or as two 128-byte-swizzled blocks of 64 columns side by side (128); B's
+// 64-column blocks simply have KD k-rows.
+template <int BN, int STAGES, bool CLUSTER, int EPI, bool PAIR, bool OUT32, int KD = kTcBlockK>
 struct SmemLayout {
   static constexpr bool RELAY = EPI == EPI_RELAY;
   static constexpr bool SINGLE = EPI == EPI_SINGLE;
-  static constexpr int kABytes = BM * BK * 2;
-  static constexpr int kBBytes = BK * BN * 2 / (PAIR ? 2 : 1);     // a CTA pair splits B's columns between its two CTAs
+  static_assert(KD == 32 || KD == 64 || KD == 128, "stage depth: 32, 64 or 128");
+  static_assert(KD == 64 || (EPI == EPI_SPLIT && !PAIR && !OUT32), "other stage depths: eight-warp epilogue, unpaired, f16 output");
+  static constexpr int kABytes = BM * KD * 2;
+  static constexpr int kBBytes = KD * BN * 2 / (PAIR ? 2 : 1);     // a CTA pair splits B's columns between its two CTAs
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kHalfCols = SINGLE ? BN / 4 : BN / 2;         // columns per epilogue thread
   // 32-row x 64-column f16 (32 x 32 f32) staging tiles per storing warp: two let a warp's
@@ -194,11 +200,13 @@ __device__ __forceinline__ void scale_pack(const uint32_t (&r)[32], float f, uin
   for (int i = 0; i < 32; i += 2) h[i >> 1] = pack_f16x2(__uint_as_float(r[i]) * f, __uint_as_float(r[i + 1]) * f);
 }
 
-template <int BN, int STAGES, bool CLUSTER, int EPI, bool PAIR, bool OUT32>
+template <int BN, int STAGES, bool CLUSTER, int EPI, bool PAIR, bool OUT32, int KD>
 __global__ void __launch_bounds__(kThreadsFor(EPI), 1)
 fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmO, const TcParams p) {
-  using L = SmemLayout<BN, STAGES, CLUSTER, EPI, PAIR, OUT32>;
+  using L = SmemLayout<BN, STAGES, CLUSTER, EPI, PAIR, OUT32, KD>;
+  constexpr int BK = KD;                // K depth of a stage (hides the default of the same name)
+  constexpr int A_BOXES = KD == 128 ? 2 : 1;   // A's copies per stage: a box is at most one swizzle span (64 columns) wide
   constexpr bool RELAY = L::RELAY;
   constexpr bool SINGLE = L::SINGLE;
   constexpr int OUT_TILES = L::kOutTiles;
@@ -272,6 +280,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     uint8_t *sb = sa + L::kABytes;
     mbar_expect_tx(&full[s], L::kStageBytes);
     tma_load_3d(sa, &tmA, &full[s], kb * BK, rb * BM, b);
+    if (A_BOXES == 2) tma_load_3d(sa + BM * 128, &tmA, &full[s], kb * BK + 64, rb * BM, b);
     if (p.b_blocks) tma_load_4d(sb, &tmB, &full[s], 0, kb * BK, nb * (BN / 64), bb);
     else {
 #pragma unroll
@@ -326,7 +335,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   // more, which is why this is neither the producer's job nor part of the set-up that the
   // whole CTA waits for.
   // The CTAs that share a panel split its K blocks: A[rb] among the cluster, B[nb] among the clusters.
-  if (CLUSTER && !PAIR && warp == 2 && first < p.num_items) {
+  if (CLUSTER && !PAIR && KD == kTcBlockK && warp == 2 && first < p.num_items) {
     int b, rb, nb; decode(first, b, rb, nb);
     const int bb = p.b_batched ? b : 0;
     const int cl = static_cast<int>(cluster_n);
@@ -710,13 +719,13 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       if (lane == 0)
         for (int s = 0; s < early; ++s) mbar_expect_tx(&full[s], L::kStageBytes);
       __syncwarp();
-      const int boxes = p.b_blocks ? 2 : 1 + BN / 64;
+      const int boxes = A_BOXES + (p.b_blocks ? 1 : BN / 64);
       for (int t = lane; t < early * boxes; t += 32) {
         const int st = t / boxes, j = t - st * boxes;
         uint8_t *sa = smem + st * L::kStageBytes;
-        if (j == 0) tma_load_3d(sa, &tmA, &full[st], st * BK, rb * BM, b);
+        if (j < A_BOXES) tma_load_3d(sa + j * (BM * 128), &tmA, &full[st], st * BK + j * 64, rb * BM, b);
         else if (p.b_blocks) tma_load_4d(sa + L::kABytes, &tmB, &full[st], 0, st * BK, nb * (BN / 64), bb);
-        else tma_load_3d(sa + L::kABytes + (j - 1) * (BK * 128), &tmB, &full[st], nb * BN + (j - 1) * 64, st * BK, bb);
+        else tma_load_3d(sa + L::kABytes + (j - A_BOXES) * (BK * 128), &tmB, &full[st], nb * BN + (j - A_BOXES) * 64, st * BK, bb);
       }
       if (lane == 0) WTC_STAMP(p, TS_TMA0);
     }
@@ -757,8 +766,9 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       constexpr uint32_t idesc = umma_idesc_f16_f32(PAIR ? 2 * BM : BM, BN, /*a_mn_major=*/0, /*b_mn_major=*/1);
       const uint16_t pair_mask = static_cast<uint16_t>(3u << leader_rank);
       // everything of the two operand descriptors but the address, which is added per stage
-      const uint64_t a_desc0 = umma_smem_desc_sw128(smem_u32(smem), kALbo, kASbo);
-      const uint64_t b_desc0 = umma_smem_desc_sw128(smem_u32(smem) + L::kABytes, kBLbo, kBSbo);
+      // (A with 64-byte rows: 64-byte swizzle, 8-row groups 512 B apart; B's 64-column blocks are KD k-rows apart)
+      const uint64_t a_desc0 = KD == 32 ? umma_smem_desc_sw64(smem_u32(smem), kALbo, kASbo / 2) : umma_smem_desc_sw128(smem_u32(smem), kALbo, kASbo);
+      const uint64_t b_desc0 = umma_smem_desc_sw128(smem_u32(smem) + L::kABytes, KD * 128, kBSbo);
       uint32_t s = 0, ph = 0;
       uint32_t landed = 0;            // the next stage's barrier was already seen complete
       WTC_STAMP(p, TS_MMA_READY);
@@ -780,7 +790,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           for (int k = 0; k < BK / 16; ++k) {
             if (PAIR) umma_f16_ss_pair(d_tmem, da, db, idesc, (kb | k) != 0);
             else umma_f16_ss(d_tmem, da, db, idesc, (kb | k) != 0);
-            da += kAKstep >> 4;
+            da += (k == 3 ? BM * 128 - 3 * kAKstep : kAKstep) >> 4;   // after four steps: the second 64-column block of a 128-deep stage
             db += kBKstep >> 4;
           }
           // while those MMAs drain: has the next stage landed already?  (The ring runs on
@@ -1047,11 +1057,11 @@ struct DeviceFacts {
   int registers = 0;
 };
 
-template <int BN, int STAGES, bool CLUSTER, int EPI, bool PAIR, bool OUT32>
+template <int BN, int STAGES, bool CLUSTER, int EPI, bool PAIR, bool OUT32, int KD>
 cudaError_t launch_impl(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO, TcParams p,
                         int cluster_n, int num_sms, cudaStream_t s, TcLaunchInfo *info) {
-  using L = SmemLayout<BN, STAGES, CLUSTER, EPI, PAIR, OUT32>;
-  auto kern = fused_tc_kernel<BN, STAGES, CLUSTER, EPI, PAIR, OUT32>;
+  using L = SmemLayout<BN, STAGES, CLUSTER, EPI, PAIR, OUT32, KD>;
+  auto kern = fused_tc_kernel<BN, STAGES, CLUSTER, EPI, PAIR, OUT32, KD>;
   static DeviceFacts facts[64];   // per template instance, per device
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
@@ -1117,15 +1127,20 @@ cudaError_t launch_impl(const CUtensorMap &tmA, const CUtensorMap &tmB, const CU
 
 } // namespace
 
-// Every instantiated variant, once: X(BN, STAGES, CLUSTER, EPI, PAIR, OUT32).
-#define WTC_TC_VARIANTS(X)                                                                        \
-  X(128, 4, true, EPI_SPLIT, false, true) X(kTcBlockN, 3, true, EPI_SPLIT, false, true)            \
-  X(128, 4, true, EPI_SPLIT, false, false) X(kTcBlockN, 3, true, EPI_SPLIT, false, false)          \
-  X(kTcBlockN, 2, true, EPI_RELAY, false, false) X(kTcBlockN, 3, true, EPI_RELAY, false, false)    \
-  X(kTcBlockN, 4, true, EPI_SINGLE, false, false)                                                  \
-  X(128, 6, false, EPI_SPLIT, false, true) X(kTcBlockN, 4, false, EPI_SPLIT, false, true)          \
-  X(128, 6, false, EPI_SPLIT, false, false) X(kTcBlockN, 4, false, EPI_SPLIT, false, false)        \
-  X(kTcBlockN, 6, false, EPI_SPLIT, true, false)
+// Every instantiated variant, once: X(BN, STAGES, CLUSTER, EPI, PAIR, OUT32, KD).
+#define WTC_TC_VARIANTS(X)                                                                                \
+  X(128, 4, true, EPI_SPLIT, false, true, 64) X(kTcBlockN, 3, true, EPI_SPLIT, false, true, 64)            \
+  X(128, 4, true, EPI_SPLIT, false, false, 64) X(kTcBlockN, 3, true, EPI_SPLIT, false, false, 64)          \
+  X(kTcBlockN, 2, true, EPI_RELAY, false, false, 64) X(kTcBlockN, 3, true, EPI_RELAY, false, false, 64)    \
+  X(kTcBlockN, 4, true, EPI_SINGLE, false, false, 64)                                                      \
+  X(128, 6, false, EPI_SPLIT, false, true, 64) X(kTcBlockN, 4, false, EPI_SPLIT, false, true, 64)          \
+  X(128, 6, false, EPI_SPLIT, false, false, 64) X(kTcBlockN, 4, false, EPI_SPLIT, false, false, 64)        \
+  X(kTcBlockN, 6, false, EPI_SPLIT, true, false, 64)                                                       \
+  /* other stage depths (the schedule's tileK): eight-warp epilogue, f16 output */                        \
+  X(128, 8, true, EPI_SPLIT, false, false, 32) X(kTcBlockN, 6, true, EPI_SPLIT, false, false, 32)          \
+  X(128, 12, false, EPI_SPLIT, false, false, 32) X(kTcBlockN, 8, false, EPI_SPLIT, false, false, 32)       \
+  X(128, 2, true, EPI_SPLIT, false, false, 128)                                                            \
+  X(128, 3, false, EPI_SPLIT, false, false, 128) X(kTcBlockN, 2, false, EPI_SPLIT, false, false, 128)
 
 // Form choice.  Cluster flavour: f32 probabilities and 128-column tiles take the split
 // epilogue; 256-column f16 tiles take the relay when a CTA sees several tiles (its two groups
@@ -1133,29 +1148,40 @@ cudaError_t launch_impl(const CUtensorMap &tmA, const CUtensorMap &tmB, const CU
 // tile per storing warp), the single-tile form when every cluster fits the chip at once, the
 // split form otherwise or on request.  Tiled flavour: two CTAs share one 256-row MMA (a third
 // less L2 operand traffic per flop) when the K loop is long and there are two row blocks.
+bool tc_stage_depth_legal(bool tiled, int bn, bool out_f32, int kd) {
+  if (kd == kTcBlockK) return true;
+  if (out_f32 || (kd != 32 && kd != 128)) return false;
+  return kd == 32 || bn == 128 || tiled;     // 128-deep stages of 256-column tiles leave no room for a cluster's statistics
+}
+
 TcVariant tc_choose_variant(bool tiled, int bn, bool out_f32, int batch, int num_rb, int num_kb, int cluster_n,
-                            int epilogue_mode, int pair_mode, int num_sms, int resident) {
-  if (tiled) {
-    if (out_f32) return bn == 128 ? TcVariant{128, 6, 0, EPI_SPLIT, 0, 1} : TcVariant{kTcBlockN, 4, 0, EPI_SPLIT, 0, 1};
-    if (bn == 128) return TcVariant{128, 6, 0, EPI_SPLIT, 0, 0};
-    const bool pair = num_rb >= 2 && (pair_mode == 2 || (pair_mode == 0 && num_kb >= 8));
-    return pair ? TcVariant{kTcBlockN, 6, 0, EPI_SPLIT, 1, 0} : TcVariant{kTcBlockN, 4, 0, EPI_SPLIT, 0, 0};
+                            int epilogue_mode, int pair_mode, int num_sms, int resident, int kd) {
+  if (kd != kTcBlockK && tc_stage_depth_legal(tiled, bn, out_f32, kd)) {
+    // same bytes of operands in flight as the default depth
+    if (tiled) return bn == 128 ? TcVariant{128, kd == 32 ? 12 : 3, 0, EPI_SPLIT, 0, 0, kd} : TcVariant{kTcBlockN, kd == 32 ? 8 : 2, 0, EPI_SPLIT, 0, 0, kd};
+    return bn == 128 ? TcVariant{128, kd == 32 ? 8 : 2, 1, EPI_SPLIT, 0, 0, kd} : TcVariant{kTcBlockN, 6, 1, EPI_SPLIT, 0, 0, kd};
   }
-  if (out_f32) return bn == 128 ? TcVariant{128, 4, 1, EPI_SPLIT, 0, 1} : TcVariant{kTcBlockN, 3, 1, EPI_SPLIT, 0, 1};
-  if (bn == 128) return TcVariant{128, 4, 1, EPI_SPLIT, 0, 0};
+  if (tiled) {
+    if (out_f32) return bn == 128 ? TcVariant{128, 6, 0, EPI_SPLIT, 0, 1, kTcBlockK} : TcVariant{kTcBlockN, 4, 0, EPI_SPLIT, 0, 1, kTcBlockK};
+    if (bn == 128) return TcVariant{128, 6, 0, EPI_SPLIT, 0, 0, kTcBlockK};
+    const bool pair = num_rb >= 2 && (pair_mode == 2 || (pair_mode == 0 && num_kb >= 8));
+    return pair ? TcVariant{kTcBlockN, 6, 0, EPI_SPLIT, 1, 0, kTcBlockK} : TcVariant{kTcBlockN, 4, 0, EPI_SPLIT, 0, 0, kTcBlockK};
+  }
+  if (out_f32) return bn == 128 ? TcVariant{128, 4, 1, EPI_SPLIT, 0, 1, kTcBlockK} : TcVariant{kTcBlockN, 3, 1, EPI_SPLIT, 0, 1, kTcBlockK};
+  if (bn == 128) return TcVariant{128, 4, 1, EPI_SPLIT, 0, 0, kTcBlockK};
   const int per_round = num_sms / (cluster_n > 0 ? cluster_n : 1);
   const int units = batch * num_rb;
   const int tiles_per_cta = (units + per_round - 1) / (per_round > 0 ? per_round : 1);
   const bool relay = epilogue_mode == kEpilogueRelay || (epilogue_mode == kEpilogueAuto && tiles_per_cta >= kRelayMinTiles);
-  if (relay) return TcVariant{kTcBlockN, num_kb <= 3 ? 2 : 3, 1, EPI_RELAY, 0, 0};
-  if (epilogue_mode == kEpilogueAuto && units <= resident) return TcVariant{kTcBlockN, 4, 1, EPI_SINGLE, 0, 0};
-  return TcVariant{kTcBlockN, 3, 1, EPI_SPLIT, 0, 0};
+  if (relay) return TcVariant{kTcBlockN, num_kb <= 3 ? 2 : 3, 1, EPI_RELAY, 0, 0, kTcBlockK};
+  if (epilogue_mode == kEpilogueAuto && units <= resident) return TcVariant{kTcBlockN, 4, 1, EPI_SINGLE, 0, 0, kTcBlockK};
+  return TcVariant{kTcBlockN, 3, 1, EPI_SPLIT, 0, 0, kTcBlockK};
 }
 
 int tc_variant_smem_bytes(const TcVariant &v) {
-#define X(BN, ST, CL, EP, PA, O32) \
-  if (v.bn == BN && v.stages == ST && (v.cluster != 0) == CL && v.epi == EP && (v.pair != 0) == PA && (v.out32 != 0) == O32) \
-    return SmemLayout<BN, ST, CL, EP, PA, O32>::kDynamic;
+#define X(BN, ST, CL, EP, PA, O32, KD) \
+  if (v.bn == BN && v.stages == ST && (v.cluster != 0) == CL && v.epi == EP && (v.pair != 0) == PA && (v.out32 != 0) == O32 && v.kd == KD) \
+    return SmemLayout<BN, ST, CL, EP, PA, O32, KD>::kDynamic;
   WTC_TC_VARIANTS(X)
 #undef X
   return 0;
@@ -1166,9 +1192,9 @@ int tc_variant_threads(const TcVariant &v) { return kThreadsFor(v.epi); }
 namespace {
 cudaError_t launch_variant(const TcVariant &v, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO,
                            const TcParams &p, int cluster_n, int num_sms, cudaStream_t s, TcLaunchInfo *info) {
-#define X(BN, ST, CL, EP, PA, O32) \
-  if (v.bn == BN && v.stages == ST && (v.cluster != 0) == CL && v.epi == EP && (v.pair != 0) == PA && (v.out32 != 0) == O32) \
-    return launch_impl<BN, ST, CL, EP, PA, O32>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+#define X(BN, ST, CL, EP, PA, O32, KD) \
+  if (v.bn == BN && v.stages == ST && (v.cluster != 0) == CL && v.epi == EP && (v.pair != 0) == PA && (v.out32 != 0) == O32 && v.kd == KD) \
+    return launch_impl<BN, ST, CL, EP, PA, O32, KD>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
   WTC_TC_VARIANTS(X)
 #undef X
   return cudaErrorInvalidConfiguration;
@@ -1182,18 +1208,19 @@ cudaError_t launch_fused_cluster(const CUtensorMap &tmA, const CUtensorMap &tmB,
   // the single-tile form is tried whenever one tile per CTA is possible at all; it declines
   // (before launching) when the clusters do not all fit the chip at once, and the split form runs
   TcVariant v = tc_choose_variant(false, bn, p.out_f32 != 0, p.batch, p.num_rb, p.num_kb, cluster_n, p.epilogue_mode, p.pair_mode,
-                                  num_sms, /*resident=*/1 << 30);
+                                  num_sms, /*resident=*/1 << 30, p.stage_k ? p.stage_k : kTcBlockK);
   if (v.epi == EPI_SINGLE) {
     const cudaError_t e = launch_variant(v, tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
     if (e != cudaErrorNotSupported) return e;
-    v = TcVariant{kTcBlockN, 3, 1, EPI_SPLIT, 0, 0};
+    v = TcVariant{kTcBlockN, 3, 1, EPI_SPLIT, 0, 0, kTcBlockK};
   }
   return launch_variant(v, tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
 }
 
 cudaError_t launch_tiled_partial(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO,
                                  const TcParams &p, int bn, int num_sms, cudaStream_t s, TcLaunchInfo *info) {
-  const TcVariant v = tc_choose_variant(true, bn, p.out_f32 != 0, p.batch, p.num_rb, p.num_kb, 1, p.epilogue_mode, p.pair_mode, num_sms, 0);
+  const TcVariant v = tc_choose_variant(true, bn, p.out_f32 != 0, p.batch, p.num_rb, p.num_kb, 1, p.epilogue_mode, p.pair_mode, num_sms, 0,
+                                        p.stage_k ? p.stage_k : kTcBlockK);
   return launch_variant(v, tmA, tmB, tmO, p, 1, num_sms, s, info);
 }
 

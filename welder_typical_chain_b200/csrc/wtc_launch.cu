@@ -45,13 +45,13 @@ const int g_use_pdl = [] { const char *e = getenv("WTC_NO_PDL"); return (e && e[
 
 // registers / spills / stack of every instance of the tensor-core kernel template, from the
 // `ptxas -v` report of this build (generated beside the objects)
-struct KernelFacts { int bn, stages, cluster, epi, pair, out32, registers, spill_store, spill_load, stack; };
+struct KernelFacts { int bn, stages, cluster, epi, pair, out32, kd, registers, spill_store, spill_load, stack; };
 const KernelFacts kKernelFacts[] = {
 #include "build/kernel_facts.inc"
 };
 const KernelFacts *facts_of(const wtc::TcVariant &v) {
   for (const KernelFacts &f : kKernelFacts)
-    if (f.bn == v.bn && f.stages == v.stages && f.cluster == (v.cluster != 0) && f.epi == v.epi && f.pair == (v.pair != 0) && f.out32 == (v.out32 != 0))
+    if (f.bn == v.bn && f.stages == v.stages && f.cluster == (v.cluster != 0) && f.epi == v.epi && f.pair == (v.pair != 0) && f.out32 == (v.out32 != 0) && f.kd == v.kd)
       return &f;
   return nullptr;
 }
@@ -60,6 +60,7 @@ struct Resolved {
   wtc_chain_desc d;  // strides filled in
   wtc_plan_info plan;
   int bn;            // column tile of the tensor-core kernels: 256, or 128 when best.json asks for it
+  int kd;            // K depth of a pipeline stage: 64, or best.json's tileK when it is 32 or 128 and a kernel exists for it
   int num_rb, num_nb, num_kb;
   bool b_batched;
   bool tc_ok;
@@ -146,7 +147,18 @@ int resolve(const wtc_chain_desc *in, Resolved &r) {
     else if (!(d.flags & WTC_FLAG_FORCE_TILED) && nb128 <= 8 && units * nb256 <= 74 && units <= kResident[nb128]) r.bn = 128;
   }
   r.num_nb = static_cast<int>((d.N + r.bn - 1) / r.bn);
-  r.num_kb = static_cast<int>((d.K + wtc::kTcBlockK - 1) / wtc::kTcBlockK);
+  // tileK is the K depth of one pipeline stage.  64 is the default; 32 and 128 have kernels in the
+  // eight-warp epilogue family (f16 probabilities, no forced epilogue form or CTA pair; 128 deep with
+  // 256-column tiles only in the tiled flavour, where no cluster statistics compete for the room).
+  r.kd = wtc::kTcBlockK;
+  {
+    const bool tiled_shape = r.num_nb > 8 || (d.flags & WTC_FLAG_FORCE_TILED);
+    const int forced = WTC_FLAG_EPILOGUE_SPLIT | WTC_FLAG_EPILOGUE_RELAY | WTC_FLAG_PAIR;
+    if ((d.tile_k == 32 || d.tile_k == 128) && d.variant == WTC_VARIANT_FUSED && !(d.flags & forced) &&
+        wtc::tc_stage_depth_legal(tiled_shape, r.bn, d.out_dtype == WTC_F32, d.tile_k))
+      r.kd = d.tile_k;
+  }
+  r.num_kb = static_cast<int>((d.K + r.kd - 1) / r.kd);
 
   const bool tc_shape = d.in_dtype == WTC_F16 && d.M > 0 && d.N > 0 && d.K > 0 &&
                         mult8(d.K) && mult8(d.N) && mult8(d.lda) && mult8(d.ldb) && mult8(d.ldo) &&
@@ -173,7 +185,7 @@ int resolve(const wtc_chain_desc *in, Resolved &r) {
       p.tile_m = 8; p.tile_n = static_cast<int32_t>(d.N); p.tile_k = 64;
     }
   } else if (r.tc_ok) {
-    p.tile_m = wtc::kTcBlockM; p.tile_n = r.bn; p.tile_k = wtc::kTcBlockK;
+    p.tile_m = wtc::kTcBlockM; p.tile_n = r.bn; p.tile_k = r.kd;
     p.tmem_columns = 2 * r.bn;
     // variant, threads, stages as the launchers choose them on a 148-SM part (the plan is made
     // without a device): clusters of n CTAs resident at once, measured (8: 15; others: one short of 148 / n)
@@ -184,7 +196,7 @@ int resolve(const wtc_chain_desc *in, Resolved &r) {
     const bool cluster = r.num_nb <= 8 && !(d.flags & WTC_FLAG_FORCE_TILED);
     const wtc::TcVariant v = wtc::tc_choose_variant(!cluster, r.bn, d.out_dtype == WTC_F32, d.batch, r.num_rb, r.num_kb,
                                                     cluster ? r.num_nb : 1, epi_mode, pair_mode, 148,
-                                                    cluster ? kResidentClusters[r.num_nb] : 0);
+                                                    cluster ? kResidentClusters[r.num_nb] : 0, r.kd);
     p.threads = wtc::tc_variant_threads(v);
     p.stages = v.stages;
     p.smem_bytes = wtc::tc_variant_smem_bytes(v);
@@ -248,10 +260,10 @@ MapTable *map_table() {
   return t;
 }
 
-// rank-3 tensor (d0 innermost, contiguous), or rank-4 when d3 > 0; f16 unless f32; 128-byte swizzle, zero fill
+// rank-3 tensor (d0 innermost, contiguous), or rank-4 when d3 > 0; f16 unless f32; 128-byte swizzle (64-byte on request), zero fill
 int get_map(const void *ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1_bytes, uint64_t s2_bytes, uint32_t b0,
-            uint32_t b1, CUtensorMap *out, bool f32 = false, uint64_t d3 = 0, uint64_t s3_bytes = 0, uint32_t b2 = 1) {
-  const MapKey key{ptr, d0, d1, d2 ^ (d3 << 32), s1_bytes, s2_bytes ^ (s3_bytes << 20), b0 | (f32 ? 0x80000000u : 0u), b1 | (b2 << 16)};
+            uint32_t b1, CUtensorMap *out, bool f32 = false, uint64_t d3 = 0, uint64_t s3_bytes = 0, uint32_t b2 = 1, bool swizzle64 = false) {
+  const MapKey key{ptr, d0, d1, d2 ^ (d3 << 32), s1_bytes, s2_bytes ^ (s3_bytes << 20), b0 | (f32 ? 0x80000000u : 0u) | (swizzle64 ? 0x40000000u : 0u), b1 | (b2 << 16)};
   MapTable *tab = map_table();
   uint64_t h = reinterpret_cast<uintptr_t>(ptr) * 0x9E3779B97F4A7C15ull;
   h ^= (d0 * 31 + d1) * 0xC2B2AE3D27D4EB4Full + key.d2 + s1_bytes + (static_cast<uint64_t>(key.b0) << 20) + key.b1;
@@ -270,7 +282,7 @@ int get_map(const void *ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1_
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUtensorMap m;
   CUresult cr = g_encode(&m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, rank, const_cast<void *>(ptr), dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (cr != CUDA_SUCCESS)
     return fail(WTC_E_CUDA, "cuTensorMapEncodeTiled failed (%d) for rank %u dims=(%llu,%llu,%llu,%llu) strides=(%llu,%llu,%llu) box=(%u,%u,%u)",
@@ -283,17 +295,17 @@ int get_map(const void *ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1_
 
 // The map of B [batch][K][N] (N contiguous).  When N is a multiple of 64 it is the rank-4 view
 // [batch][N/64][K][64]: one copy then brings `blocks` 64-column blocks of a K block, each laid
-// out as the tensor core wants it (64 k-rows x 128 bytes); otherwise one copy per 64 columns.
+// out as the tensor core wants it (one stage's k-rows x 128 bytes); otherwise one copy per 64 columns.
 int get_map_b(const void *B, const Resolved &r, int blocks, CUtensorMap *out, int *b_blocks) {
   const wtc_chain_desc &d = r.d;
   const uint64_t nbatch = r.b_batched ? d.batch : 1;
   const uint64_t bstride = (r.b_batched ? d.b_batch_stride : d.K * d.ldb) * 2;
   if (d.N % 64 == 0) {
     *b_blocks = 1;
-    return get_map(B, 64, d.K, d.N / 64, d.ldb * 2, 128, 64, wtc::kTcBlockK, out, false, nbatch, bstride, blocks);
+    return get_map(B, 64, d.K, d.N / 64, d.ldb * 2, 128, 64, r.kd, out, false, nbatch, bstride, blocks);
   }
   *b_blocks = 0;
-  return get_map(B, d.N, d.K, nbatch, d.ldb * 2, bstride, 64, wtc::kTcBlockK, out);
+  return get_map(B, d.N, d.K, nbatch, d.ldb * 2, bstride, 64, r.kd, out);
 }
 
 int num_sms() {
@@ -422,11 +434,12 @@ int launch_resolved(Resolved &r, const void *A, const void *B, void *Out, void *
     const int sms = num_sms();
     if (sms <= 0) return fail(WTC_E_CUDA, "no usable CUDA device");
     CUtensorMap tmA, tmB, tmO;
-    int rc = get_map(A, d.K, d.M, d.batch, d.lda * 2, d.a_batch_stride * 2, wtc::kTcBlockK, wtc::kTcBlockM, &tmA);
+    // A's box is one swizzle span wide at most: 64 columns (a 128-deep stage takes two), or 32 with the 64-byte swizzle
+    int rc = get_map(A, d.K, d.M, d.batch, d.lda * 2, d.a_batch_stride * 2, r.kd < 64 ? r.kd : 64, wtc::kTcBlockM, &tmA, false, 0, 0, 1, r.kd == 32);
     if (rc) return rc;
     // (a CTA pair loads half of the tile's columns per CTA: the variant decides the box)
     const int pm = (d.flags & WTC_FLAG_NO_PAIR) ? 1 : ((d.flags & WTC_FLAG_PAIR) ? 2 : 0);
-    const wtc::TcVariant v = wtc::tc_choose_variant(tiled, r.bn, d.out_dtype == WTC_F32, d.batch, r.num_rb, r.num_kb, tiled ? 1 : r.num_nb, 0, pm, sms, 0);
+    const wtc::TcVariant v = wtc::tc_choose_variant(tiled, r.bn, d.out_dtype == WTC_F32, d.batch, r.num_rb, r.num_kb, tiled ? 1 : r.num_nb, 0, pm, sms, 0, r.kd);
     int b_blocks = 0;
     rc = get_map_b(B, r, v.pair ? r.bn / 128 : r.bn / 64, &tmB, &b_blocks);
     if (rc) return rc;
@@ -450,6 +463,7 @@ int launch_resolved(Resolved &r, const void *A, const void *B, void *Out, void *
 #endif
     p.use_pdl = g_use_pdl;
     p.out_f32 = out32;
+    p.stage_k = r.kd;
     p.pair_mode = (d.flags & WTC_FLAG_NO_PAIR) ? 1 : ((d.flags & WTC_FLAG_PAIR) ? 2 : 0);
     p.epilogue_mode = (d.flags & WTC_FLAG_EPILOGUE_SPLIT) ? wtc::kEpilogueSplit
                       : ((d.flags & WTC_FLAG_EPILOGUE_RELAY) ? wtc::kEpilogueRelay : wtc::kEpilogueAuto);

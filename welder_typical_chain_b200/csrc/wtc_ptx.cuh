@@ -272,6 +272,17 @@ __device__ __forceinline__ uint64_t umma_smem_desc_sw128(uint32_t smem_addr, uin
   return d;
 }
 
+// The same with the 64-byte swizzle (layout 4): rows of 64 bytes, 8-row groups 512 bytes apart.
+__device__ __forceinline__ uint64_t umma_smem_desc_sw64(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(4) << 61;
+  return d;
+}
+
 // Instruction descriptor for kind::f16 with f16 operands and f32 accumulate.
 // bits [4,6) D format (1 = f32), [7,10) A format (0 = f16), [10,13) B format,
 // bit 15 A major (0 = K, 1 = MN), bit 16 B major, [17,23) N >> 3, [24,29) M >> 4.
