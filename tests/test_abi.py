@@ -79,7 +79,16 @@ def test_plan_fallbacks_and_variants(wtc_lib):
         assert w.plan_query(d).kernel == w.KERNEL_SIMT_UNFUSED and w.plan_query(d).launches == 5
     # tile hints: legal ones pass, others are replaced and flagged
     assert w.plan_query(w.make_desc(1, 4096, 1024, 1024, tile_m=128, tile_n=256, tile_k=64)).tile_substituted == 0
-    assert w.plan_query(w.make_desc(1, 4096, 1024, 1024, tile_m=64, tile_n=128, tile_k=32)).tile_substituted == 1
+    # the reference's own pinned search result, 64 x 128 x 32, is honoured as given
+    p = w.plan_query(w.make_desc(1, 4096, 1024, 1024, tile_m=64, tile_n=128, tile_k=32))
+    assert (p.tile_m, p.tile_n, p.tile_k, p.tile_substituted, p.cluster_n, p.stages) == (64, 128, 32, 0, 8, 8)
+    # stage depths 32 / 128 and 64-row tiles belong to the eight-warp family: f16 probabilities, no forced form
+    assert w.plan_query(w.make_desc(1, 4096, 1024, 1024, tile_m=128, tile_n=128, tile_k=128)).tile_substituted == 0
+    assert w.plan_query(w.make_desc(1, 4096, 1024, 1024, tile_m=128, tile_n=256, tile_k=128)).tile_k == 64     # no room beside a cluster's statistics
+    assert w.plan_query(w.make_desc(1, 4096, 4096, 1024, tile_m=128, tile_n=256, tile_k=128)).tile_k == 128    # tiled flavour
+    assert w.plan_query(w.make_desc(1, 4096, 1024, 1024, tile_m=64, tile_n=128, tile_k=128)).tile_m == 128
+    assert w.plan_query(w.make_desc(1, 4096, 1024, 1024, tile_m=32, tile_n=64, tile_k=16)).tile_substituted == 1
+    assert w.plan_query(w.make_desc(1, 4096, 1024, 1024, tile_m=64, tile_k=32, flags=w.FLAG_EPILOGUE_RELAY)).tile_m == 128
     # the second legal column tile is honoured as given: 128 columns per CTA, eight CTAs per cluster
     p = w.plan_query(w.make_desc(1, 4096, 1024, 1024, tile_m=128, tile_n=128, tile_k=64))
     assert (p.tile_n, p.cluster_n, p.tile_substituted, p.tmem_columns) == (128, 8, 0, 256)

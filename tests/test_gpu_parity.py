@@ -346,7 +346,7 @@ def test_tile_choice_from_best_json_is_honoured(w, cuda_dev):
         ref = oracle.chain(A, B, 1 / 32)
         _check(_run(w, cuda_dev, A, B, 1 / 32, tiles=(128, 128, 64)), ref)
         _check(_run(w, cuda_dev, A, B, 1 / 32, tiles=(128, 256, 64)), ref)
-        _check(_run(w, cuda_dev, A, B, 1 / 32, tiles=(64, 128, 32)), ref)     # tileM replaced, tileN and tileK honoured
+        _check(_run(w, cuda_dev, A, B, 1 / 32, tiles=(64, 128, 32)), ref)     # the reference's pinned tile, honoured as given
 
 
 @pytest.mark.parametrize("tile_k", [32, 128])
@@ -369,6 +369,38 @@ def test_stage_depth_from_best_json_is_honoured(w, cuda_dev, M, N, K, tile_n, fl
     A = oracle.normal((M, K), 71)
     B = oracle.normal((K, N), 72)
     _check(_run(w, cuda_dev, A, B, 0.05, flags=fl, tiles=(128, tile_n, tile_k)), oracle.chain(A, B, 0.05))
+
+
+@pytest.mark.parametrize("tile_n,tile_k", [(128, 32), (128, 64), (256, 32), (256, 64)])
+@pytest.mark.parametrize("M,N,K,flags", [
+    (777, 1024, 200, 0),            # clusters, ragged M (a last tile of 9 rows), K tail
+    (64, 520, 72, 0),               # exactly one 64-row tile, ragged N
+    (4096, 1024, 1024, 0),          # the headline shape
+    (300, 2304, 128, 0),            # two-pass tiled schedule
+    (130, 520, 40, "tiled"),        # tiled by request
+])
+def test_64_row_tiles_from_best_json_are_honoured(w, cuda_dev, M, N, K, flags, tile_n, tile_k):
+    """tileM = 64 runs tcgen05.mma with M = 64 (accumulator rows in lanes 0-15 of each quarter of tensor
+    memory); 64 x 128 x 32 is the tile the reference's own pinned search result names."""
+    fl = w.FLAG_FORCE_TILED if flags == "tiled" else 0
+    plan = w.plan_query(w.make_desc(1, M, N, K, flags=fl, tile_m=64, tile_n=tile_n, tile_k=tile_k))
+    assert (plan.tile_m, plan.tile_n, plan.tile_k, plan.tile_substituted) == (64, tile_n, tile_k, 0)
+    A = oracle.normal((M, K), 75)
+    B = oracle.normal((K, N), 76)
+    _check(_run(w, cuda_dev, A, B, 0.05, flags=fl, tiles=(64, tile_n, tile_k)), oracle.chain(A, B, 0.05))
+
+
+def test_64_row_tiles_batched_and_replaced(w, cuda_dev):
+    A = oracle.normal((3, 1000, 160), 77)
+    B = oracle.normal((3, 160, 1024), 78)
+    ref = np.stack([oracle.chain(A[b], B[b], 0.08) for b in range(3)])
+    _check(_run(w, cuda_dev, A, B, 0.08, tiles=(64, 128, 32)), ref)
+    # no 64-row kernel with 128-deep stages or f32 probabilities: the row tile is replaced and reported
+    plan = w.plan_query(w.make_desc(1, 256, 1024, 256, tile_m=64, tile_n=128, tile_k=128))
+    assert (plan.tile_m, plan.tile_k, plan.tile_substituted) == (128, 128, 1)
+    plan = w.plan_query(w.make_desc(1, 256, 1024, 256, out_dtype=w.F32, tile_m=64, tile_n=128, tile_k=32))
+    assert (plan.tile_m, plan.tile_k, plan.tile_substituted) == (128, 64, 1)
+    _check(_run(w, cuda_dev, A[0], B[0], 0.08, out_dtype=w.F32, tiles=(64, 128, 32)), ref[0])
 
 
 def test_stage_depth_batched_many_tiles(w, cuda_dev):

@@ -153,7 +153,8 @@ def test_tile_source_priority_and_overrides(tmp_path):
     assert not (out / "search/best_summary.json").exists()            # --best-json given: no search
     assert json.load(open(out / "search/best.json")) == dict(tileM=64, tileN=128, tileK=16, threadTileM=8, threadTileN=2)
     plan = open(out / "fused/05.out.nvvm.runnable.mlir").read()
-    assert "requested_m = 64" in plan and "tile_m = 128" in plan and "substituted = 1" in plan
+    # 64-row tiles and the 128-column tile are honoured; a 16-deep stage has no kernel and is replaced
+    assert "requested_m = 64" in plan and "tile_m = 64" in plan and "requested_k = 16" in plan and "tile_k = 64" in plan and "substituted = 1" in plan
     assert "substituted" in open(out / "fused/compile.log").read()
     # --no-search without tiles: built-in defaults 32x64x16, thread tile 2x2
     out2 = tmp_path / "o2"

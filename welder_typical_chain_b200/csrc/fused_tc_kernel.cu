@@ -68,13 +68,16 @@ constexpr uint32_t kBLbo = 8192, kBSbo = 1024, kBKstep = 2048;
 // the eight-warp epilogue forms.  A's 128 rows are then staged as 64-byte rows with the 64-byte
 // swizzle (32), or as two 128-byte-swizzled blocks of 64 columns side by side (128); B's
 // 64-column blocks simply have KD k-rows.
-template <int BN, int STAGES, bool CLUSTER, int EPI, bool PAIR, bool OUT32, int KD = kTcBlockK>
+// TM: rows of a tile (the schedule's tileM): 128, or 64 (tcgen05.mma with M = 64, whose
+// accumulator rows lie in lanes 0-15 of each 32-lane quarter of tensor memory) in the same family.
+template <int BN, int STAGES, bool CLUSTER, int EPI, bool PAIR, bool OUT32, int KD = kTcBlockK, int TM = kTcBlockM>
 struct SmemLayout {
   static constexpr bool RELAY = EPI == EPI_RELAY;
   static constexpr bool SINGLE = EPI == EPI_SINGLE;
   static_assert(KD == 32 || KD == 64 || KD == 128, "stage depth: 32, 64 or 128");
   static_assert(KD == 64 || (EPI == EPI_SPLIT && !PAIR && !OUT32), "other stage depths: eight-warp epilogue, unpaired, f16 output");
-  static constexpr int kABytes = BM * KD * 2;
+  static_assert(TM == 128 || (TM == 64 && EPI == EPI_SPLIT && !PAIR && !OUT32), "64-row tiles: eight-warp epilogue, unpaired, f16 output");
+  static constexpr int kABytes = TM * KD * 2;
   static constexpr int kBBytes = KD * BN * 2 / (PAIR ? 2 : 1);     // a CTA pair splits B's columns between its two CTAs
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kHalfCols = SINGLE ? BN / 4 : BN / 2;         // columns per epilogue thread
@@ -200,11 +203,11 @@ __device__ __forceinline__ void scale_pack(const uint32_t (&r)[32], float f, uin
   for (int i = 0; i < 32; i += 2) h[i >> 1] = pack_f16x2(__uint_as_float(r[i]) * f, __uint_as_float(r[i + 1]) * f);
 }
 
-template <int BN, int STAGES, bool CLUSTER, int EPI, bool PAIR, bool OUT32, int KD>
+template <int BN, int STAGES, bool CLUSTER, int EPI, bool PAIR, bool OUT32, int KD, int TM>
 __global__ void __launch_bounds__(kThreadsFor(EPI), 1)
 fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmO, const TcParams p) {
-  using L = SmemLayout<BN, STAGES, CLUSTER, EPI, PAIR, OUT32, KD>;
+  using L = SmemLayout<BN, STAGES, CLUSTER, EPI, PAIR, OUT32, KD, TM>;
   constexpr int BK = KD;                // K depth of a stage (hides the default of the same name)
   constexpr int A_BOXES = KD == 128 ? 2 : 1;   // A's copies per stage: a box is at most one swizzle span (64 columns) wide
   constexpr bool RELAY = L::RELAY;
@@ -213,7 +216,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   constexpr int HC = L::kHalfCols;      // columns per epilogue thread
   constexpr int NCH = HC / 32;          // 32-column chunks per epilogue thread
   constexpr int kEpiThreads = (RELAY || SINGLE) ? 512 : 256;
-  static_assert(!(RELAY || SINGLE) || (CLUSTER && !PAIR && !OUT32 && BN == 256), "sixteen-warp epilogues: cluster flavour, 256-column tiles, f16 staged stores");
+  static_assert(!(RELAY || SINGLE) || (CLUSTER && !PAIR && !OUT32 && BN == 256 && TM == 128), "sixteen-warp epilogues: cluster flavour, 128 x 256 tiles, f16 staged stores");
   static_assert(!OUT32 || !PAIR, "f32 output: unpaired CTAs");
   static_assert(!PAIR || !CLUSTER, "CTA pairs: tiled flavour only");
   // The 128-byte swizzle needs the stage buffers on 1024-byte boundaries.  There is no
@@ -279,8 +282,8 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     uint8_t *sa = smem + s * L::kStageBytes;
     uint8_t *sb = sa + L::kABytes;
     mbar_expect_tx(&full[s], L::kStageBytes);
-    tma_load_3d(sa, &tmA, &full[s], kb * BK, rb * BM, b);
-    if (A_BOXES == 2) tma_load_3d(sa + BM * 128, &tmA, &full[s], kb * BK + 64, rb * BM, b);
+    tma_load_3d(sa, &tmA, &full[s], kb * BK, rb * TM, b);
+    if (A_BOXES == 2) tma_load_3d(sa + TM * 128, &tmA, &full[s], kb * BK + 64, rb * TM, b);
     if (p.b_blocks) tma_load_4d(sb, &tmB, &full[s], 0, kb * BK, nb * (BN / 64), bb);
     else {
 #pragma unroll
@@ -343,7 +346,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     for (int base = 0; base < p.num_kb; base += 4) {
       const int kb = base + lane;
       if (lane < 4 && kb < p.num_kb) {
-        if (kb % cl == nb || kb < early) tma_prefetch_l2_3d(&tmA, kb * BK, rb * BM, b);
+        if (kb % cl == nb || kb < early) tma_prefetch_l2_3d(&tmA, kb * BK, rb * TM, b);
         if (kb % groups == first % groups || kb < early) {
           if (p.b_blocks) tma_prefetch_l2_4d(&tmB, 0, kb * BK, nb * (BN / 64), bb);
           else {
@@ -723,7 +726,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       for (int t = lane; t < early * boxes; t += 32) {
         const int st = t / boxes, j = t - st * boxes;
         uint8_t *sa = smem + st * L::kStageBytes;
-        if (j < A_BOXES) tma_load_3d(sa + j * (BM * 128), &tmA, &full[st], st * BK + j * 64, rb * BM, b);
+        if (j < A_BOXES) tma_load_3d(sa + j * (TM * 128), &tmA, &full[st], st * BK + j * 64, rb * TM, b);
         else if (p.b_blocks) tma_load_4d(sa + L::kABytes, &tmB, &full[st], 0, st * BK, nb * (BN / 64), bb);
         else tma_load_3d(sa + L::kABytes + (j - A_BOXES) * (BK * 128), &tmB, &full[st], nb * BN + (j - A_BOXES) * 64, st * BK, bb);
       }
@@ -763,7 +766,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   } else if (warp == 1) {
     // ======================= MMA issuer: one thread (of the even CTA of a pair) =======
     if (is_leader && elect_one()) {
-      constexpr uint32_t idesc = umma_idesc_f16_f32(PAIR ? 2 * BM : BM, BN, /*a_mn_major=*/0, /*b_mn_major=*/1);
+      constexpr uint32_t idesc = umma_idesc_f16_f32(PAIR ? 2 * BM : TM, BN, /*a_mn_major=*/0, /*b_mn_major=*/1);
       const uint16_t pair_mask = static_cast<uint16_t>(3u << leader_rank);
       // everything of the two operand descriptors but the address, which is added per stage
       // (A with 64-byte rows: 64-byte swizzle, 8-row groups 512 B apart; B's 64-column blocks are KD k-rows apart)
@@ -790,7 +793,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           for (int k = 0; k < BK / 16; ++k) {
             if (PAIR) umma_f16_ss_pair(d_tmem, da, db, idesc, (kb | k) != 0);
             else umma_f16_ss(d_tmem, da, db, idesc, (kb | k) != 0);
-            da += (k == 3 ? BM * 128 - 3 * kAKstep : kAKstep) >> 4;   // after four steps: the second 64-column block of a 128-deep stage
+            da += (k == 3 ? TM * 128 - 3 * kAKstep : kAKstep) >> 4;   // after four steps: the second 64-column block of a 128-deep stage
             db += kBKstep >> 4;
           }
           // while those MMAs drain: has the next stage landed already?  (The ring runs on
@@ -817,7 +820,10 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     if (CLUSTER) { cluster_wait_acquire(); cluster_waited = true; }
     const int q = warp & 3;                      // TMEM lane quarter this warp may read
     const int half = (warp - 2) >> 2;            // which half of the tile's columns
-    const int row_in_tile = q * 32 + lane;
+    // (64-row tiles: the accumulator's rows are in lanes 0-15 of each quarter; the other lanes run
+    //  along on whatever their lanes hold, in statistics slots 64.. that no row uses, and store nothing)
+    const bool lane_live = TM == 128 || lane < 16;
+    const int row_in_tile = TM == 128 ? q * 32 + lane : (lane < 16 ? q * 16 + lane : 48 + q * 16 + lane);
     const bool lead = threadIdx.x == 64;         // first epilogue thread: posts expect_tx, stamps
     uint8_t *stg = smem + L::kOffOut + (warp - 2) * L::kOutWarpBytes;
     float2 *mine = &pair[half * BM + row_in_tile];
@@ -837,7 +843,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ab * BN + half * HC;
       const int col0 = nb * BN + half * HC;               // first matrix column of this thread
       const int valid = max(0, min(HC, p.N - col0));      // my columns that exist
-      const int row0 = rb * BM + q * 32;                  // first row of this warp
+      const int row0 = rb * TM + q * (TM / 4);            // first row of this warp
       const bool rows_live = row0 < p.M;
 
       // ---- the thread's whole share of the accumulator row goes to registers at once,
@@ -1021,8 +1027,8 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         // tile statistics: max of the tile row, sum of the stored values of both halves
         mine->y = sum_r;
         named_bar_sync(1 + q, 64);
-        const int row = rb * BM + row_in_tile;
-        if (half == 0 && row < p.M)
+        const int row = rb * TM + row_in_tile;
+        if (half == 0 && lane_live && row < p.M)
           p.tile_stats[(static_cast<int64_t>(b) * p.M + row) * p.num_nb + nb] = make_float2(lm, sum_r + other->y);
         named_bar_sync(1 + q, 64);
       }
@@ -1057,11 +1063,11 @@ struct DeviceFacts {
   int registers = 0;
 };
 
-template <int BN, int STAGES, bool CLUSTER, int EPI, bool PAIR, bool OUT32, int KD>
+template <int BN, int STAGES, bool CLUSTER, int EPI, bool PAIR, bool OUT32, int KD, int TM>
 cudaError_t launch_impl(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO, TcParams p,
                         int cluster_n, int num_sms, cudaStream_t s, TcLaunchInfo *info) {
-  using L = SmemLayout<BN, STAGES, CLUSTER, EPI, PAIR, OUT32, KD>;
-  auto kern = fused_tc_kernel<BN, STAGES, CLUSTER, EPI, PAIR, OUT32, KD>;
+  using L = SmemLayout<BN, STAGES, CLUSTER, EPI, PAIR, OUT32, KD, TM>;
+  auto kern = fused_tc_kernel<BN, STAGES, CLUSTER, EPI, PAIR, OUT32, KD, TM>;
   static DeviceFacts facts[64];   // per template instance, per device
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
@@ -1127,20 +1133,25 @@ cudaError_t launch_impl(const CUtensorMap &tmA, const CUtensorMap &tmB, const CU
 
 } // namespace
 
-// Every instantiated variant, once: X(BN, STAGES, CLUSTER, EPI, PAIR, OUT32, KD).
+// Every instantiated variant, once: X(BN, STAGES, CLUSTER, EPI, PAIR, OUT32, KD, TM).
 #define WTC_TC_VARIANTS(X)                                                                                \
-  X(128, 4, true, EPI_SPLIT, false, true, 64) X(kTcBlockN, 3, true, EPI_SPLIT, false, true, 64)            \
-  X(128, 4, true, EPI_SPLIT, false, false, 64) X(kTcBlockN, 3, true, EPI_SPLIT, false, false, 64)          \
-  X(kTcBlockN, 2, true, EPI_RELAY, false, false, 64) X(kTcBlockN, 3, true, EPI_RELAY, false, false, 64)    \
-  X(kTcBlockN, 4, true, EPI_SINGLE, false, false, 64)                                                      \
-  X(128, 6, false, EPI_SPLIT, false, true, 64) X(kTcBlockN, 4, false, EPI_SPLIT, false, true, 64)          \
-  X(128, 6, false, EPI_SPLIT, false, false, 64) X(kTcBlockN, 4, false, EPI_SPLIT, false, false, 64)        \
-  X(kTcBlockN, 6, false, EPI_SPLIT, true, false, 64)                                                       \
+  X(128, 4, true, EPI_SPLIT, false, true, 64, 128) X(kTcBlockN, 3, true, EPI_SPLIT, false, true, 64, 128)            \
+  X(128, 4, true, EPI_SPLIT, false, false, 64, 128) X(kTcBlockN, 3, true, EPI_SPLIT, false, false, 64, 128)          \
+  X(kTcBlockN, 2, true, EPI_RELAY, false, false, 64, 128) X(kTcBlockN, 3, true, EPI_RELAY, false, false, 64, 128)    \
+  X(kTcBlockN, 4, true, EPI_SINGLE, false, false, 64, 128)                                                      \
+  X(128, 6, false, EPI_SPLIT, false, true, 64, 128) X(kTcBlockN, 4, false, EPI_SPLIT, false, true, 64, 128)          \
+  X(128, 6, false, EPI_SPLIT, false, false, 64, 128) X(kTcBlockN, 4, false, EPI_SPLIT, false, false, 64, 128)        \
+  X(kTcBlockN, 6, false, EPI_SPLIT, true, false, 64, 128)                                                       \
   /* other stage depths (the schedule's tileK): eight-warp epilogue, f16 output */                        \
-  X(128, 8, true, EPI_SPLIT, false, false, 32) X(kTcBlockN, 6, true, EPI_SPLIT, false, false, 32)          \
-  X(128, 12, false, EPI_SPLIT, false, false, 32) X(kTcBlockN, 8, false, EPI_SPLIT, false, false, 32)       \
-  X(128, 2, true, EPI_SPLIT, false, false, 128)                                                            \
-  X(128, 3, false, EPI_SPLIT, false, false, 128) X(kTcBlockN, 2, false, EPI_SPLIT, false, false, 128)
+  X(128, 8, true, EPI_SPLIT, false, false, 32, 128) X(kTcBlockN, 6, true, EPI_SPLIT, false, false, 32, 128)          \
+  X(128, 12, false, EPI_SPLIT, false, false, 32, 128) X(kTcBlockN, 8, false, EPI_SPLIT, false, false, 32, 128)       \
+  X(128, 2, true, EPI_SPLIT, false, false, 128, 128)                                                            \
+  X(128, 3, false, EPI_SPLIT, false, false, 128, 128) X(kTcBlockN, 2, false, EPI_SPLIT, false, false, 128, 128)       \
+  /* 64-row tiles (the schedule's tileM = 64), stage depth 32 or 64 */                                         \
+  X(128, 4, true, EPI_SPLIT, false, false, 64, 64) X(kTcBlockN, 3, true, EPI_SPLIT, false, false, 64, 64)      \
+  X(128, 6, false, EPI_SPLIT, false, false, 64, 64) X(kTcBlockN, 4, false, EPI_SPLIT, false, false, 64, 64)    \
+  X(128, 8, true, EPI_SPLIT, false, false, 32, 64) X(kTcBlockN, 6, true, EPI_SPLIT, false, false, 32, 64)      \
+  X(128, 12, false, EPI_SPLIT, false, false, 32, 64) X(kTcBlockN, 8, false, EPI_SPLIT, false, false, 32, 64)
 
 // Form choice.  Cluster flavour: f32 probabilities and 128-column tiles take the split
 // epilogue; 256-column f16 tiles take the relay when a CTA sees several tiles (its two groups
@@ -1148,40 +1159,43 @@ cudaError_t launch_impl(const CUtensorMap &tmA, const CUtensorMap &tmB, const CU
 // tile per storing warp), the single-tile form when every cluster fits the chip at once, the
 // split form otherwise or on request.  Tiled flavour: two CTAs share one 256-row MMA (a third
 // less L2 operand traffic per flop) when the K loop is long and there are two row blocks.
-bool tc_stage_depth_legal(bool tiled, int bn, bool out_f32, int kd) {
+bool tc_stage_depth_legal(bool tiled, int bn, bool out_f32, int kd, int tm) {
+  if (tm != kTcBlockM && (tm != 64 || out_f32 || kd == 128)) return false;
   if (kd == kTcBlockK) return true;
   if (out_f32 || (kd != 32 && kd != 128)) return false;
   return kd == 32 || bn == 128 || tiled;     // 128-deep stages of 256-column tiles leave no room for a cluster's statistics
 }
 
 TcVariant tc_choose_variant(bool tiled, int bn, bool out_f32, int batch, int num_rb, int num_kb, int cluster_n,
-                            int epilogue_mode, int pair_mode, int num_sms, int resident, int kd) {
-  if (kd != kTcBlockK && tc_stage_depth_legal(tiled, bn, out_f32, kd)) {
-    // same bytes of operands in flight as the default depth
-    if (tiled) return bn == 128 ? TcVariant{128, kd == 32 ? 12 : 3, 0, EPI_SPLIT, 0, 0, kd} : TcVariant{kTcBlockN, kd == 32 ? 8 : 2, 0, EPI_SPLIT, 0, 0, kd};
-    return bn == 128 ? TcVariant{128, kd == 32 ? 8 : 2, 1, EPI_SPLIT, 0, 0, kd} : TcVariant{kTcBlockN, 6, 1, EPI_SPLIT, 0, 0, kd};
+                            int epilogue_mode, int pair_mode, int num_sms, int resident, int kd, int tm) {
+  if ((kd != kTcBlockK || tm != kTcBlockM) && tc_stage_depth_legal(tiled, bn, out_f32, kd, tm)) {
+    // as many stages as keep the default's K depth in flight (more than its bytes, with 64-row tiles)
+    const int st_cl = bn == 128 ? (kd == 32 ? 8 : (kd == 64 ? 4 : 2)) : (kd == 32 ? 6 : 3);
+    const int st_ti = bn == 128 ? (kd == 32 ? 12 : (kd == 64 ? 6 : 3)) : (kd == 32 ? 8 : (kd == 64 ? 4 : 2));
+    return tiled ? TcVariant{bn == 128 ? 128 : kTcBlockN, st_ti, 0, EPI_SPLIT, 0, 0, kd, tm}
+                 : TcVariant{bn == 128 ? 128 : kTcBlockN, st_cl, 1, EPI_SPLIT, 0, 0, kd, tm};
   }
   if (tiled) {
-    if (out_f32) return bn == 128 ? TcVariant{128, 6, 0, EPI_SPLIT, 0, 1, kTcBlockK} : TcVariant{kTcBlockN, 4, 0, EPI_SPLIT, 0, 1, kTcBlockK};
-    if (bn == 128) return TcVariant{128, 6, 0, EPI_SPLIT, 0, 0, kTcBlockK};
+    if (out_f32) return bn == 128 ? TcVariant{128, 6, 0, EPI_SPLIT, 0, 1, kTcBlockK, kTcBlockM} : TcVariant{kTcBlockN, 4, 0, EPI_SPLIT, 0, 1, kTcBlockK, kTcBlockM};
+    if (bn == 128) return TcVariant{128, 6, 0, EPI_SPLIT, 0, 0, kTcBlockK, kTcBlockM};
     const bool pair = num_rb >= 2 && (pair_mode == 2 || (pair_mode == 0 && num_kb >= 8));
-    return pair ? TcVariant{kTcBlockN, 6, 0, EPI_SPLIT, 1, 0, kTcBlockK} : TcVariant{kTcBlockN, 4, 0, EPI_SPLIT, 0, 0, kTcBlockK};
+    return pair ? TcVariant{kTcBlockN, 6, 0, EPI_SPLIT, 1, 0, kTcBlockK, kTcBlockM} : TcVariant{kTcBlockN, 4, 0, EPI_SPLIT, 0, 0, kTcBlockK, kTcBlockM};
   }
-  if (out_f32) return bn == 128 ? TcVariant{128, 4, 1, EPI_SPLIT, 0, 1, kTcBlockK} : TcVariant{kTcBlockN, 3, 1, EPI_SPLIT, 0, 1, kTcBlockK};
-  if (bn == 128) return TcVariant{128, 4, 1, EPI_SPLIT, 0, 0, kTcBlockK};
+  if (out_f32) return bn == 128 ? TcVariant{128, 4, 1, EPI_SPLIT, 0, 1, kTcBlockK, kTcBlockM} : TcVariant{kTcBlockN, 3, 1, EPI_SPLIT, 0, 1, kTcBlockK, kTcBlockM};
+  if (bn == 128) return TcVariant{128, 4, 1, EPI_SPLIT, 0, 0, kTcBlockK, kTcBlockM};
   const int per_round = num_sms / (cluster_n > 0 ? cluster_n : 1);
   const int units = batch * num_rb;
   const int tiles_per_cta = (units + per_round - 1) / (per_round > 0 ? per_round : 1);
   const bool relay = epilogue_mode == kEpilogueRelay || (epilogue_mode == kEpilogueAuto && tiles_per_cta >= kRelayMinTiles);
-  if (relay) return TcVariant{kTcBlockN, num_kb <= 3 ? 2 : 3, 1, EPI_RELAY, 0, 0, kTcBlockK};
-  if (epilogue_mode == kEpilogueAuto && units <= resident) return TcVariant{kTcBlockN, 4, 1, EPI_SINGLE, 0, 0, kTcBlockK};
-  return TcVariant{kTcBlockN, 3, 1, EPI_SPLIT, 0, 0, kTcBlockK};
+  if (relay) return TcVariant{kTcBlockN, num_kb <= 3 ? 2 : 3, 1, EPI_RELAY, 0, 0, kTcBlockK, kTcBlockM};
+  if (epilogue_mode == kEpilogueAuto && units <= resident) return TcVariant{kTcBlockN, 4, 1, EPI_SINGLE, 0, 0, kTcBlockK, kTcBlockM};
+  return TcVariant{kTcBlockN, 3, 1, EPI_SPLIT, 0, 0, kTcBlockK, kTcBlockM};
 }
 
 int tc_variant_smem_bytes(const TcVariant &v) {
-#define X(BN, ST, CL, EP, PA, O32, KD) \
-  if (v.bn == BN && v.stages == ST && (v.cluster != 0) == CL && v.epi == EP && (v.pair != 0) == PA && (v.out32 != 0) == O32 && v.kd == KD) \
-    return SmemLayout<BN, ST, CL, EP, PA, O32, KD>::kDynamic;
+#define X(BN, ST, CL, EP, PA, O32, KD, TM) \
+  if (v.bn == BN && v.stages == ST && (v.cluster != 0) == CL && v.epi == EP && (v.pair != 0) == PA && (v.out32 != 0) == O32 && v.kd == KD && v.tm == TM) \
+    return SmemLayout<BN, ST, CL, EP, PA, O32, KD, TM>::kDynamic;
   WTC_TC_VARIANTS(X)
 #undef X
   return 0;
@@ -1192,9 +1206,9 @@ int tc_variant_threads(const TcVariant &v) { return kThreadsFor(v.epi); }
 namespace {
 cudaError_t launch_variant(const TcVariant &v, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO,
                            const TcParams &p, int cluster_n, int num_sms, cudaStream_t s, TcLaunchInfo *info) {
-#define X(BN, ST, CL, EP, PA, O32, KD) \
-  if (v.bn == BN && v.stages == ST && (v.cluster != 0) == CL && v.epi == EP && (v.pair != 0) == PA && (v.out32 != 0) == O32 && v.kd == KD) \
-    return launch_impl<BN, ST, CL, EP, PA, O32, KD>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
+#define X(BN, ST, CL, EP, PA, O32, KD, TM) \
+  if (v.bn == BN && v.stages == ST && (v.cluster != 0) == CL && v.epi == EP && (v.pair != 0) == PA && (v.out32 != 0) == O32 && v.kd == KD && v.tm == TM) \
+    return launch_impl<BN, ST, CL, EP, PA, O32, KD, TM>(tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
   WTC_TC_VARIANTS(X)
 #undef X
   return cudaErrorInvalidConfiguration;
@@ -1208,11 +1222,11 @@ cudaError_t launch_fused_cluster(const CUtensorMap &tmA, const CUtensorMap &tmB,
   // the single-tile form is tried whenever one tile per CTA is possible at all; it declines
   // (before launching) when the clusters do not all fit the chip at once, and the split form runs
   TcVariant v = tc_choose_variant(false, bn, p.out_f32 != 0, p.batch, p.num_rb, p.num_kb, cluster_n, p.epilogue_mode, p.pair_mode,
-                                  num_sms, /*resident=*/1 << 30, p.stage_k ? p.stage_k : kTcBlockK);
+                                  num_sms, /*resident=*/1 << 30, p.stage_k ? p.stage_k : kTcBlockK, p.tile_rows ? p.tile_rows : kTcBlockM);
   if (v.epi == EPI_SINGLE) {
     const cudaError_t e = launch_variant(v, tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
     if (e != cudaErrorNotSupported) return e;
-    v = TcVariant{kTcBlockN, 3, 1, EPI_SPLIT, 0, 0, kTcBlockK};
+    v = TcVariant{kTcBlockN, 3, 1, EPI_SPLIT, 0, 0, kTcBlockK, kTcBlockM};
   }
   return launch_variant(v, tmA, tmB, tmO, p, cluster_n, num_sms, s, info);
 }
@@ -1220,7 +1234,7 @@ cudaError_t launch_fused_cluster(const CUtensorMap &tmA, const CUtensorMap &tmB,
 cudaError_t launch_tiled_partial(const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmO,
                                  const TcParams &p, int bn, int num_sms, cudaStream_t s, TcLaunchInfo *info) {
   const TcVariant v = tc_choose_variant(true, bn, p.out_f32 != 0, p.batch, p.num_rb, p.num_kb, 1, p.epilogue_mode, p.pair_mode, num_sms, 0,
-                                        p.stage_k ? p.stage_k : kTcBlockK);
+                                        p.stage_k ? p.stage_k : kTcBlockK, p.tile_rows ? p.tile_rows : kTcBlockM);
   return launch_variant(v, tmA, tmB, tmO, p, 1, num_sms, s, info);
 }
 

@@ -27,6 +27,7 @@ struct TcParams {
   int use_pdl;     // launch with programmatic stream serialisation
   int round_logits_f16;  // chain spelled with an f16 matmul result: round s to f16 before the softmax
   int stage_k;     // K depth of a pipeline stage (0: 64)
+  int tile_rows;   // rows of a tile (0: 128)
   int logits_only; // tiled flavour, f32 output: store scale * A . B and stop (the unfused baseline's first kernel)
   float scale;     // the chain's scale factor
   float c2;        // scale * log2(e)
@@ -46,14 +47,15 @@ struct TcLaunchInfo {
 struct TcVariant {
   int bn, stages, cluster, epi, pair, out32;
   int kd;    // K depth of one pipeline stage: 64, or the schedule's tileK when it is 32 or 128 and legal
+  int tm;    // rows of a tile: 128, or the schedule's tileM when it is 64 and legal
 };
 // The variant the launchers below take for a call, worked out without a device: `resident` is how
 // many clusters of `cluster_n` CTAs the chip holds at once (the launchers ask the runtime; a plan
 // made without a device uses the figures measured on a 148-SM part).
 TcVariant tc_choose_variant(bool tiled, int bn, bool out_f32, int batch, int num_rb, int num_kb, int cluster_n,
-                            int epilogue_mode, int pair_mode, int num_sms, int resident, int kd = 64);
-// Whether a stage depth other than 64 has a kernel for this flavour, column tile and output type.
-bool tc_stage_depth_legal(bool tiled, int bn, bool out_f32, int kd);
+                            int epilogue_mode, int pair_mode, int num_sms, int resident, int kd = 64, int tm = 128);
+// Whether this stage depth and tile height have a kernel for this flavour, column tile and output type.
+bool tc_stage_depth_legal(bool tiled, int bn, bool out_f32, int kd, int tm = 128);
 // Dynamic shared memory and threads per CTA of a variant (0 if it is not instantiated).
 int tc_variant_smem_bytes(const TcVariant &v);
 int tc_variant_threads(const TcVariant &v);

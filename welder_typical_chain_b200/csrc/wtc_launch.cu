@@ -45,13 +45,13 @@ const int g_use_pdl = [] { const char *e = getenv("WTC_NO_PDL"); return (e && e[
 
 // registers / spills / stack of every instance of the tensor-core kernel template, from the
 // `ptxas -v` report of this build (generated beside the objects)
-struct KernelFacts { int bn, stages, cluster, epi, pair, out32, kd, registers, spill_store, spill_load, stack; };
+struct KernelFacts { int bn, stages, cluster, epi, pair, out32, kd, tm, registers, spill_store, spill_load, stack; };
 const KernelFacts kKernelFacts[] = {
 #include "build/kernel_facts.inc"
 };
 const KernelFacts *facts_of(const wtc::TcVariant &v) {
   for (const KernelFacts &f : kKernelFacts)
-    if (f.bn == v.bn && f.stages == v.stages && f.cluster == (v.cluster != 0) && f.epi == v.epi && f.pair == (v.pair != 0) && f.out32 == (v.out32 != 0) && f.kd == v.kd)
+    if (f.bn == v.bn && f.stages == v.stages && f.cluster == (v.cluster != 0) && f.epi == v.epi && f.pair == (v.pair != 0) && f.out32 == (v.out32 != 0) && f.kd == v.kd && f.tm == v.tm)
       return &f;
   return nullptr;
 }
@@ -60,6 +60,7 @@ struct Resolved {
   wtc_chain_desc d;  // strides filled in
   wtc_plan_info plan;
   int bn;            // column tile of the tensor-core kernels: 256, or 128 when best.json asks for it
+  int tm;            // rows of a tile: 128, or best.json's tileM when it is 64 and a kernel exists for it
   int kd;            // K depth of a pipeline stage: 64, or best.json's tileK when it is 32 or 128 and a kernel exists for it
   int num_rb, num_nb, num_kb;
   bool b_batched;
@@ -129,6 +130,7 @@ int resolve(const wtc_chain_desc *in, Resolved &r) {
   wtc_plan_info &p = r.plan;
   memset(&p, 0, sizeof(p));
   p.cluster_n = 1;
+  r.tm = wtc::kTcBlockM;
   r.num_rb = static_cast<int>((d.M + wtc::kTcBlockM - 1) / wtc::kTcBlockM);
   // tileN = 128 is the second legal column tile; everything else resolves to 256.  Without a
   // tile hint the 128-column kernels are taken (a) for rows of at most 128 columns (half of a
@@ -150,13 +152,18 @@ int resolve(const wtc_chain_desc *in, Resolved &r) {
   // tileK is the K depth of one pipeline stage.  64 is the default; 32 and 128 have kernels in the
   // eight-warp epilogue family (f16 probabilities, no forced epilogue form or CTA pair; 128 deep with
   // 256-column tiles only in the tiled flavour, where no cluster statistics compete for the room).
+  // tileM = 64 (tcgen05.mma with M = 64) has kernels in the same family, for stages 32 or 64 deep.
   r.kd = wtc::kTcBlockK;
   {
     const bool tiled_shape = r.num_nb > 8 || (d.flags & WTC_FLAG_FORCE_TILED);
     const int forced = WTC_FLAG_EPILOGUE_SPLIT | WTC_FLAG_EPILOGUE_RELAY | WTC_FLAG_PAIR;
-    if ((d.tile_k == 32 || d.tile_k == 128) && d.variant == WTC_VARIANT_FUSED && !(d.flags & forced) &&
-        wtc::tc_stage_depth_legal(tiled_shape, r.bn, d.out_dtype == WTC_F32, d.tile_k))
-      r.kd = d.tile_k;
+    const bool family = d.variant == WTC_VARIANT_FUSED && !(d.flags & forced);
+    const bool f32o = d.out_dtype == WTC_F32;
+    if ((d.tile_k == 32 || d.tile_k == 128) && family && wtc::tc_stage_depth_legal(tiled_shape, r.bn, f32o, d.tile_k)) r.kd = d.tile_k;
+    if (d.tile_m == 64 && family && wtc::tc_stage_depth_legal(tiled_shape, r.bn, f32o, r.kd, 64)) {
+      r.tm = 64;
+      r.num_rb = static_cast<int>((d.M + 63) / 64);
+    }
   }
   r.num_kb = static_cast<int>((d.K + r.kd - 1) / r.kd);
 
@@ -185,7 +192,7 @@ int resolve(const wtc_chain_desc *in, Resolved &r) {
       p.tile_m = 8; p.tile_n = static_cast<int32_t>(d.N); p.tile_k = 64;
     }
   } else if (r.tc_ok) {
-    p.tile_m = wtc::kTcBlockM; p.tile_n = r.bn; p.tile_k = r.kd;
+    p.tile_m = r.tm; p.tile_n = r.bn; p.tile_k = r.kd;
     p.tmem_columns = 2 * r.bn;
     // variant, threads, stages as the launchers choose them on a 148-SM part (the plan is made
     // without a device): clusters of n CTAs resident at once, measured (8: 15; others: one short of 148 / n)
@@ -196,7 +203,7 @@ int resolve(const wtc_chain_desc *in, Resolved &r) {
     const bool cluster = r.num_nb <= 8 && !(d.flags & WTC_FLAG_FORCE_TILED);
     const wtc::TcVariant v = wtc::tc_choose_variant(!cluster, r.bn, d.out_dtype == WTC_F32, d.batch, r.num_rb, r.num_kb,
                                                     cluster ? r.num_nb : 1, epi_mode, pair_mode, 148,
-                                                    cluster ? kResidentClusters[r.num_nb] : 0, r.kd);
+                                                    cluster ? kResidentClusters[r.num_nb] : 0, r.kd, r.tm);
     p.threads = wtc::tc_variant_threads(v);
     p.stages = v.stages;
     p.smem_bytes = wtc::tc_variant_smem_bytes(v);
@@ -435,17 +442,17 @@ int launch_resolved(Resolved &r, const void *A, const void *B, void *Out, void *
     if (sms <= 0) return fail(WTC_E_CUDA, "no usable CUDA device");
     CUtensorMap tmA, tmB, tmO;
     // A's box is one swizzle span wide at most: 64 columns (a 128-deep stage takes two), or 32 with the 64-byte swizzle
-    int rc = get_map(A, d.K, d.M, d.batch, d.lda * 2, d.a_batch_stride * 2, r.kd < 64 ? r.kd : 64, wtc::kTcBlockM, &tmA, false, 0, 0, 1, r.kd == 32);
+    int rc = get_map(A, d.K, d.M, d.batch, d.lda * 2, d.a_batch_stride * 2, r.kd < 64 ? r.kd : 64, r.tm, &tmA, false, 0, 0, 1, r.kd == 32);
     if (rc) return rc;
     // (a CTA pair loads half of the tile's columns per CTA: the variant decides the box)
     const int pm = (d.flags & WTC_FLAG_NO_PAIR) ? 1 : ((d.flags & WTC_FLAG_PAIR) ? 2 : 0);
-    const wtc::TcVariant v = wtc::tc_choose_variant(tiled, r.bn, d.out_dtype == WTC_F32, d.batch, r.num_rb, r.num_kb, tiled ? 1 : r.num_nb, 0, pm, sms, 0, r.kd);
+    const wtc::TcVariant v = wtc::tc_choose_variant(tiled, r.bn, d.out_dtype == WTC_F32, d.batch, r.num_rb, r.num_kb, tiled ? 1 : r.num_nb, 0, pm, sms, 0, r.kd, r.tm);
     int b_blocks = 0;
     rc = get_map_b(B, r, v.pair ? r.bn / 128 : r.bn / 64, &tmB, &b_blocks);
     if (rc) return rc;
     const bool out32 = d.out_dtype == WTC_F32;
     rc = out32 ? get_map(Out, d.N, d.M, d.batch, d.ldo * 4, d.o_batch_stride * 4, 32, 32, &tmO, true)
-               : get_map(Out, d.N, d.M, d.batch, d.ldo * 2, d.o_batch_stride * 2, 64, 32, &tmO);
+               : get_map(Out, d.N, d.M, d.batch, d.ldo * 2, d.o_batch_stride * 2, 64, r.tm / 4, &tmO);   // a warp stores its quarter of the tile's rows
     if (rc) return rc;
 
     wtc::TcParams p;
@@ -464,6 +471,7 @@ int launch_resolved(Resolved &r, const void *A, const void *B, void *Out, void *
     p.use_pdl = g_use_pdl;
     p.out_f32 = out32;
     p.stage_k = r.kd;
+    p.tile_rows = r.tm;
     p.pair_mode = (d.flags & WTC_FLAG_NO_PAIR) ? 1 : ((d.flags & WTC_FLAG_PAIR) ? 2 : 0);
     p.epilogue_mode = (d.flags & WTC_FLAG_EPILOGUE_SPLIT) ? wtc::kEpilogueSplit
                       : ((d.flags & WTC_FLAG_EPILOGUE_RELAY) ? wtc::kEpilogueRelay : wtc::kEpilogueAuto);
