@@ -52,17 +52,17 @@ namespace wtc {
 namespace {
 
 constexpr int BM = kTcBlockM;
-constexpr int BK = kTcBlockK;
 constexpr int kMaxCluster = 8;
 enum : int { EPI_SPLIT = 0, EPI_RELAY = 1, EPI_SINGLE = 2 };
 constexpr int kThreadsFor(int epi) { return epi == EPI_SPLIT ? 320 : (epi == EPI_RELAY ? 640 : 576); }
 
 // UMMA shared-memory descriptor geometry (bytes).
 //   A (K-major, 128-byte swizzle): 8-row groups are 1024 B apart; one 16-wide K step is 32 B.
-//   B (MN-major, 128-byte swizzle): 64-column blocks are 64 k-rows * 128 B = 8192 B apart
-//   (leading), 8-k-row groups are 1024 B apart (stride); one 16-deep K step is 16 * 128 B.
+//   B (MN-major, 128-byte swizzle): 64-column blocks are (k-rows of a stage) * 128 B apart
+//   (leading: 8192 B for 64-deep stages), 8-k-row groups are 1024 B apart (stride); one
+//   16-deep K step is 16 * 128 B.
 constexpr uint32_t kALbo = 16, kASbo = 1024, kAKstep = 32;
-constexpr uint32_t kBLbo = 8192, kBSbo = 1024, kBKstep = 2048;
+constexpr uint32_t kBSbo = 1024, kBKstep = 2048;
 
 // KD: the K depth of one pipeline stage (the schedule's tileK): 64 by default; 32 and 128 for
 // the eight-warp epilogue forms.  A's 128 rows are then staged as 64-byte rows with the 64-byte
@@ -208,7 +208,7 @@ __global__ void __launch_bounds__(kThreadsFor(EPI), 1)
 fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmO, const TcParams p) {
   using L = SmemLayout<BN, STAGES, CLUSTER, EPI, PAIR, OUT32, KD, TM>;
-  constexpr int BK = KD;                // K depth of a stage (hides the default of the same name)
+  constexpr int BK = KD;                // K depth of a stage
   constexpr int A_BOXES = KD == 128 ? 2 : 1;   // A's copies per stage: a box is at most one swizzle span (64 columns) wide
   constexpr bool RELAY = L::RELAY;
   constexpr bool SINGLE = L::SINGLE;
