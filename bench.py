@@ -54,10 +54,16 @@ HBM_BOUND = ("cfg3", "cfg5")
 # profiles/ (dram__bytes_read.sum + dram__bytes_write.sum of ONE captured launch; output lines that
 # are still in L2 when the launch ends are not in the write figure).
 NCU_TRAFFIC = {
-    "cfg2": dict(bytes=10555648, capture="profiles/fused_tc_kernel_cfg2_4096x1024x1024.md",
-                 note="single cold launch; the 8.39 MB of output was still in L2 when it ended and is not counted"),
-    "cfg3": dict(bytes=545029632, capture="profiles/fused_tc_kernel_cfg3_batched_attention.md", note="single launch"),
-    "cfg5": dict(bytes=267214336, capture="profiles/fused_tc_kernel_cfg5_skinny_decode.md", note="tiled kernel + rescale pass"),
+    "cfg2": dict(bytes=10550016, capture="profiles/fused_tc_kernel_cfg2_4096x1024x1024.md",
+                 note="single cold launch, write-back not counted: the 8.39 MB of output was still in L2 when it ended"),
+    "cfg3": dict(bytes=546158336, capture="profiles/fused_tc_kernel_cfg3_batched_64x2048x2048x128.md",
+                 note="single launch; 58 MB of the output was still in L2 when it ended"),
+    "cfg4": dict(bytes=2172000000, capture="profiles/fused_tc_kernel_cfg4_tiled_pair_1024x32000x4096.md",
+                 note="both kernels, scaled from a capture at M = 1024 by the rows processed (B streamed once per 4096 rows)"),
+    "cfg4s": dict(bytes=407866368, capture="profiles/fused_tc_kernel_cfg4_tiled_pair_1024x32000x4096.md",
+                  note="both kernels, single launches"),
+    "cfg5": dict(bytes=266929664, capture="profiles/fused_tc_kernel_cfg5_skinny_16x32000x4096.md",
+                 note="both kernels, single launches"),
 }
 
 
@@ -452,9 +458,11 @@ def roofline_of(res, pk):
     roof["peak_source"] = pk["source"]
     roof["per"] = "GPU (whole-job figure / n_gpus); step time = max over ranks"
     t = NCU_TRAFFIC.get(name)
-    roof["traffic"] = t["bytes"] if t else None
+    world = max(1, res.get("world", 1))
+    strong = WORKLOADS[name]["shard"] in ("batch", "cols")      # the whole workload is cut over the GPUs
+    roof["traffic"] = (t["bytes"] // world if strong else t["bytes"]) if t else None
     if t:
-        roof["traffic_source"] = f"{t['capture']}: {t['note']}"
+        roof["traffic_source"] = f"{t['capture']}: {t['note']}" + (f"; divided by the {world} GPUs that share the workload" if strong and world > 1 else "")
     roof["algorithmic_per_launch"] = dict(flops=res["flops_step"], bytes=res["bytes_step"])
     return roof
 

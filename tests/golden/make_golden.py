@@ -60,7 +60,9 @@ def special_floats():
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    here = os.path.dirname(os.path.abspath(__file__))
+    ap.add_argument("--reference", default=os.environ.get("WTC_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(here))), "reference"),
+                    help="the reference tree ($WTC_REFERENCE_ROOT, else a directory `reference` beside this repository)")
     args = ap.parse_args()
     ref = load_ref_checker(args.reference)
 

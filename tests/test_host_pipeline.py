@@ -341,7 +341,8 @@ def test_chains_that_are_not_the_operator_are_rejected(tmp_path):
         assert run(["--input", str(path), "--out-dir", str(tmp_path / "g"), "--search-only", "--backend-mode", "api"]).returncode == 0
 
 
-REFERENCE_ROOT = os.environ.get("WTC_REFERENCE_ROOT", "/root/reference")
+# the reference tree: $WTC_REFERENCE_ROOT, else a directory `reference` beside this repository
+REFERENCE_ROOT = os.environ.get("WTC_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
 
 
 @pytest.mark.skipif(not os.path.isdir(os.path.join(REFERENCE_ROOT, "mlir")), reason="the reference tree is not mounted here")
