@@ -163,6 +163,22 @@ int wtc_matmul_softmax_finish_launch(const wtc_chain_desc *desc, void *Out, cons
 int wtc_matmul_softmax_host(const wtc_chain_desc *desc, const void *hostA, const void *hostB, void *hostOut);
 
 /*
+ * The same call in two halves, for callers with a stream of chains: submit
+ * enqueues the copies and kernels and returns a ticket; wait blocks until that
+ * call's results (and its device status) are in host memory.  A thread has two
+ * slots of device buffers: with two calls in flight (submit i+1, then wait i) the
+ * operands of one call travel to the device while the rows of the other travel
+ * back, and the link is busy in both directions all the time.  A third submit
+ * first waits for the oldest call itself.  The host buffers of a call must stay
+ * valid, and hostOut unread, until its wait returns.  Tickets belong to the
+ * thread that issued them; waiting twice, or for a ticket of -1 (an empty call),
+ * returns WTC_OK at once.  wtc_matmul_softmax_host is submit followed by wait.
+ */
+int wtc_matmul_softmax_host_submit(const wtc_chain_desc *desc, const void *hostA, const void *hostB, void *hostOut,
+                                   int64_t *ticket);
+int wtc_matmul_softmax_host_wait(int64_t ticket);
+
+/*
  * Same chain, for callers that must not allocate device memory.  (No counterpart
  * in the reference: its profiler allocates every buffer itself with cuMemAlloc.)
  *

@@ -255,6 +255,43 @@ def test_host_buffer_entry_point(w, cuda_dev):
     _check(w.matmul_softmax_host(A32, B32, 1.0), oracle.chain(A32, B32, 1.0))
 
 
+def test_host_calls_in_flight(w, cuda_dev):
+    """submit / wait: several calls with different operands through the two slots of device buffers, two in
+    flight at a time, waited for in order, out of order and twice; each result against the CPU checker."""
+    import torch
+    M, N, K = 700, 1024, 192
+    hc = w.HostChain(1, M, N, K, 0.07)
+    As = [torch.from_numpy(oracle.normal((M, K), 90 + i)).pin_memory().numpy() for i in range(5)]
+    B = torch.from_numpy(oracle.normal((K, N), 99)).pin_memory().numpy()
+    outs = [torch.empty((M, N), dtype=torch.float16).pin_memory().numpy() for _ in range(5)]
+    tickets = []
+    for i in range(5):
+        tickets.append(hc.submit(As[i], B, outs[i]))       # the third submit waits for the first call itself
+        if i >= 1 and i % 2 == 1:
+            hc.wait(tickets[i - 1])
+    assert tickets == list(range(tickets[0], tickets[0] + 5))
+    for t in reversed(tickets):
+        hc.wait(t)
+    hc.wait(tickets[2])                                     # waiting twice is fine
+    hc.wait(-1)
+    with pytest.raises(w.WtcError):
+        hc.wait(tickets[-1] + 7)                            # never issued
+    for i in range(5):
+        _check(outs[i], oracle.chain(As[i], B, 0.07))
+    # a batched chain with a B per batch, two-pass tiled schedule per slab, between two cluster calls
+    hb = w.HostChain(3, 200, 2304, 64, 0.125)
+    Ab = torch.from_numpy(oracle.normal((3, 200, 64), 81)).pin_memory().numpy()
+    Bb = torch.from_numpy(oracle.normal((3, 64, 2304), 82)).pin_memory().numpy()
+    ob = torch.empty((3, 200, 2304), dtype=torch.float16).pin_memory().numpy()
+    t0 = hc.submit(As[0], B, outs[1])
+    t1 = hb.submit(Ab, Bb, ob)
+    hb.wait(t1)
+    hc.wait(t0)
+    _check(ob, np.stack([oracle.chain(Ab[b], Bb[b], 0.125) for b in range(3)]))
+    assert np.array_equal(outs[1], outs[0])
+    assert np.array_equal(w.matmul_softmax_host(As[3], B, 0.07), outs[3])   # the one-call form is submit + wait
+
+
 @pytest.mark.parametrize("slabs", ["1", "3", "8"])
 def test_host_entry_point_slabs(w, cuda_dev, monkeypatch, slabs):
     """The host-buffer call moves row ranges (or batch ranges) through copy-in, compute and

@@ -620,12 +620,52 @@ int wtc_matmul_softmax_time(const wtc_chain_desc *desc, const void *A, const voi
 // of a batched call) that move through three streams -- copy in, compute, copy out -- so the
 // transfer of slab i+1 and the read-back of slab i-1 run under the kernel of slab i and the
 // two PCIe directions are busy at the same time.  B goes first, whole.
-int wtc_matmul_softmax_host(const wtc_chain_desc *desc, const void *hostA, const void *hostB, void *hostOut) {
+// ---- calls with host buffers ---------------------------------------------------
+// Per host thread: three streams (copies in, kernels, copies back) shared by all calls, and
+// two slots of device buffers, so that a second call's operands travel to the device while
+// the first call's rows are still on their way back: a caller that keeps two calls in flight
+// (submit i+1, then wait for i) keeps both directions of the link busy all the time.
+namespace {
+constexpr int kMaxSlabs = 16;
+constexpr int kHostSlots = 2;
+struct HostBuf { void *p = nullptr; size_t cap = 0; };
+struct HostSlot {
+  HostBuf bufs[4];                    // A, B, Out, workspace
+  cudaEvent_t finished = nullptr;     // recorded behind the slot's last copy back
+  int *host_status = nullptr;         // pinned: the device status word as the call left it
+  int64_t ticket = -1;                // the call in flight in this slot, or -1
+};
+struct HostSlab { Resolved r; size_t a_off, a_len, o_off, o_len, b_off, b_len; };
+struct HostCtx {
+  int dev = -1;
+  cudaStream_t in = nullptr, run = nullptr, out = nullptr;
+  cudaEvent_t a_in[kMaxSlabs] = {}, done[kMaxSlabs] = {};
+  HostSlot slot[kHostSlots];
+  int64_t next_ticket = 0;
+  // slab schedule of the last descriptor
+  wtc_chain_desc key; int key_dev = -1; int slab_env = 0; int n = 0; HostSlab slabs[kMaxSlabs];
+};
+HostCtx &host_ctx() { thread_local HostCtx c; return c; }
+
+int host_wait_slot(HostCtx &hc, HostSlot &sl) {
+  if (sl.ticket < 0) return WTC_OK;
+  sl.ticket = -1;
+  cudaError_t e = cudaEventSynchronize(sl.finished);
+  if (e != cudaSuccess) return cuda_fail(e, "waiting for the results");
+  const int v = *sl.host_status;
+  if (v != 0) cudaMemsetAsync(default_status(), 0, sizeof(int), hc.out);   // reported once, then cleared
+  return status_result(v);
+}
+} // namespace
+
+int wtc_matmul_softmax_host_submit(const wtc_chain_desc *desc, const void *hostA, const void *hostB, void *hostOut, int64_t *ticket) {
+  if (!ticket) return fail(WTC_E_ARG, "null ticket pointer");
+  *ticket = -1;
   Resolved r;
   int rc = resolve(desc, r);
   if (rc) return rc;
   const wtc_chain_desc &d = r.d;
-  if (d.M == 0 || d.N == 0) return WTC_OK;
+  if (d.M == 0 || d.N == 0) return WTC_OK;        // nothing to do: ticket -1 is always complete
   if (!hostA || !hostB || !hostOut) return fail(WTC_E_ARG, "null host pointer");
   const size_t in_sz = d.in_dtype == WTC_F16 ? 2 : 4, out_sz = d.out_dtype == WTC_F16 ? 2 : 4;
   const size_t a_bytes = static_cast<size_t>(d.batch) * d.a_batch_stride * in_sz;
@@ -633,56 +673,58 @@ int wtc_matmul_softmax_host(const wtc_chain_desc *desc, const void *hostA, const
   const size_t o_bytes = static_cast<size_t>(d.batch) * d.o_batch_stride * out_sz;
   const size_t w_bytes = r.plan.workspace_bytes;
 
-  struct Buf { void *p = nullptr; size_t cap = 0; int dev = -1; };
-  thread_local Buf bufs[4];
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
-  const size_t want[4] = {a_bytes, b_bytes, o_bytes, w_bytes};
-  for (int i = 0; i < 4; ++i) {
-    if (bufs[i].dev != dev || bufs[i].cap < want[i]) {
-      if (bufs[i].p && bufs[i].dev == dev) cudaFree(bufs[i].p);
-      bufs[i].p = nullptr; bufs[i].cap = 0; bufs[i].dev = dev;
-      if (want[i]) {
-        e = cudaMalloc(&bufs[i].p, want[i]);
-        if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc (host-buffer entry point)");
-        bufs[i].cap = want[i];
-      }
-    }
-  }
-  constexpr int kMaxSlabs = 16;
-  // Streams: one for the copies in (two concurrent host-to-device copies only get in each
-  // other's way), one for the kernels, one for the copies back, so that the link is busy in
-  // both directions while the kernels of the slab in between run.
-  struct Lanes { cudaStream_t in = nullptr, run = nullptr, out = nullptr; cudaEvent_t a_in[kMaxSlabs] = {}, done[kMaxSlabs] = {}; int dev = -1; };
-  thread_local Lanes ln;
-  if (ln.dev != dev) {
-    ln = Lanes();
-    for (cudaStream_t *st : {&ln.in, &ln.run, &ln.out}) {
+  HostCtx &hc = host_ctx();
+  if (hc.dev != dev) {
+    // first call of this thread on this device (a thread that changes device starts over; what it
+    // held on the other device stays allocated until the process ends)
+    hc = HostCtx();
+    for (cudaStream_t *st : {&hc.in, &hc.run, &hc.out}) {
       e = cudaStreamCreateWithFlags(st, cudaStreamNonBlocking);
       if (e != cudaSuccess) return cuda_fail(e, "cudaStreamCreate");
     }
     for (int i = 0; i < kMaxSlabs && e == cudaSuccess; ++i) {
-      e = cudaEventCreateWithFlags(&ln.a_in[i], cudaEventDisableTiming);
-      if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ln.done[i], cudaEventDisableTiming);
+      e = cudaEventCreateWithFlags(&hc.a_in[i], cudaEventDisableTiming);
+      if (e == cudaSuccess) e = cudaEventCreateWithFlags(&hc.done[i], cudaEventDisableTiming);
     }
-    if (e != cudaSuccess) return cuda_fail(e, "cudaEventCreate");
-    ln.dev = dev;
+    for (int i = 0; i < kHostSlots && e == cudaSuccess; ++i) {
+      e = cudaEventCreateWithFlags(&hc.slot[i].finished, cudaEventDisableTiming);
+      if (e == cudaSuccess) e = cudaHostAlloc(reinterpret_cast<void **>(&hc.slot[i].host_status), sizeof(int), cudaHostAllocDefault);
+    }
+    if (e != cudaSuccess) return cuda_fail(e, "streams, events and status words of the host-buffer calls");
+    hc.dev = dev;
+  }
+  // the slot's previous call must be over before its buffers are written again
+  HostSlot &sl = hc.slot[hc.next_ticket % kHostSlots];
+  rc = host_wait_slot(hc, sl);
+  if (rc) return rc;
+  const size_t want[4] = {a_bytes, b_bytes, o_bytes, w_bytes};
+  for (int i = 0; i < 4; ++i) {
+    if (sl.bufs[i].cap < want[i]) {
+      if (sl.bufs[i].p) cudaFree(sl.bufs[i].p);
+      sl.bufs[i].p = nullptr; sl.bufs[i].cap = 0;
+      e = cudaMalloc(&sl.bufs[i].p, want[i]);
+      if (e != cudaSuccess) return cuda_fail(e, "cudaMalloc (host-buffer entry point)");
+      sl.bufs[i].cap = want[i];
+    }
   }
 
   // ---- slabs: rows in multiples of the 128-row tile (whole batches of a batched chain), about
-  //      4 MB of A each.  With equal slabs the call takes (copy in of everything) + (one slab's
+  //      4 MB of A each.  With equal slabs a lone call takes (copy in of everything) + (one slab's
   //      kernels and copy back) + a hand-over between the engines per slab, which was measured at
   //      about 20 us on PCIe 5 x16: two to four slabs are best for 8 MB of A, eight already lose.
   //      A batched B travels with its slab.  The slab schedule of the last descriptor is kept,
   //      so a caller that repeats a shape resolves it once.
-  struct Slab { Resolved r; size_t a_off, a_len, o_off, o_len, b_off, b_len; };
-  struct HostPlan { wtc_chain_desc key; int dev = -1; int slab_env = 0; int n = 0; Slab slabs[kMaxSlabs]; };
-  thread_local HostPlan hp;
+  //      When the thread's other slot still has a call in flight the caller overlaps whole calls, and
+  //      cutting this one up only adds hand-overs: it then goes in one piece (measured, config 2, two
+  //      calls in flight: 245 us per call in one piece, 289 in two slabs, 314 in four).
   int slab_env = 0;
   if (const char *ev = getenv("WTC_HOST_SLABS")) slab_env = atoi(ev) > 0 ? atoi(ev) : 1;
-  if (hp.dev != dev || hp.slab_env != slab_env || std::memcmp(&hp.key, &d, sizeof(d)) != 0) {
-    hp.dev = -1;
+  if (!slab_env && hc.slot[(hc.next_ticket + 1) % kHostSlots].ticket >= 0) slab_env = 1;
+  if (hc.key_dev != dev || hc.slab_env != slab_env || std::memcmp(&hc.key, &d, sizeof(d)) != 0) {
+    hc.key_dev = -1;
     const bool by_batch = d.batch > 1;
     const int64_t units = by_batch ? d.batch : (d.M + wtc::kTcBlockM - 1) / wtc::kTcBlockM;
     int64_t slabs = slab_env ? slab_env : static_cast<int64_t>(a_bytes >> 22);
@@ -693,78 +735,89 @@ int wtc_matmul_softmax_host(const wtc_chain_desc *desc, const void *hostA, const
     int n = 0;
     for (int64_t u0 = 0; u0 < units; u0 += per, ++n) {
       const int64_t u1 = u0 + per < units ? u0 + per : units;
-      Slab &sl = hp.slabs[n];
+      HostSlab &hs = hc.slabs[n];
       wtc_chain_desc sd = d;
-      sl.b_off = 0; sl.b_len = 0;
+      hs.b_off = 0; hs.b_len = 0;
       if (by_batch) {
         sd.batch = static_cast<int32_t>(u1 - u0);
-        sl.a_off = static_cast<size_t>(u0) * d.a_batch_stride * in_sz;  sl.a_len = static_cast<size_t>(u1 - u0) * d.a_batch_stride * in_sz;
-        sl.o_off = static_cast<size_t>(u0) * d.o_batch_stride * out_sz; sl.o_len = static_cast<size_t>(u1 - u0) * d.o_batch_stride * out_sz;
-        if (r.b_batched) { sl.b_off = static_cast<size_t>(u0) * d.b_batch_stride * in_sz; sl.b_len = static_cast<size_t>(u1 - u0) * d.b_batch_stride * in_sz; }
+        hs.a_off = static_cast<size_t>(u0) * d.a_batch_stride * in_sz;  hs.a_len = static_cast<size_t>(u1 - u0) * d.a_batch_stride * in_sz;
+        hs.o_off = static_cast<size_t>(u0) * d.o_batch_stride * out_sz; hs.o_len = static_cast<size_t>(u1 - u0) * d.o_batch_stride * out_sz;
+        if (r.b_batched) { hs.b_off = static_cast<size_t>(u0) * d.b_batch_stride * in_sz; hs.b_len = static_cast<size_t>(u1 - u0) * d.b_batch_stride * in_sz; }
         else sd.b_batch_stride = -1;
       } else {
         const int64_t r0 = u0 * wtc::kTcBlockM, r1 = u1 * wtc::kTcBlockM < d.M ? u1 * wtc::kTcBlockM : d.M;
         sd.M = r1 - r0;
         sd.a_batch_stride = 0; sd.o_batch_stride = 0;
-        sl.a_off = static_cast<size_t>(r0) * d.lda * in_sz;  sl.a_len = static_cast<size_t>(r1 - r0) * d.lda * in_sz;
-        sl.o_off = static_cast<size_t>(r0) * d.ldo * out_sz; sl.o_len = static_cast<size_t>(r1 - r0) * d.ldo * out_sz;
+        hs.a_off = static_cast<size_t>(r0) * d.lda * in_sz;  hs.a_len = static_cast<size_t>(r1 - r0) * d.lda * in_sz;
+        hs.o_off = static_cast<size_t>(r0) * d.ldo * out_sz; hs.o_len = static_cast<size_t>(r1 - r0) * d.ldo * out_sz;
       }
-      rc = resolve(&sd, sl.r);
+      rc = resolve(&sd, hs.r);
       if (rc) return rc;
     }
-    hp.n = n; hp.key = d; hp.slab_env = slab_env; hp.dev = dev;
+    hc.n = n; hc.key = d; hc.slab_env = slab_env; hc.key_dev = dev;
   }
 
+  char *dA = static_cast<char *>(sl.bufs[0].p), *dB = static_cast<char *>(sl.bufs[1].p), *dO = static_cast<char *>(sl.bufs[2].p);
+  if (!r.b_batched || d.batch == 1) {
+    e = cudaMemcpyAsync(dB, hostB, b_bytes, cudaMemcpyHostToDevice, hc.in);
+    if (e != cudaSuccess) return cuda_fail(e, "copy of B to the device");
+  }
+  for (int n = 0; n < hc.n; ++n) {
+    HostSlab &hs = hc.slabs[n];
+    e = cudaSuccess;
+    if (hs.b_len) e = cudaMemcpyAsync(dB + hs.b_off, static_cast<const char *>(hostB) + hs.b_off, hs.b_len, cudaMemcpyHostToDevice, hc.in);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(dA + hs.a_off, static_cast<const char *>(hostA) + hs.a_off, hs.a_len, cudaMemcpyHostToDevice, hc.in);
+    if (e == cudaSuccess) e = cudaEventRecord(hc.a_in[n], hc.in);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(hc.run, hc.a_in[n], 0);
+    if (e != cudaSuccess) return cuda_fail(e, "copy of the operands to the device");
+    rc = launch_resolved(hs.r, dA + hs.a_off, dB + hs.b_off, dO + hs.o_off, sl.bufs[3].p, sl.bufs[3].cap, nullptr, 0, hc.run, nullptr);
+    if (rc) return rc;
+    e = cudaEventRecord(hc.done[n], hc.run);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(hc.out, hc.done[n], 0);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(static_cast<char *>(hostOut) + hs.o_off, dO + hs.o_off, hs.o_len, cudaMemcpyDeviceToHost, hc.out);
+    if (e != cudaSuccess) return cuda_fail(e, "copy of the result to the host");
+  }
+  // the device status word rides back behind the last rows into pinned memory: one wait
+  // covers the results and the status (no separate blocking read)
+  const int *dev_status = default_status();
+  if (!dev_status) return fail(WTC_E_CUDA, "no status word");
+  *sl.host_status = 0;
+  e = cudaMemcpyAsync(sl.host_status, dev_status, sizeof(int), cudaMemcpyDeviceToHost, hc.out);
+  if (e == cudaSuccess) e = cudaEventRecord(sl.finished, hc.out);
+  if (e != cudaSuccess) return cuda_fail(e, "copy of the status word");
+  sl.ticket = hc.next_ticket++;
+  *ticket = sl.ticket;
+  return WTC_OK;
+}
+
+int wtc_matmul_softmax_host_wait(int64_t ticket) {
+  if (ticket < 0) return WTC_OK;
+  HostCtx &hc = host_ctx();
+  if (ticket >= hc.next_ticket) return fail(WTC_E_ARG, "ticket %lld was not issued on this thread", (long long)ticket);
+  HostSlot &sl = hc.slot[ticket % kHostSlots];
+  if (sl.ticket != ticket) return WTC_OK;          // already waited for (by the caller, or by a later submit that needed the slot)
+  return host_wait_slot(hc, sl);
+}
+
+int wtc_matmul_softmax_host(const wtc_chain_desc *desc, const void *hostA, const void *hostB, void *hostOut) {
+  int64_t ticket = -1;
 #ifdef WTC_BRINGUP
   timespec ts0, ts1, ts2;
   clock_gettime(CLOCK_MONOTONIC, &ts0);
 #endif
-  if (!r.b_batched || d.batch == 1) {
-    e = cudaMemcpyAsync(bufs[1].p, hostB, b_bytes, cudaMemcpyHostToDevice, ln.in);
-    if (e != cudaSuccess) return cuda_fail(e, "copy of B to the device");
-  }
-  for (int n = 0; n < hp.n; ++n) {
-    Slab &sl = hp.slabs[n];
-    e = cudaSuccess;
-    if (sl.b_len) e = cudaMemcpyAsync(static_cast<char *>(bufs[1].p) + sl.b_off, static_cast<const char *>(hostB) + sl.b_off, sl.b_len, cudaMemcpyHostToDevice, ln.in);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(static_cast<char *>(bufs[0].p) + sl.a_off, static_cast<const char *>(hostA) + sl.a_off, sl.a_len, cudaMemcpyHostToDevice, ln.in);
-    if (e == cudaSuccess) e = cudaEventRecord(ln.a_in[n], ln.in);
-    if (e == cudaSuccess) e = cudaStreamWaitEvent(ln.run, ln.a_in[n], 0);
-    if (e != cudaSuccess) return cuda_fail(e, "copy of the operands to the device");
-    rc = launch_resolved(sl.r, static_cast<char *>(bufs[0].p) + sl.a_off, static_cast<char *>(bufs[1].p) + sl.b_off,
-                         static_cast<char *>(bufs[2].p) + sl.o_off, bufs[3].p, bufs[3].cap, nullptr, 0, ln.run, nullptr);
-    if (rc) return rc;
-    e = cudaEventRecord(ln.done[n], ln.run);
-    if (e == cudaSuccess) e = cudaStreamWaitEvent(ln.out, ln.done[n], 0);
-    if (e == cudaSuccess) e = cudaMemcpyAsync(static_cast<char *>(hostOut) + sl.o_off, static_cast<char *>(bufs[2].p) + sl.o_off, sl.o_len, cudaMemcpyDeviceToHost, ln.out);
-    if (e != cudaSuccess) return cuda_fail(e, "copy of the result to the host");
-  }
-  // (the call returns only after the copy-back stream has drained, which waited for every kernel,
-  //  which waited for every copy in: the next call finds all three streams idle)
-  // the device status word rides back behind the last rows into pinned memory: one wait
-  // covers the results and the status (no separate blocking read)
-  thread_local int *host_status = nullptr;
-  if (!host_status) {
-    e = cudaHostAlloc(reinterpret_cast<void **>(&host_status), sizeof(int), cudaHostAllocDefault);
-    if (e != cudaSuccess) { host_status = nullptr; return cuda_fail(e, "cudaHostAlloc (status word)"); }
-  }
-  const int *dev_status = default_status();
-  if (!dev_status) return fail(WTC_E_CUDA, "no status word");
-  *host_status = 0;
-  e = cudaMemcpyAsync(host_status, dev_status, sizeof(int), cudaMemcpyDeviceToHost, ln.out);
+  int rc = wtc_matmul_softmax_host_submit(desc, hostA, hostB, hostOut, &ticket);
+  if (rc) return rc;
 #ifdef WTC_BRINGUP
   clock_gettime(CLOCK_MONOTONIC, &ts1);
 #endif
-  if (e == cudaSuccess) e = cudaStreamSynchronize(ln.out);
+  rc = wtc_matmul_softmax_host_wait(ticket);
 #ifdef WTC_BRINGUP
   clock_gettime(CLOCK_MONOTONIC, &ts2);
   if (getenv("WTC_HOST_TRACE"))
-    fprintf(stderr, "host call: %d slabs, enqueue %.1f us, wait %.1f us\n", hp.n, (ts1.tv_sec - ts0.tv_sec) * 1e6 + (ts1.tv_nsec - ts0.tv_nsec) * 1e-3,
+    fprintf(stderr, "host call: enqueue %.1f us, wait %.1f us\n", (ts1.tv_sec - ts0.tv_sec) * 1e6 + (ts1.tv_nsec - ts0.tv_nsec) * 1e-3,
             (ts2.tv_sec - ts1.tv_sec) * 1e6 + (ts2.tv_nsec - ts1.tv_nsec) * 1e-3);
 #endif
-  if (e != cudaSuccess) return cuda_fail(e, "waiting for the results");
-  if (*host_status != 0) cudaMemsetAsync(default_status(), 0, sizeof(int), ln.out);   // reported once, then cleared
-  return status_result(*host_status);
+  return rc;
 }
 
 // ---- the entry point that allocates nothing -----------------------------------

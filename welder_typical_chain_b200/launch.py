@@ -23,7 +23,8 @@ KERNEL_NAMES = {0: "simt_fused", 1: "tc_cluster", 2: "tc_tiled", 3: "simt_unfuse
 EXPORTS = [
     "wtc_abi_version", "wtc_last_error", "wtc_plan_query", "wtc_matmul_softmax_workspace_bytes",
     "wtc_matmul_softmax_launch", "wtc_matmul_softmax_partial_launch", "wtc_matmul_softmax_finish_launch",
-    "wtc_matmul_softmax_host", "wtc_check_device_status", "wtc_matmul_softmax_time",
+    "wtc_matmul_softmax_host", "wtc_matmul_softmax_host_submit", "wtc_matmul_softmax_host_wait",
+    "wtc_check_device_status", "wtc_matmul_softmax_time",
     "wtc_matmul_softmax_launch_static", "wtc_row_chain_launch", "wtc_row_chain_time",
 ]
 
@@ -351,6 +352,30 @@ def time_launch(A, B, out, scale: float = 1.0, warmup: int = 10, iters: int = 20
 
 
 # ------------------------------------------------------------------ host buffers
+
+class HostChain:
+    """A chain of fixed shape called again and again with HOST arrays (numpy; pinned memory makes the
+    copies asynchronous).  submit() enqueues copy in, kernels and copy back and returns a ticket; wait()
+    blocks until that call's result is in `out`.  Keep two calls in flight (submit i+1, then wait i) and
+    both directions of the link stay busy; the arrays of a call must stay alive, and `out` unread,
+    until its wait returns."""
+
+    def __init__(self, batch, M, N, K, scale: float = 1.0, in_dtype: int = F16, out_dtype: int = F16, acc_dtype: int = F32,
+                 shared_b: bool = False, variant: int = VARIANT_FUSED, flags: int = 0):
+        self.desc = make_desc(batch, M, N, K, in_dtype, out_dtype, acc_dtype, scale, shared_b, variant, flags)
+        self._lib = lib()
+        self._lib.wtc_matmul_softmax_host_submit.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_int64)]
+        self._lib.wtc_matmul_softmax_host_wait.argtypes = [C.c_int64]
+        self._ref = C.byref(self.desc)
+
+    def submit(self, A, B, out) -> int:
+        t = C.c_int64(-1)
+        _check(self._lib.wtc_matmul_softmax_host_submit(self._ref, A.ctypes.data, B.ctypes.data, out.ctypes.data, C.byref(t)))
+        return int(t.value)
+
+    def wait(self, ticket: int) -> None:
+        _check(self._lib.wtc_matmul_softmax_host_wait(ticket))
+
 
 def matmul_softmax_host(A, B, scale: float = 1.0, out=None, out_dtype=None, acc_dtype: int = F32,
                         variant: int = VARIANT_FUSED, flags: int = 0):
