@@ -404,6 +404,23 @@ def measure(ctx, name, steps, warmup, parity=True, e2e=False, isolated=False):
                                 note="median of 5 steps with events between the phases, max over ranks; "
                                      "the gather is one NCCL all-gather of [rows,2] f32 per rank")
 
+    # ---- HBM-bound workloads: what a plain fill of this rank's output buffer takes.  The copy figure
+    #      that `roofline.peak` holds counts reads and writes together; a stream of writes alone is
+    #      slower on this part, and a kernel whose traffic is nearly all output cannot beat it.
+    if name in HBM_BOUND and 2 * sets[0][2].numel() * sets[0][2].element_size() >= res["bytes_step"]:
+        O = sets[0][2]
+        fills = []
+        for i in range(8):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            sets[i % len(sets)][2].fill_(0.5)
+            b.record(stream)
+            b.synchronize()
+            fills.append(a.elapsed_time(b) * 1e3)
+        fill_us = ctx.max_over_ranks(float(min(fills[2:])))
+        res["fill_us"] = fill_us
+        res["fill_bytes"] = int(O.numel() * O.element_size())
+
     # ---- isolated calls (the stream is idle before each), each between its own pair of events, this rank
     if isolated:
         single = []
@@ -485,6 +502,12 @@ def roofline_of(res, pk):
     if t:
         roof["traffic_source"] = f"{t['capture']}: {t['note']}" + (f"; divided by the {world} GPUs that share the workload" if strong and world > 1 else "")
     roof["algorithmic_per_launch"] = dict(flops=res["flops_step"], bytes=res["bytes_step"])
+    if res.get("fill_us"):
+        roof["write_stream"] = dict(fill_us=res["fill_us"], fill_gbs=res["fill_bytes"] / res["fill_us"] / 1e3,
+                                    output_bytes_per_gpu=res["fill_bytes"], call_us=res["ms_per_step"] * 1e3,
+                                    fill_over_call=res["fill_us"] / (res["ms_per_step"] * 1e3),
+                                    note="a torch fill_ of this GPU's output buffer, timed here with CUDA events: the time "
+                                         "the output alone needs as a plain stream of writes")
     return roof
 
 
