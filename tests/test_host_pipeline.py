@@ -276,23 +276,24 @@ def test_solver_profiles_top_candidates_through_the_profiler_binary(tmp_path):
     cache = tmp_path / "profile_cache.tsv"
     args = [solver, os.path.join(MLIR, "cfg2_f16_native_4096x1024x1024.mlir"), "--enable-generic-problem", "--max-connect-level", "1",
             "--dump-best-summary-json", str(tmp_path / "bs.json"), "--dump-candidates-tsv", str(tmp_path / "c.tsv"),
-            "--enable-profiling", "--schedule-topk", "2", "--profile-warmup", "1", "--profile-iters=3",
+            "--enable-profiling", "--schedule-topk", "3", "--profile-warmup", "1", "--profile-iters=3",
             "--profile-cache", str(cache), "--profile-profiler-bin", str(fake)]
     r = subprocess.run(args, capture_output=True, text=True)
     assert r.returncode == 0, r.stderr
     assert "tileN=128" in r.stdout                      # the faster measured tile wins over the model's first choice
     rows = [l.split("\t") for l in open(tmp_path / "c.tsv").read().splitlines()]
     col = rows[0].index("profiledMs")
-    assert [float(x[col]) for x in rows[1:3]] == [0.25, 0.75] and all(float(x[col]) == -1 for x in rows[3:])
+    # (the model's first three: 128x256x64, its 32-deep sibling, then 128x128x64)
+    assert [float(x[col]) for x in rows[1:4]] == [0.25, 0.75, 0.75] and all(float(x[col]) == -1 for x in rows[4:])
     assert json.load(open(tmp_path / "bs.json"))["best"]["profiledMs"] == 0.25
     lines = open(cache).read().splitlines()
-    assert len(lines) == 2 and all(re.fullmatch(r"wtc_b200_chain\|.*\|tile=128x(128|256)x64\|level=1\|profile_key_rev=\S+\t0\.(25|75)", l) for l in lines)
-    assert len(open(calls).read().splitlines()) == 2 and "--warmup=1 --iters=3" in open(calls).read()
+    assert len(lines) == 3 and all(re.fullmatch(r"wtc_b200_chain\|.*\|tile=128x(128|256)x(32|64)\|level=1\|profile_key_rev=\S+\t0\.(25|75)", l) for l in lines)
+    assert len(open(calls).read().splitlines()) == 3 and "--warmup=1 --iters=3" in open(calls).read()
     # second run: the cache answers, the profiler is not started (it would now fail)
     fake.write_text("#!/bin/bash\nexit 3\n")
     r = subprocess.run(args, capture_output=True, text=True)
     assert r.returncode == 0 and "tileN=128" in r.stdout
-    assert len(open(cache).read().splitlines()) == 2
+    assert len(open(cache).read().splitlines()) == 3
     # a profiler that fails leaves the candidates unmeasured and the model's order in place
     r = subprocess.run(args[:-4] + ["--profile-profiler-bin", str(fake)], capture_output=True, text=True)
     assert r.returncode == 0 and "tileN=256" in r.stdout

@@ -11,7 +11,8 @@
 //                    kernel (row_softmax_kernels.cu) rescales the rows.  Used when
 //                    a row does not fit one cluster, and for skinny M.
 //
-// Warp roles: ONE thread of warp 0 feeds shared memory with TMA, ONE thread of warp 1
+// Warp roles: ONE thread of warp 0 feeds shared memory with TMA (its warp only helps to
+// request the first stages of the first tile, one box per lane), ONE thread of warp 1
 // issues tcgen05.mma (warp 1 also owns the TMEM allocation), the remaining warps are the
 // softmax epilogue.  The two single-thread loops are kept as short as possible: the tensor
 // pipe holds only a few instructions ahead, so every cycle the issuing thread spends on
@@ -39,10 +40,13 @@
 //               fourth operand stage.
 // PAIR: two CTAs issue one 256-row tcgen05 cta_group::2 MMA (tiled flavour, long K).
 // OUT32: f32 probabilities.
+// KD, TM: K depth of a pipeline stage (64; 32 or 128 on request) and rows of a tile (128;
+// 64 on request, tcgen05.mma with M = 64) -- the schedule's tileK and tileM.
 //
-// Operand layouts: A [M,K] is K-major, staged as 128 rows x 128 B with the 128-byte
-// swizzle.  B [K,N] has N contiguous, i.e. it is MN-major for the MMA: it is staged
-// as BN/64 blocks of (64 k-rows x 128 B), and the instruction descriptor's B-major
+// Operand layouts: A [M,K] is K-major, staged as TM rows x 128 B with the 128-byte
+// swizzle (64-byte rows and swizzle for 32-deep stages, two 128-byte blocks side by side
+// for 128-deep ones).  B [K,N] has N contiguous, i.e. it is MN-major for the MMA: it is
+// staged as BN/64 blocks of (KD k-rows x 128 B), and the instruction descriptor's B-major
 // bit asks the tensor core to transpose it.  No operand is pre-transposed.
 #include "wtc_kernels.h"
 #include "wtc_ptx.cuh"

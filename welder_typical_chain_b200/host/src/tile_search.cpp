@@ -99,7 +99,15 @@ std::vector<Candidate> enumerateCandidates(const ir::ChainSpec &spec, const Arch
         c.threadTileM = 1; c.threadTileN = std::max<int64_t>(1, tn / 2);   // one epilogue thread: one row x half the tile
         c.stages = static_cast<int>(stages);
         c.clusterN = twoPass ? 1 : static_cast<int>(clusterN);
-        c.implemented = f16 && tm == 128 && (tn == 256 || tn == 128) && tk == 64;   // tile shapes the kernel library has
+        // tile shapes the kernel library has (the rule of tc_stage_depth_legal in csrc/fused_tc_kernel.cu):
+        // 128 x {128,256} x 64 always; with f16 probabilities in the fused variant also 32-deep stages,
+        // 128-deep stages (with 256 columns only in the two-pass schedule) and 64-row tiles (stages 32 or 64 deep)
+        const bool wide = tn == 256 || tn == 128;
+        const bool family = fused && spec.outType == "f16";
+        c.implemented = f16 && wide &&
+                        ((tm == 128 && tk == 64) ||
+                         (family && tm == 128 && (tk == 32 || (tk == 128 && (tn == 128 || twoPass)))) ||
+                         (family && tm == 64 && (tk == 32 || tk == 64)));
         c.bytesA = bytesA; c.bytesB = bytesB; c.bytesC = bytesC; c.bytesCut = bytesCut;
         c.score = (bytesA + bytesB + bytesC + bytesCut) * waves;
         // latency model: the slowest of tensor time (M=64 MMAs run at half rate), L2 operand feed,
@@ -127,6 +135,9 @@ std::vector<Candidate> enumerateCandidates(const ir::ChainSpec &spec, const Arch
     // among tiles that have kernels the latency model decides (it knows about idle SMs and
     // cluster residency); the rest keep the reference's traffic x waves order
     if (x.implemented && x.estimatedLatencyUs != y.estimatedLatencyUs) return x.estimatedLatencyUs < y.estimatedLatencyUs;
+    // the model does not see the stage depth: the 64-deep kernels are the tuned ones (on-device
+    // profiling of the candidates, when enabled, replaces this order with measured times)
+    if (x.implemented && (x.tileK == 64) != (y.tileK == 64)) return x.tileK == 64;
     if (x.score != y.score) return x.score < y.score;
     return x.estimatedLatencyUs < y.estimatedLatencyUs;
   });
