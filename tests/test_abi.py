@@ -134,3 +134,26 @@ def test_no_cpu_fallback(wtc_lib):
     assert e.value.code == -4
     with pytest.raises(wtc_lib.WtcError):
         wtc_lib.matmul_softmax(torch.zeros(4, 8), torch.zeros(8, 8))
+
+
+def test_host_call_tickets_without_a_device(wtc_lib):
+    """The ticket rules of the two-halved host-buffer call need no device: an empty chain is complete at
+    once (ticket -1), waiting for a ticket nobody issued is an argument error, and without a device a
+    submit fails loudly like every other launch."""
+    import ctypes as C
+    import numpy as np
+    import torch
+    L = wtc_lib.lib()
+    L.wtc_matmul_softmax_host_submit.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_int64)]
+    L.wtc_matmul_softmax_host_wait.argtypes = [C.c_int64]
+    t = C.c_int64(123)
+    empty = wtc_lib.make_desc(1, 0, 64, 64)
+    assert L.wtc_matmul_softmax_host_submit(C.byref(empty), None, None, None, C.byref(t)) == 0 and t.value == -1
+    assert L.wtc_matmul_softmax_host_wait(-1) == 0
+    assert L.wtc_matmul_softmax_host_submit(C.byref(empty), None, None, None, None) == -1
+    assert L.wtc_matmul_softmax_host_wait(1 << 40) == -1 and b"not issued" in L.wtc_last_error()
+    if not torch.cuda.is_available():
+        a = np.zeros((128, 64), np.float16)
+        d = wtc_lib.make_desc(1, 128, 64, 64)
+        assert L.wtc_matmul_softmax_host_submit(C.byref(d), a.ctypes.data, a.ctypes.data, a.ctypes.data, C.byref(t)) == -4
+        assert t.value == -1
