@@ -53,6 +53,13 @@ extern "C" {
 #define WTC_FLAG_EPILOGUE_RELAY 0x10 /* cluster flavour: two warp groups relay consecutive tiles      */
 #define WTC_FLAG_NO_PAIR 0x20        /* tiled flavour: never pair CTAs for tcgen05 cta_group::2       */
 #define WTC_FLAG_PAIR 0x40           /* tiled flavour: pair CTAs whenever there are two row blocks    */
+/* The caller promises that A and B are not written by work that is still running earlier on the
+ * stream (they were resident before, or the caller ordered them itself).  The tensor-core kernels
+ * are launched behind one another with programmatic stream serialisation; by default their loads
+ * wait until the previous launch on the stream is complete, because its output may be this
+ * launch's operands.  With this flag only the stores wait (the previous launch may still read or
+ * write the output buffer), and the loads of one call run under the tail of the one before. */
+#define WTC_FLAG_OPERANDS_READY 0x80
 
 /* error codes */
 #define WTC_OK 0

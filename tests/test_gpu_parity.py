@@ -482,6 +482,7 @@ def test_few_rows_wide_row_rescale_is_split_over_ctas(w, cuda_dev):
     "FLAG_EPILOGUE_SPLIT",      # eight epilogue warps share a tile
     "FLAG_PAIR",                # tcgen05 cta_group::2 whenever the tiled flavour has two row blocks
     "FLAG_NO_PAIR",             # never pair
+    "FLAG_OPERANDS_READY",      # loads do not wait for the previous launch on the stream, only the stores do
     None,                       # the launch layer's own choice
 ])
 def test_every_kernel_variant_matches_the_checker(w, cuda_dev, extra):
@@ -505,3 +506,23 @@ def test_every_kernel_variant_matches_the_checker(w, cuda_dev, extra):
     got = _run(w, cuda_dev, A, B, 1.0, acc_dtype=w.F16, flags=xf)
     ref = np.stack([oracle.chain(A[i], B[i], 1.0, acc=oracle.ACC_F16_SEQ) for i in range(3)])
     assert np.abs(got.astype(np.float64) - ref).max() < 5e-3
+
+
+def test_operands_ready_keeps_the_order_of_the_stores(w, cuda_dev):
+    """With WTC_FLAG_OPERANDS_READY a call's loads run under the tail of the call before it, but its
+    stores still come after: back-to-back calls with different operands into ONE output buffer leave
+    the last call's result, for every epilogue form (single tile, several tiles per CTA, split, tiled)."""
+    import torch
+    for (M, N, K, extra) in ((4096, 1024, 256, 0), (9000, 2048, 64, 0), (1024, 1024, 128, w.FLAG_EPILOGUE_SPLIT),
+                             (600, 2304, 128, 0)):
+        As = [torch.from_numpy(oracle.normal((M, K), 300 + i)).to(cuda_dev) for i in range(6)]
+        B = torch.from_numpy(oracle.normal((K, N), 310)).to(cuda_dev)
+        out = torch.empty((M, N), dtype=torch.float16, device=cuda_dev)
+        calls = [w.PreparedCall(a, B, out, 0.05, flags=w.FLAG_OPERANDS_READY | extra) for a in As]
+        sp = w.current_stream_ptr()
+        for rep in range(3):
+            for c in calls:
+                c.launch(sp)
+        w.check_device_status()
+        torch.cuda.synchronize()
+        _check(out.cpu().numpy(), oracle.chain(As[-1].cpu().numpy(), B.cpu().numpy(), 0.05))

@@ -9,7 +9,7 @@ from .launch import (  # noqa: F401
     matmul_softmax, matmul_softmax_host, HostChain, matmul_softmax_partial, matmul_softmax_finish,
     time_launch, check_device_status, row_softmax, row_variance, RowChainDesc, ROW_SOFTMAX, ROW_VARIANCE, PreparedCall, PreparedShardCall, current_stream_ptr, matmul_softmax_static,
     F32, F16, VARIANT_FUSED, VARIANT_BASELINE, FLAG_FORCE_SIMT, FLAG_FORCE_TILED, FLAG_MATMUL_F16,
-    FLAG_EPILOGUE_SPLIT, FLAG_EPILOGUE_RELAY, FLAG_NO_PAIR, FLAG_PAIR,
+    FLAG_EPILOGUE_SPLIT, FLAG_EPILOGUE_RELAY, FLAG_NO_PAIR, FLAG_PAIR, FLAG_OPERANDS_READY,
     KERNEL_SIMT_FUSED, KERNEL_TC_CLUSTER, KERNEL_TC_TILED, KERNEL_SIMT_UNFUSED, KERNEL_TC_UNFUSED,
 )
 

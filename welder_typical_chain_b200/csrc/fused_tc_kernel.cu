@@ -543,6 +543,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       if (lead) mbar_expect_tx(&stats_bar[sset], cluster_n * BM * 8);
       if (!mbar_wait(&xdone[ab], tile_phase)) { record_failure(p.status, WTC_DEV_TIMEOUT_ACCUM); break; }
       tc_fence_after_sync();
+      if (p.operands_ready && it == 0) grid_dependency_wait();   // the store group is the relay's only writer of global memory
       if (lead && it == 8) WTC_STAMP(p, TS_R_XDONE8);
       const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ab * BN + half * HC;
       const int col0 = nb * BN + half * HC;
@@ -616,6 +617,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       if (!mbar_wait(&accum_full[0], 0)) record_failure(p.status, WTC_DEV_TIMEOUT_ACCUM);
       else {
         tc_fence_after_sync();
+        if (p.operands_ready) grid_dependency_wait();
         if (lead) WTC_STAMP(p, TS_ACCUM);
         const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + part * HC;
         const int col0 = nb * BN + part * HC;
@@ -715,8 +717,9 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   if (RELAY) setmaxnreg_dec<48>();
   if (warp == 0) {
     // ======================= TMA producer ====================================
-    // programmatic dependent launch: the operands may be the previous kernel's output
-    grid_dependency_wait();
+    // programmatic dependent launch: the operands may be the previous kernel's output -- unless the
+    // caller has said they are not; then only the stores wait (see the epilogues)
+    if (!p.operands_ready) grid_dependency_wait();
     if (lane == 0) WTC_STAMP(p, TS_DEPS);
     if (!PAIR && first < p.num_items) {
       // the first stages of the first tile, one box per lane (box 0 of a stage is A's, the
@@ -843,6 +846,7 @@ fused_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       if (CLUSTER && lead) mbar_expect_tx(&stats_bar[par], cluster_n * BM * 8);
       if (!mbar_wait(&accum_full[ab], tile_phase)) { record_failure(p.status, WTC_DEV_TIMEOUT_ACCUM); break; }
       tc_fence_after_sync();
+      if (p.operands_ready && it == 0) grid_dependency_wait();   // nothing of this warp has touched global memory yet
       if (lead && it == 0) WTC_STAMP(p, TS_ACCUM);
       const uint32_t tbase = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + ab * BN + half * HC;
       const int col0 = nb * BN + half * HC;               // first matrix column of this thread

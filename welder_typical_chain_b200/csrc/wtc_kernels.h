@@ -25,6 +25,7 @@ struct TcParams {
   int pair_mode;   // tiled flavour: 0 choose, 1 never pair CTAs, 2 pair whenever the shape allows
   int epilogue_mode;  // cluster flavour: kEpilogue*
   int use_pdl;     // launch with programmatic stream serialisation
+  int operands_ready;  // A and B do not depend on earlier work on the stream: only the stores wait for it
   int round_logits_f16;  // chain spelled with an f16 matmul result: round s to f16 before the softmax
   int stage_k;     // K depth of a pipeline stage (0: 64)
   int tile_rows;   // rows of a tile (0: 128)

@@ -469,6 +469,7 @@ int launch_resolved(Resolved &r, const void *A, const void *B, void *Out, void *
     p.timeline = g_timeline ? g_timeline + static_cast<size_t>(g_timeline_launch++ % 4) * 148 * 48 : nullptr;
 #endif
     p.use_pdl = g_use_pdl;
+    p.operands_ready = (d.flags & WTC_FLAG_OPERANDS_READY) ? 1 : 0;
     p.out_f32 = out32;
     p.stage_k = r.kd;
     p.tile_rows = r.tm;

@@ -17,6 +17,7 @@ F32, F16 = 0, 1
 VARIANT_FUSED, VARIANT_BASELINE = 0, 1
 FLAG_FORCE_SIMT, FLAG_FORCE_TILED, FLAG_MATMUL_F16 = 0x1, 0x2, 0x4
 FLAG_EPILOGUE_SPLIT, FLAG_EPILOGUE_RELAY, FLAG_NO_PAIR, FLAG_PAIR = 0x8, 0x10, 0x20, 0x40
+FLAG_OPERANDS_READY = 0x80   # A and B do not depend on earlier work on the stream: only the stores wait for it
 KERNEL_SIMT_FUSED, KERNEL_TC_CLUSTER, KERNEL_TC_TILED, KERNEL_SIMT_UNFUSED, KERNEL_TC_UNFUSED = 0, 1, 2, 3, 4
 KERNEL_NAMES = {0: "simt_fused", 1: "tc_cluster", 2: "tc_tiled", 3: "simt_unfused", 4: "tc_unfused"}
 
