@@ -723,7 +723,9 @@ int wtc_matmul_softmax_host_submit(const wtc_chain_desc *desc, const void *hostA
   //      calls in flight: 245 us per call in one piece, 289 in two slabs, 314 in four).
   int slab_env = 0;
   if (const char *ev = getenv("WTC_HOST_SLABS")) slab_env = atoi(ev) > 0 ? atoi(ev) : 1;
-  if (!slab_env && hc.slot[(hc.next_ticket + 1) % kHostSlots].ticket >= 0) slab_env = 1;
+  if (!slab_env)
+    for (const HostSlot &other : hc.slot)
+      if (&other != &sl && other.ticket >= 0) slab_env = 1;
   if (hc.key_dev != dev || hc.slab_env != slab_env || std::memcmp(&hc.key, &d, sizeof(d)) != 0) {
     hc.key_dev = -1;
     const bool by_batch = d.batch > 1;
