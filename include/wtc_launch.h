@@ -209,8 +209,7 @@ int wtc_matmul_softmax_host_wait(int64_t ticket);
  *    that device current), and, like the first launch of any kernel of the
  *    library, makes the CUDA runtime load the library's device image -- the
  *    16 MiB array included.  A host whose pool already owns HBM should make that
- *    first call at start-up, before it hands the memory out, and outside any
- *    stream capture.
+ *    first call at start-up, before it hands the memory out.
  *  - Every call on a device shares the one array.  Calls whose kernels may
  *    overlap on the GPU (two streams, two threads) race on it: serialise them.
  *    Nothing is assumed about what the previous call left there.
