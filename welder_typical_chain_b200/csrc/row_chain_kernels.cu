@@ -6,11 +6,13 @@
 //                     (sum -> mean -> squared differences -> sum -> variance -> broadcast;
 //                     backend/welder/mlir_pipeline/layernorm_variance_chain.mlir:12-104)
 //
-// Both are bandwidth-bound: every element is read once and written once.  A row is owned by
-// one warp (N <= 2048: the row lives in the warp's registers between the passes, 128-bit
-// loads and stores when the rows allow) or by one 256-thread CTA (longer rows: the row is
-// re-read from L2 for the second and third pass).  f32 or f16 elements (input and output of
-// the same type); the arithmetic is f32.
+// Both are bandwidth-bound: every element is read once and written once, with 16-byte loads and
+// stores (8 f16 or 4 f32 a lane) whenever the rows start on 16-byte boundaries and N is a
+// multiple of the vector.  A row is owned by one warp (N <= 2048: 64 values a lane) or by one
+// CTA of up to 512 threads (f32 rows up to 32768, f16 rows up to 65536 elements: 16 to 128 values
+// a thread); in both the row lives in registers between the passes.  Longer or unaligned rows take a CTA per row that re-reads the row (from
+// L2) for the second and third pass.  f32 or f16 elements (input and output of the same type);
+// the arithmetic is f32.
 #include "wtc_kernels.h"
 #include "wtc_ptx.cuh"
 
@@ -51,69 +53,131 @@ __device__ __forceinline__ float block_reduce(float v, bool is_max, float *scrat
   return t;
 }
 
-// KIND 0: softmax, 1: variance.  One warp per row, row in registers (strided by lane: element j
-// of the row is value j / 32 of lane j % 32, so a warp's loads are contiguous).  PER = values a
-// lane holds (rows of up to 32 * PER elements); the loops are fully unrolled over it.
-template <int KIND, bool IN16, bool OUT16, int PER>
-__global__ void __launch_bounds__(256) row_chain_warp_kernel(const void *__restrict__ X, void *__restrict__ Out, int64_t rows, int N,
-                                                             int64_t ld_in, int64_t ld_out, float c1, float c2) {
-  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (row >= rows) return;
-  const int lane = threadIdx.x & 31;
-  const int64_t in0 = row * ld_in, out0 = row * ld_out;
-  float v[PER];
+// ---- 16-byte vectors: 8 f16 or 4 f32 ----------------------------------------------------------
+template <bool F16> struct VecOf { static constexpr int N = F16 ? 8 : 4; };
+
+template <bool F16> __device__ __forceinline__ void load_vec(const void *base, int64_t elem, float (&v)[VecOf<F16>::N]) {
+  if (F16) {
+    const uint4 q = *reinterpret_cast<const uint4 *>(static_cast<const __half *>(base) + elem);
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+      v[2 * i] = f.x; v[2 * i + 1] = f.y;
+    }
+  } else {
+    const float4 q = *reinterpret_cast<const float4 *>(static_cast<const float *>(base) + elem);
+    v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+  }
+}
+template <bool F16> __device__ __forceinline__ void store_vec(void *base, int64_t elem, const float (&v)[VecOf<F16>::N]) {
+  if (F16) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) w[i] = pack_f16x2(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4 *>(static_cast<__half *>(base) + elem) = make_uint4(w[0], w[1], w[2], w[3]);
+  } else {
+    *reinterpret_cast<float4 *>(static_cast<float *>(base) + elem) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+}
+
+// The chain on a row that is spread over a group of threads (a warp, or a CTA), NV vectors a
+// thread: vector t of thread `tid` is vector number t * group + tid of the row, so that the
+// group's loads are contiguous.  `reduce(x, is_max)` reduces over the group.
+template <int KIND, bool F16, int NV, typename Reduce>
+__device__ __forceinline__ void chain_on_row(const void *X, void *Out, int64_t in0, int64_t out0, int N, int tid, int group, float c1, float c2,
+                                             Reduce reduce) {
+  constexpr int V = VecOf<F16>::N;
+  float v[NV][V];
+  // all loads first: NV independent 16-byte requests a thread
+#pragma unroll
+  for (int t = 0; t < NV; ++t) {
+    const int j = (t * group + tid) * V;
+    if (j < N) load_vec<F16>(X, in0 + j, v[t]);
+    else {
+#pragma unroll
+      for (int e = 0; e < V; ++e) v[t][e] = KIND == 0 ? -INFINITY : 0.f;
+    }
+  }
   if (KIND == 0) {
     float m = -INFINITY;
 #pragma unroll
-    for (int t = 0; t < PER; ++t) {
-      const int j = t * 32 + lane;
-      v[t] = j < N ? load_elem<IN16>(X, in0 + j) : -INFINITY;
-      m = fmaxf(m, v[t]);
-    }
-    m = warp_max_f(m);
+    for (int t = 0; t < NV; ++t)
+#pragma unroll
+      for (int e = 0; e < V; ++e) m = fmaxf(m, v[t][e]);
+    m = reduce(m, true);
+    const float mb = m * kLog2e;
     float s = 0.f;
 #pragma unroll
-    for (int t = 0; t < PER; ++t) {
-      v[t] = ex2_approx((v[t] - m) * kLog2e);     // exp(x - max); -inf padding gives 0
-      s += v[t];
-    }
-    s = warp_sum_f(s);
+    for (int t = 0; t < NV; ++t)
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        v[t][e] = ex2_approx(fmaf(v[t][e], kLog2e, -mb));     // exp(x - max); -inf padding gives 0
+        s += v[t][e];
+      }
+    s = reduce(s, false);
     const float inv = 1.0f / s;
 #pragma unroll
-    for (int t = 0; t < PER; ++t) {
-      const int j = t * 32 + lane;
-      if (j < N) store_elem<OUT16>(Out, out0 + j, v[t] * inv);
+    for (int t = 0; t < NV; ++t) {
+      const int j = (t * group + tid) * V;
+      if (j < N) {
+#pragma unroll
+        for (int e = 0; e < V; ++e) v[t][e] *= inv;
+        store_vec<F16>(Out, out0 + j, v[t]);
+      }
     }
   } else {
     float s = 0.f;
 #pragma unroll
-    for (int t = 0; t < PER; ++t) {
-      const int j = t * 32 + lane;
-      v[t] = j < N ? load_elem<IN16>(X, in0 + j) : 0.f;
-      s += v[t];
-    }
-    const float mean = warp_sum_f(s) * c1;
+    for (int t = 0; t < NV; ++t)
+#pragma unroll
+      for (int e = 0; e < V; ++e) s += v[t][e];
+    const float mean = reduce(s, false) * c1;
     float q = 0.f;
 #pragma unroll
-    for (int t = 0; t < PER; ++t) {
-      const int j = t * 32 + lane;
-      const float d = v[t] - mean;
-      if (j < N) q += d * d;
-    }
-    const float var = warp_sum_f(q) * c2;
+    for (int t = 0; t < NV; ++t) {
+      const int j = (t * group + tid) * V;
+      if (j < N) {
 #pragma unroll
-    for (int t = 0; t < PER; ++t) {
-      const int j = t * 32 + lane;
-      if (j < N) store_elem<OUT16>(Out, out0 + j, var);
+        for (int e = 0; e < V; ++e) { const float d = v[t][e] - mean; q += d * d; }
+      }
+    }
+    const float var = reduce(q, false) * c2;
+    float o[V];
+#pragma unroll
+    for (int e = 0; e < V; ++e) o[e] = var;
+#pragma unroll
+    for (int t = 0; t < NV; ++t) {
+      const int j = (t * group + tid) * V;
+      if (j < N) store_vec<F16>(Out, out0 + j, o);
     }
   }
 }
 
-// One CTA per row, any length: three passes over the row (the second and third come from L2).
+// One warp per row (eight rows a CTA), the row in the warp's registers.
+template <int KIND, bool F16, int NV>
+__global__ void __launch_bounds__(256) row_chain_warp_kernel(const void *__restrict__ X, void *__restrict__ Out, int64_t rows, int N,
+                                                             int64_t ld_in, int64_t ld_out, float c1, float c2) {
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  chain_on_row<KIND, F16, NV>(X, Out, row * ld_in, row * ld_out, N, threadIdx.x & 31, 32, c1, c2,
+                              [](float x, bool is_max) { return is_max ? warp_max_f(x) : warp_sum_f(x); });
+}
+
+// One CTA of up to 512 threads per row, the row in the CTA's registers (NV vectors a thread).
+template <int KIND, bool F16, int NV>
+__global__ void __launch_bounds__(512) row_chain_cta_kernel(const void *__restrict__ X, void *__restrict__ Out, int N, int64_t ld_in,
+                                                             int64_t ld_out, float c1, float c2) {
+  __shared__ float scratch[32];
+  chain_on_row<KIND, F16, NV>(X, Out, static_cast<int64_t>(blockIdx.x) * ld_in, static_cast<int64_t>(blockIdx.x) * ld_out, N, threadIdx.x,
+                              blockDim.x, c1, c2, [&](float x, bool is_max) { return block_reduce(x, is_max, scratch); });
+}
+
+// One CTA per row, any length and alignment: three passes over the row (the second and third come from L2).
 template <int KIND, bool IN16, bool OUT16>
 __global__ void __launch_bounds__(256) row_chain_block_kernel(const void *__restrict__ X, void *__restrict__ Out, int N, int64_t ld_in,
                                                               int64_t ld_out, float c1, float c2) {
-  __shared__ float scratch[8];
+  __shared__ float scratch[32];
   const int64_t in0 = static_cast<int64_t>(blockIdx.x) * ld_in, out0 = static_cast<int64_t>(blockIdx.x) * ld_out;
   if (KIND == 0) {
     float m = -INFINITY;
@@ -136,18 +200,31 @@ __global__ void __launch_bounds__(256) row_chain_block_kernel(const void *__rest
   }
 }
 
-template <int KIND, bool IN16, bool OUT16>
+template <int KIND, bool F16>
 cudaError_t launch_typed(const void *X, void *Out, int64_t rows, int N, int64_t ld_in, int64_t ld_out, float c1, float c2, cudaStream_t s) {
-  if (N <= kWarpRowMax) {
-    const int64_t blocks = (rows + 7) / 8;
-    if (blocks > 0x7fffffff) return cudaErrorInvalidConfiguration;
-    const unsigned g = static_cast<unsigned>(blocks);
-    if (N <= 256) row_chain_warp_kernel<KIND, IN16, OUT16, 8><<<g, 256, 0, s>>>(X, Out, rows, N, ld_in, ld_out, c1, c2);
-    else if (N <= 1024) row_chain_warp_kernel<KIND, IN16, OUT16, 32><<<g, 256, 0, s>>>(X, Out, rows, N, ld_in, ld_out, c1, c2);
-    else row_chain_warp_kernel<KIND, IN16, OUT16, 64><<<g, 256, 0, s>>>(X, Out, rows, N, ld_in, ld_out, c1, c2);
+  constexpr int V = VecOf<F16>::N;
+  constexpr int ES = F16 ? 2 : 4;
+  const bool vec = N % V == 0 && (ld_in * ES) % 16 == 0 && (ld_out * ES) % 16 == 0 &&
+                   (reinterpret_cast<uintptr_t>(X) & 15) == 0 && (reinterpret_cast<uintptr_t>(Out) & 15) == 0;
+  if (rows > 0x7fffffff) return cudaErrorInvalidConfiguration;
+  if (vec && N <= kWarpRowMax) {
+    const unsigned g = static_cast<unsigned>((rows + 7) / 8);
+    const int nv = (N + 32 * V - 1) / (32 * V);            // vectors a lane
+    constexpr int kMaxNv = 64 / V;                          // 64 values a lane at most
+    if (nv <= 1) row_chain_warp_kernel<KIND, F16, 1><<<g, 256, 0, s>>>(X, Out, rows, N, ld_in, ld_out, c1, c2);
+    else if (nv <= 2) row_chain_warp_kernel<KIND, F16, 2><<<g, 256, 0, s>>>(X, Out, rows, N, ld_in, ld_out, c1, c2);
+    else if (nv <= 4) row_chain_warp_kernel<KIND, F16, 4><<<g, 256, 0, s>>>(X, Out, rows, N, ld_in, ld_out, c1, c2);
+    else if (nv <= 8 || kMaxNv == 8) row_chain_warp_kernel<KIND, F16, 8><<<g, 256, 0, s>>>(X, Out, rows, N, ld_in, ld_out, c1, c2);
+    else row_chain_warp_kernel<KIND, F16, kMaxNv><<<g, 256, 0, s>>>(X, Out, rows, N, ld_in, ld_out, c1, c2);
+  } else if (vec && N <= 512 * 16 * V) {
+    // as many threads as the row needs with 4, 8 or 16 vectors a thread, in whole warps, 512 at most
+    const unsigned g = static_cast<unsigned>(rows);
+    auto threads_for = [&](int nv) { return (((N + nv * V - 1) / (nv * V)) + 31) & ~31; };
+    if (threads_for(4) <= 512) row_chain_cta_kernel<KIND, F16, 4><<<g, threads_for(4), 0, s>>>(X, Out, N, ld_in, ld_out, c1, c2);
+    else if (threads_for(8) <= 512) row_chain_cta_kernel<KIND, F16, 8><<<g, threads_for(8), 0, s>>>(X, Out, N, ld_in, ld_out, c1, c2);
+    else row_chain_cta_kernel<KIND, F16, 16><<<g, threads_for(16), 0, s>>>(X, Out, N, ld_in, ld_out, c1, c2);
   } else {
-    if (rows > 0x7fffffff) return cudaErrorInvalidConfiguration;
-    row_chain_block_kernel<KIND, IN16, OUT16><<<static_cast<unsigned>(rows), 256, 0, s>>>(X, Out, N, ld_in, ld_out, c1, c2);
+    row_chain_block_kernel<KIND, F16, F16><<<static_cast<unsigned>(rows), 256, 0, s>>>(X, Out, N, ld_in, ld_out, c1, c2);
   }
   return cudaGetLastError();
 }
@@ -158,10 +235,10 @@ cudaError_t launch_row_chain(int kind, const void *X, void *Out, int64_t rows, i
                              int out_f16, float c1, float c2, cudaStream_t s) {
   if (rows <= 0 || N <= 0) return cudaSuccess;
   if (N > 0x7fffffff) return cudaErrorInvalidValue;
+  if ((in_f16 != 0) != (out_f16 != 0)) return cudaErrorInvalidValue;
   const int n = static_cast<int>(N);
-#define WTC_ROW_CASE(K, I, O) if (kind == K && (in_f16 != 0) == I && (out_f16 != 0) == O) return launch_typed<K, I, O>(X, Out, rows, n, ld_in, ld_out, c1, c2, s);
-  WTC_ROW_CASE(0, false, false) WTC_ROW_CASE(0, true, true) WTC_ROW_CASE(1, false, false) WTC_ROW_CASE(1, true, true)
-#undef WTC_ROW_CASE
+  if (kind == 0) return in_f16 ? launch_typed<0, true>(X, Out, rows, n, ld_in, ld_out, c1, c2, s) : launch_typed<0, false>(X, Out, rows, n, ld_in, ld_out, c1, c2, s);
+  if (kind == 1) return in_f16 ? launch_typed<1, true>(X, Out, rows, n, ld_in, ld_out, c1, c2, s) : launch_typed<1, false>(X, Out, rows, n, ld_in, ld_out, c1, c2, s);
   return cudaErrorInvalidValue;
 }
 
