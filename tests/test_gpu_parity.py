@@ -194,6 +194,14 @@ def test_f16_matmul_result_chain(w, cuda_dev):
     assert np.abs(out - ref16).max() < 5e-3
     out_tc = _run(w, cuda_dev, A, B, 1.0, acc_dtype=w.F16)
     assert np.abs(out_tc.astype(np.float64) - ref16).max() < 5e-3
+    # what the kernel is specified to compute -- the f32-accumulated logit rounded to f16 ONCE, then an f32
+    # softmax -- restated here in f64 and held to the chain's own tolerance (2e-3 / 1e-3 / argmax)
+    logits = (A.astype(np.float64) @ B.astype(np.float64)).astype(np.float16).astype(np.float64)
+    e = np.exp(logits - logits.max(axis=1, keepdims=True))
+    once = e / e.sum(axis=1, keepdims=True)
+    for got in (out, out_tc):
+        r = oracle.compare(got, once)
+        assert r["ok"], r
 
 
 def test_f32_arguments_rounded_to_f16_before_the_matmul(w, cuda_dev):
