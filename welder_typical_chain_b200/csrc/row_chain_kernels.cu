@@ -10,7 +10,8 @@
 // stores (8 f16 or 4 f32 a lane) whenever the rows start on 16-byte boundaries and N is a
 // multiple of the vector.  A row is owned by one warp (N <= 2048: 64 values a lane) or by one
 // CTA of up to 512 threads (f32 rows up to 32768, f16 rows up to 65536 elements: 16 to 128 values
-// a thread); in both the row lives in registers between the passes.  Longer or unaligned rows take a CTA per row that re-reads the row (from
+// a thread; f16 rows beyond 16384 elements stay packed as loaded); in both the row lives in
+// registers between the passes.  Longer or unaligned rows take a CTA per row that re-reads the row (from
 // L2) for the second and third pass.  f32 or f16 elements (input and output of the same type);
 // the arithmetic is f32.
 #include "wtc_kernels.h"
@@ -154,6 +155,91 @@ __device__ __forceinline__ void chain_on_row(const void *X, void *Out, int64_t i
   }
 }
 
+// The same for long f16 rows with the row kept as it was loaded (8 halves in four registers
+// instead of eight f32 values): half the registers, so that two 512-thread CTAs fit an SM and the
+// phases of different rows overlap.  The exponentials are taken twice (once for the sum, once
+// for the result); the special-function unit has the headroom, the memory system does not.
+template <int KIND, int NV, typename Reduce>
+__device__ __forceinline__ void chain_on_row_packed(const void *X, void *Out, int64_t in0, int64_t out0, int N, int tid, int group, float c1,
+                                                    float c2, Reduce reduce) {
+  const __half *x = static_cast<const __half *>(X);
+  uint4 raw[NV];
+#pragma unroll
+  for (int t = 0; t < NV; ++t) {
+    const int j = (t * group + tid) * 8;
+    raw[t] = j < N ? *reinterpret_cast<const uint4 *>(x + in0 + j) : make_uint4(0u, 0u, 0u, 0u);
+  }
+  auto unpack = [](const uint4 &q, float (&v)[8]) {
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[i]));
+      v[2 * i] = f.x; v[2 * i + 1] = f.y;
+    }
+  };
+  if (KIND == 0) {
+    float m = -INFINITY;
+#pragma unroll
+    for (int t = 0; t < NV; ++t) {
+      if ((t * group + tid) * 8 < N) {
+        float v[8]; unpack(raw[t], v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) m = fmaxf(m, v[e]);
+      }
+    }
+    m = reduce(m, true);
+    const float mb = m * kLog2e;
+    float s = 0.f;
+#pragma unroll
+    for (int t = 0; t < NV; ++t) {
+      if ((t * group + tid) * 8 < N) {
+        float v[8]; unpack(raw[t], v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s += ex2_approx(fmaf(v[e], kLog2e, -mb));
+      }
+    }
+    s = reduce(s, false);
+    const float inv = 1.0f / s;
+#pragma unroll
+    for (int t = 0; t < NV; ++t) {
+      const int j = (t * group + tid) * 8;
+      if (j < N) {
+        float v[8]; unpack(raw[t], v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = ex2_approx(fmaf(v[e], kLog2e, -mb)) * inv;
+        store_vec<true>(Out, out0 + j, v);
+      }
+    }
+  } else {
+    float s = 0.f;
+#pragma unroll
+    for (int t = 0; t < NV; ++t) {
+      float v[8]; unpack(raw[t], v);             // (padding vectors are zeros)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) s += v[e];
+    }
+    const float mean = reduce(s, false) * c1;
+    float q = 0.f;
+#pragma unroll
+    for (int t = 0; t < NV; ++t) {
+      if ((t * group + tid) * 8 < N) {
+        float v[8]; unpack(raw[t], v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { const float d = v[e] - mean; q += d * d; }
+      }
+    }
+    const float var = reduce(q, false) * c2;
+    float o[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = var;
+#pragma unroll
+    for (int t = 0; t < NV; ++t) {
+      const int j = (t * group + tid) * 8;
+      if (j < N) store_vec<true>(Out, out0 + j, o);
+    }
+  }
+}
+
 // One warp per row (eight rows a CTA), the row in the warp's registers.
 template <int KIND, bool F16, int NV>
 __global__ void __launch_bounds__(256) row_chain_warp_kernel(const void *__restrict__ X, void *__restrict__ Out, int64_t rows, int N,
@@ -171,6 +257,14 @@ __global__ void __launch_bounds__(512) row_chain_cta_kernel(const void *__restri
   __shared__ float scratch[32];
   chain_on_row<KIND, F16, NV>(X, Out, static_cast<int64_t>(blockIdx.x) * ld_in, static_cast<int64_t>(blockIdx.x) * ld_out, N, threadIdx.x,
                               blockDim.x, c1, c2, [&](float x, bool is_max) { return block_reduce(x, is_max, scratch); });
+}
+
+template <int KIND, int NV>
+__global__ void __launch_bounds__(512, 2) row_chain_cta_packed_kernel(const void *__restrict__ X, void *__restrict__ Out, int N, int64_t ld_in,
+                                                                     int64_t ld_out, float c1, float c2) {
+  __shared__ float scratch[32];
+  chain_on_row_packed<KIND, NV>(X, Out, static_cast<int64_t>(blockIdx.x) * ld_in, static_cast<int64_t>(blockIdx.x) * ld_out, N, threadIdx.x,
+                                blockDim.x, c1, c2, [&](float x, bool is_max) { return block_reduce(x, is_max, scratch); });
 }
 
 // One CTA per row, any length and alignment: three passes over the row (the second and third come from L2).
@@ -221,6 +315,8 @@ cudaError_t launch_typed(const void *X, void *Out, int64_t rows, int N, int64_t 
     const unsigned g = static_cast<unsigned>(rows);
     auto threads_for = [&](int nv) { return (((N + nv * V - 1) / (nv * V)) + 31) & ~31; };
     if (threads_for(4) <= 512) row_chain_cta_kernel<KIND, F16, 4><<<g, threads_for(4), 0, s>>>(X, Out, N, ld_in, ld_out, c1, c2);
+    else if (F16 && threads_for(8) <= 512) row_chain_cta_packed_kernel<KIND, 8><<<g, threads_for(8), 0, s>>>(X, Out, N, ld_in, ld_out, c1, c2);
+    else if (F16) row_chain_cta_packed_kernel<KIND, 16><<<g, threads_for(16), 0, s>>>(X, Out, N, ld_in, ld_out, c1, c2);
     else if (threads_for(8) <= 512) row_chain_cta_kernel<KIND, F16, 8><<<g, threads_for(8), 0, s>>>(X, Out, N, ld_in, ld_out, c1, c2);
     else row_chain_cta_kernel<KIND, F16, 16><<<g, threads_for(16), 0, s>>>(X, Out, N, ld_in, ld_out, c1, c2);
   } else {
