@@ -101,7 +101,7 @@ def test_f32_arguments_rounded_to_f16_are_recognised(tmp_path):
     chain = json.load(open(out / "ir" / "chain.json"))
     assert (chain["arg_dtype"], chain["in_dtype"], chain["acc_dtype"], chain["out_dtype"]) == ("f32", "f16", "f16", "f32")
     plan = open(out / "fused" / "05.out.nvvm.runnable.mlir").read()
-    assert 'arg_dtype = "f32", in_dtype = "f16"' in plan and "launches = 3" in plan     # two rounding passes + the fused kernel
+    assert 'arg_dtype = "f32", in_dtype = "f16"' in plan and "launches = 2" in plan     # one launch that rounds both operands + the fused kernel
     ws = int(re.search(r"workspace_bytes = (\d+)", plan).group(1))
     assert ws == 8192 * 64 * 2 + 64 * 128 * 2                                           # the two rounded copies
     bad = tmp_path / "bad.mlir"

@@ -156,43 +156,77 @@ cudaError_t launch_rescale_rows(void *out, int out_f32, int64_t rows, int N, int
                             global_stats, num_parts, rows, chunk);
 }
 
-// ---- f32 -> f16 rounding of an operand (the chain that truncates its f32 arguments) --------
+// ---- f32 -> f16 rounding of both operands (the chain that truncates its f32 arguments) --------
 namespace {
-__global__ void round_to_f16_kernel(const float *__restrict__ src, __half *__restrict__ dst, int64_t rows, int64_t cols,
-                                    int64_t ld, int64_t batch_stride, int64_t total_quads, int vec) {
-  // one thread per four consecutive columns of a row (or per element when rows are not 16-byte friendly)
-  for (int64_t q = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; q < total_quads;
-       q += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    if (vec) {
-      const int64_t per_row = cols >> 2;
-      const int64_t row = q / per_row, c = (q - row * per_row) << 2;
-      const int64_t b = row / rows, r = row - b * rows;
-      const float4 v = *reinterpret_cast<const float4 *>(src + b * batch_stride + r * ld + c);
-      const __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
-      uint2 o;
-      o.x = *reinterpret_cast<const uint32_t *>(&lo);
-      o.y = *reinterpret_cast<const uint32_t *>(&hi);
-      *reinterpret_cast<uint2 *>(dst + row * cols + c) = o;
-    } else {
-      const int64_t row = q / cols, c = q - row * cols;
-      const int64_t b = row / rows, r = row - b * rows;
-      dst[q] = __float2half_rn(src[b * batch_stride + r * ld + c]);
-    }
+struct RoundJob {
+  const float *src; __half *dst;
+  int64_t rows, cols, ld, batch_stride, work;   // work: quads (vec) or elements
+  int vec;
+};
+
+__device__ __forceinline__ void round_one(const RoundJob &j, int64_t q) {
+  if (j.vec) {
+    const int64_t per_row = j.cols >> 2;
+    const int64_t row = q / per_row, c = (q - row * per_row) << 2;
+    const int64_t b = row / j.rows, r = row - b * j.rows;
+    const float4 v = *reinterpret_cast<const float4 *>(j.src + b * j.batch_stride + r * j.ld + c);
+    const __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+    uint2 o;
+    o.x = *reinterpret_cast<const uint32_t *>(&lo);
+    o.y = *reinterpret_cast<const uint32_t *>(&hi);
+    *reinterpret_cast<uint2 *>(j.dst + row * j.cols + c) = o;
+  } else {
+    const int64_t row = q / j.cols, c = q - row * j.cols;
+    const int64_t b = row / j.rows, r = row - b * j.rows;
+    j.dst[q] = __float2half_rn(j.src[b * j.batch_stride + r * j.ld + c]);
   }
+}
+
+// One launch rounds A and B: one thread per four consecutive columns of a row (or per element
+// when the rows are not 16-byte friendly), the work items of A first, then B's.  Launched with
+// programmatic stream serialisation: the chain's kernel behind it starts its set-up as soon as
+// these CTAs are resident, and waits for them to finish before its first load.
+__global__ void round_to_f16_kernel(const RoundJob a, const RoundJob b) {
+  grid_dependency_wait();                    // the operands may be the previous kernel's output
+  grid_launch_dependents();
+  const int64_t total = a.work + b.work;
+  for (int64_t q = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; q < total;
+       q += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    if (q < a.work) round_one(a, q);
+    else round_one(b, q - a.work);
+  }
+}
+
+RoundJob make_job(const float *src, void *dst, int batch, int64_t rows, int64_t cols, int64_t ld, int64_t batch_stride) {
+  RoundJob j;
+  j.src = src; j.dst = static_cast<__half *>(dst);
+  j.rows = rows; j.cols = cols; j.ld = ld; j.batch_stride = batch_stride;
+  const int64_t total = static_cast<int64_t>(batch) * rows * cols;
+  j.vec = (cols % 4 == 0) && (ld % 4 == 0) && (batch_stride % 4 == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0) &&
+          ((reinterpret_cast<uintptr_t>(dst) & 7) == 0);
+  j.work = j.vec ? total / 4 : total;
+  return j;
 }
 } // namespace
 
-cudaError_t launch_round_to_f16(const float *src, void *dst, int batch, int64_t rows, int64_t cols, int64_t ld,
-                                int64_t batch_stride, cudaStream_t s) {
-  const int64_t total = static_cast<int64_t>(batch) * rows * cols;
-  if (total == 0) return cudaSuccess;
-  const int vec = (cols % 4 == 0) && (ld % 4 == 0) && (batch_stride % 4 == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0) &&
-                  ((reinterpret_cast<uintptr_t>(dst) & 7) == 0);
-  const int64_t work = vec ? total / 4 : total;
+cudaError_t launch_round_to_f16(const float *A, void *dstA, int batchA, int64_t rowsA, int64_t colsA, int64_t ldA, int64_t strideA,
+                                const float *B, void *dstB, int batchB, int64_t rowsB, int64_t colsB, int64_t ldB, int64_t strideB,
+                                cudaStream_t s) {
+  const RoundJob a = make_job(A, dstA, batchA, rowsA, colsA, ldA, strideA);
+  const RoundJob b = make_job(B, dstB, batchB, rowsB, colsB, ldB, strideB);
+  const int64_t work = a.work + b.work;
+  if (work == 0) return cudaSuccess;
   const int64_t blocks = (work + 255) / 256;
-  round_to_f16_kernel<<<static_cast<unsigned>(blocks < 148 * 16 ? blocks : 148 * 16), 256, 0, s>>>(
-      src, static_cast<__half *>(dst), rows, cols, ld, batch_stride, work, vec);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(blocks < 148 * 16 ? blocks : 148 * 16), 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, round_to_f16_kernel, a, b);
 }
 
 } // namespace wtc

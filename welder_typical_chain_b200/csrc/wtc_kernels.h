@@ -81,10 +81,11 @@ cudaError_t launch_rescale_rows(void *out, int out_f32, int64_t rows, int N, int
                                 const float2 *tile_stats, const float2 *global_stats, int num_parts,
                                 cudaStream_t s);
 
-// dst[b][r][c] (dense f16: row stride cols, batch stride rows * cols) = round-to-nearest-even of
-// src[b * batch_stride + r * ld + c] (f32).
-cudaError_t launch_round_to_f16(const float *src, void *dst, int batch, int64_t rows, int64_t cols, int64_t ld,
-                                int64_t batch_stride, cudaStream_t s);
+// For both operands in one launch: dst[b][r][c] (dense f16: row stride cols, batch stride rows * cols)
+// = round-to-nearest-even of src[b * batch_stride + r * ld + c] (f32).
+cudaError_t launch_round_to_f16(const float *A, void *dstA, int batchA, int64_t rowsA, int64_t colsA, int64_t ldA, int64_t strideA,
+                                const float *B, void *dstB, int batchB, int64_t rowsB, int64_t colsB, int64_t ldB, int64_t strideB,
+                                cudaStream_t s);
 
 // The four softmax passes of the unfused baseline on logits C32[rows, N] already in global
 // memory: row max -> exp -> row sum -> divide (intermediates E[rows, N], mx[rows], sum[rows]).

@@ -123,7 +123,7 @@ int resolve(const wtc_chain_desc *in, Resolved &r) {
     r.stage_a = align256(static_cast<size_t>(d.batch) * d.M * d.K * 2);
     r.stage_b = align256(static_cast<size_t>(bb ? d.batch : 1) * d.K * d.N * 2);
     r.plan.workspace_bytes += r.stage_a + r.stage_b;
-    r.plan.launches += 2;
+    r.plan.launches += 1;     // one launch rounds both operands
     return WTC_OK;
   }
 
@@ -380,10 +380,9 @@ int launch_resolved(Resolved &r, const void *A, const void *B, void *Out, void *
       return fail(WTC_E_WORKSPACE, "rounding the f32 operands to f16 needs %zu workspace bytes, got %zu", r.plan.workspace_bytes, ws_bytes);
     if ((reinterpret_cast<uintptr_t>(ws) & 15) != 0) return fail(WTC_E_ARG, "workspace must be 16-byte aligned");
     unsigned char *base = static_cast<unsigned char *>(ws);
-    cudaError_t e = wtc::launch_round_to_f16(static_cast<const float *>(A), base, d.batch, d.M, d.K, d.lda, d.a_batch_stride, s);
-    if (e == cudaSuccess)
-      e = wtc::launch_round_to_f16(static_cast<const float *>(B), base + r.stage_a, r.b_batched ? d.batch : 1, d.K, d.N, d.ldb,
-                                   r.b_batched ? d.b_batch_stride : 0, s);
+    const cudaError_t e = wtc::launch_round_to_f16(static_cast<const float *>(A), base, d.batch, d.M, d.K, d.lda, d.a_batch_stride,
+                                                   static_cast<const float *>(B), base + r.stage_a, r.b_batched ? d.batch : 1, d.K, d.N, d.ldb,
+                                                   r.b_batched ? d.b_batch_stride : 0, s);
     if (e != cudaSuccess) return cuda_fail(e, "operand rounding launch");
     Resolved ri;
     int rc = resolve(&r.inner, ri);
