@@ -500,6 +500,49 @@ def measure(ctx, name, steps, warmup, parity=True, e2e=False, isolated=False):
     return res
 
 
+def measure_row_chains(ctx, pk, steps):
+    """The two row-only chains of the reference's backend inputs (row softmax of a given matrix; row
+    variance broadcast along the row) on this rank's GPU: microseconds per call over rotating buffers
+    larger than L2, bytes read + written per second against the measured copy rate, and a check of a
+    few rows against the CPU checker.  Rank 0 only (the chains shard by rows without any exchange)."""
+    import numpy as np
+    from oracle import oracle
+    torch, wtc = ctx.torch, ctx.wtc
+    out = {}
+    cases = [("row_softmax", "f16", 65536, 2048), ("row_softmax", "f32", 65536, 2048), ("row_softmax", "f16", 8192, 32000),
+             ("row_variance", "f32", 16384, 8192), ("row_variance", "f16", 8192, 32000)]
+    for kind, dt, rows, n in cases:
+        tdt = torch.float16 if dt == "f16" else torch.float32
+        xs = [torch.randn((rows, n), device=ctx.dev, dtype=torch.float32).mul_(2.0).to(tdt) for _ in range(3)]
+        outs = [torch.empty_like(x) for x in xs]
+        fn = wtc.row_softmax if kind == "row_softmax" else wtc.row_variance
+        for i in range(3):
+            fn(xs[i], out=outs[i])
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        k = max(6, min(steps, 30))
+        a.record()
+        for i in range(k):
+            fn(xs[i % 3], out=outs[i % 3])
+        b.record()
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) * 1e3 / k
+        nbytes = 2 * rows * n * xs[0].element_size()
+        sample = [0, 1, rows // 2, rows - 1]
+        x = xs[(k - 1) % 3][sample].cpu().numpy()
+        got = outs[(k - 1) % 3][sample].cpu().numpy().astype(np.float64)
+        if kind == "row_softmax":
+            ok = bool(oracle.compare(got, oracle.row_softmax(x))["ok"])
+        else:
+            ref = oracle.row_variance(x)
+            ok = bool(np.abs(got - ref).max() <= (2e-3 if dt == "f16" else 1e-4) * np.abs(ref).max())
+        out[f"{kind}_{dt}_{rows}x{n}"] = dict(us_per_call=us, gbs=nbytes / us / 1e3, frac_of_copy_rate=nbytes / us / 1e3 / pk["hbm_gbs"],
+                                              bytes=nbytes, parity_ok=ok)
+        del xs, outs
+        torch.cuda.empty_cache()
+    return out
+
+
 def roofline_of(res, pk):
     name = res["name"]
     launch_s = res["ms_per_step"] * 1e-3
@@ -538,6 +581,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
     ap.add_argument("--no-splits", action="store_true", help="skip the scaling_cfg3 / scaling_cfg4 measurements")
+    ap.add_argument("--no-siblings", action="store_true", help="skip the row-only chains (row softmax, row variance)")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
     if args.warmup < 3:
@@ -571,6 +615,10 @@ def main():
     plan = head["plan"]
     roof = roofline_of(head, pk)
     roof["kernel"] = wtc.launch.KERNEL_NAMES[plan.kernel]
+    # (rank 0 alone from here on: the other ranks have left; nothing below is a collective)
+    siblings = None
+    if args.workload == "cfg2" and not args.no_siblings and world == 1:
+        siblings = measure_row_chains(ctx, pk, args.steps)
 
     cpu = None
     if not args.no_cpu_baseline and world == 1:
@@ -626,6 +674,8 @@ def main():
         if "phases_us" in r:
             obj["phases_us"] = r["phases_us"]
         line[f"scaling_{nm}"] = obj
+    if siblings:
+        line["row_chains"] = siblings
     print(json.dumps(line), flush=True)
     ctx.close()
 
