@@ -172,6 +172,23 @@ int pick_rows(const SimtParams &p, size_t smem_limit) {
   return best;
 }
 
+// The opt-in to more than 48 KB of dynamic shared memory is per kernel instance and per device:
+// it is raised once to the largest window this instance has been asked for there, not on every call.
+template <int R, bool IN16>
+cudaError_t fused_r_window(size_t smem) {
+  static size_t granted[64] = {0};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (smem > granted[dev]) {
+    e = cudaFuncSetAttribute(simt_fused_kernel<R, IN16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    granted[dev] = smem;
+  }
+  return cudaSuccess;
+}
+
 template <int R>
 cudaError_t launch_fused_r(const void *A, const void *B, void *Out, const SimtParams &p, cudaStream_t s) {
   const size_t smem = (static_cast<size_t>(R) * kKChunk + static_cast<size_t>(R) * p.N) * sizeof(float);
@@ -179,11 +196,11 @@ cudaError_t launch_fused_r(const void *A, const void *B, void *Out, const SimtPa
   if (blocks > 0x7fffffff) return cudaErrorInvalidConfiguration;
   cudaError_t e;
   if (p.in_f16) {
-    e = cudaFuncSetAttribute(simt_fused_kernel<R, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    e = fused_r_window<R, true>(smem);
     if (e != cudaSuccess) return e;
     simt_fused_kernel<R, true><<<static_cast<unsigned>(blocks), kSimtThreads, smem, s>>>(A, B, Out, p);
   } else {
-    e = cudaFuncSetAttribute(simt_fused_kernel<R, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    e = fused_r_window<R, false>(smem);
     if (e != cudaSuccess) return e;
     simt_fused_kernel<R, false><<<static_cast<unsigned>(blocks), kSimtThreads, smem, s>>>(A, B, Out, p);
   }
