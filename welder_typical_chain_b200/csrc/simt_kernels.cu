@@ -48,8 +48,20 @@ __device__ __forceinline__ void matmul_rows(const void *A, const void *B, const 
       }
       __syncthreads();
       if (j < p.N) {
-#pragma unroll 8
-        for (int k = 0; k < kc; ++k) {
+        // sixteen independent loads of B's column are in flight before the first is used (a thread
+        // walks down one column: without this the loop is a chain of L2 round trips); k stays ascending
+        int k = 0;
+        for (; k + 16 <= kc; k += 16) {
+          float bv[16];
+#pragma unroll
+          for (int u = 0; u < 16; ++u) bv[u] = ld_elem<F16>(B, b_off + static_cast<int64_t>(k0 + k + u) * p.ldb + j);
+#pragma unroll
+          for (int u = 0; u < 16; ++u) {
+#pragma unroll
+            for (int r = 0; r < R; ++r) acc[r] = fmaf(As[r * kKChunk + k + u], bv[u], acc[r]);
+          }
+        }
+        for (; k < kc; ++k) {
           const float bv = ld_elem<F16>(B, b_off + static_cast<int64_t>(k0 + k) * p.ldb + j);
 #pragma unroll
           for (int r = 0; r < R; ++r) acc[r] = fmaf(As[r * kKChunk + k], bv, acc[r]);
